@@ -1,0 +1,432 @@
+"""Benchmark of the blockwise-int8 linear hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One "step" is one forward of the layer on one batch: block-quantize the bf16 activations
+(x [M, K]) and run the int8 block GEMM with fused dequantize against pre-quantized weights
+(W [N, K]) into a bf16 output.  The default workload is the largest Llama-2-7B projection of
+the benchmark configuration (M = 8192 tokens, K = 4096, N = 11008, block 64); the metric is the
+reference's own (``triton_functions.py:565``): 2*M*N*K / time, in tera-ops per second.
+
+With N > 1 (launched by torchrun, one rank per GPU) every rank runs the same step on its own
+batch of tokens: the layer is data-parallel in the token dimension, there is no collective on the
+path, so scaling is weak and ``value`` is the sum over ranks divided by the slowest rank's time.
+
+Prints ONE JSON line.  Besides the headline it carries
+  roofline      the GEMM kernel alone (CUDA events around its launches inside the timed region)
+  e2e           the same step through the public Python API with host buffers (pinned H2D of x, D2H of y)
+  cpu_baseline  the CPU restatement of the reference timed on this host on a bounded sample (rank 0, N = 1)
+  extra         the memory-bound kernels (quantize / dequantize sweep) and the other GEMM shapes
+``--impl reference`` times the CPU restatement only (the reference has no CPU path of its own and
+cannot be imported without a GPU and Triton 2.3; the restatement is pinned to its kernels by golden vectors).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+BLOCK = 64
+WORKLOADS = {
+    # name: (M, K, N)
+    "llama7b_up_proj_m8192": (8192, 4096, 11008),
+    "llama7b_attn_proj_m8192": (8192, 4096, 4096),
+    "llama7b_down_proj_m8192": (8192, 11008, 4096),
+    "llama7b_up_proj_m2048": (2048, 4096, 11008),
+}
+DEFAULT_WORKLOAD = "llama7b_up_proj_m8192"
+INT8_NOMINAL_TOPS = 4500.0
+HBM_FALLBACK, BF16_FALLBACK = 6650.0, 1590.0
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+    return HBM_FALLBACK, BF16_FALLBACK, "fallback"
+
+
+def ncu_traffic(key: str):
+    p = os.path.join(ROOT, "profiles", "ncu_traffic.json")
+    if os.path.exists(p):
+        return json.load(open(p)).get(key)
+    return None
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+# ---------------------------------------------------------------------------------------------------------
+# CPU restatement (reference arm and cpu_baseline)
+# ---------------------------------------------------------------------------------------------------------
+def cpu_step(O, x, wq, ws):
+    xq, xs = O.quantize(x, BLOCK)
+    return O.gemm(xq, wq.t(), xs, ws, None, BLOCK, torch.bfloat16)
+
+
+def cpu_baseline(workload: str, budget_s: float = 12.0):
+    """Times the CPU restatement on a bounded row sample of the workload; returns the cpu_baseline object."""
+    from oracle import blockwise_int8_oracle as O
+    M, K, N = WORKLOADS[workload]
+    torch.set_num_threads(os.cpu_count() or 1)
+    w = O.synthetic((N, K), 3100, std=0.02, outlier_frac=0.0)
+    wq, ws = O.quantize(w, BLOCK)
+    x = O.synthetic((256, K), 3000, outlier_frac=0.0)
+    cpu_step(O, x[:64], wq, ws)                  # warm the thread pool
+    t0 = time.perf_counter()
+    cpu_step(O, x, wq, ws)
+    t256 = time.perf_counter() - t0
+    rows = int(max(64, min(M, 256 * budget_s / max(t256, 1e-3) / 2)))
+    rows -= rows % 64
+    x = O.synthetic((rows, K), 3001, outlier_frac=0.0)
+    cpu_step(O, x, wq, ws)                       # warm
+    t0 = time.perf_counter()
+    cpu_step(O, x, wq, ws)
+    dt = time.perf_counter() - t0
+    tops = 2.0 * rows * N * K / dt / 1e12
+    return {"value": tops, "unit": "TOP/s", "cores": torch.get_num_threads(), "host_cpus": os.cpu_count(),
+            "kind": "port", "sample": f"{rows} of {M} rows of {workload} (quantize x + block GEMM, weights pre-quantized), "
+                                      f"{dt:.2f} s, torch CPU fp32 restatement"}, rows
+
+
+def run_reference(args):
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    from oracle import blockwise_int8_oracle as O
+    M, K, N = WORKLOADS[args.workload]
+    torch.set_num_threads(os.cpu_count() or 1)
+    w = O.synthetic((N, K), 3100, std=0.02, outlier_frac=0.0)
+    wq, ws = O.quantize(w, BLOCK)
+    # size one step so that warmup + steps stay within a couple of minutes
+    x = O.synthetic((256, K), 3000, outlier_frac=0.0)
+    cpu_step(O, x[:64], wq, ws)                  # warm the thread pool
+    t0 = time.perf_counter()
+    cpu_step(O, x, wq, ws)
+    t256 = time.perf_counter() - t0
+    budget = 100.0 / max(1, args.steps + args.warmup)
+    rows = int(max(64, min(M, 256 * budget / max(t256, 1e-3))))
+    rows -= rows % 64
+    x = O.synthetic((rows, K), 3001, outlier_frac=0.0)
+    for _ in range(args.warmup):
+        cpu_step(O, x, wq, ws)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_step(O, x, wq, ws)
+    dt = (time.perf_counter() - t0) / args.steps
+    tops = 2.0 * rows * N * K / dt / 1e12
+    sample = f"{rows} of {M} rows per step of {args.workload}; torch CPU fp32 restatement of the reference kernels"
+    line = {
+        "impl": "reference", "metric": "int8_block_gemm_tops", "value": tops, "unit": "TOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": args.workload, "M": M, "K": K, "N": N, "block": BLOCK, "rows_per_step": rows},
+        "cpu_baseline": {"value": tops, "unit": "TOP/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": tops, "unit": "TOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference has no CPU implementation (its wrappers assert CUDA tensors); this arm times the CPU "
+                "restatement that the golden vectors pin to the reference's kernels",
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------------------
+def time_kernel(fn, reps: int, flush) -> float:
+    """Median milliseconds of fn() over reps launches, L2 flushed before each (the flush is not timed)."""
+    ts = []
+    for _ in range(reps):
+        flush()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        b.synchronize()
+        ts.append(a.elapsed_time(b))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def extras(dev, hbm_gbs, flush):
+    """Memory-bound kernels (quantize / dequantize sweep) and the other GEMM shapes; cold L2, median of 7."""
+    import block_linear_config as cfg
+    from triton_functions import (dequantize_block_rowwise, int8_matmul_block64_rowwise_dequantize,
+                                  quantize_block_colwise, quantize_block_rowwise)
+    cfg.GROUP_SIZE, cfg.INPUT_OUTPUT_TORCH_TYPE = BLOCK, torch.bfloat16
+    out = {"quantize": [], "dequantize": [], "quantize_colwise": [], "gemm": []}
+    for n in (4096, 8192, 16384):
+        g = torch.Generator(device=dev).manual_seed(2000 + n)
+        x = torch.randn((n, n), device=dev, dtype=torch.float32, generator=g)
+        x = torch.where(torch.rand((n, n), device=dev, generator=g) < 0.001, x * 20, x).to(torch.bfloat16)
+        nbytes = n * n * (2 + 1 + 4 / BLOCK)
+        for _ in range(3):
+            q, s = quantize_block_rowwise(x)
+        ms = time_kernel(lambda: quantize_block_rowwise(x), 7, flush)
+        out["quantize"].append({"shape": [n, n], "us": ms * 1e3, "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / hbm_gbs})
+        for _ in range(3):
+            dequantize_block_rowwise(q, s)
+        ms = time_kernel(lambda: dequantize_block_rowwise(q, s), 7, flush)
+        out["dequantize"].append({"shape": [n, n], "us": ms * 1e3, "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / hbm_gbs})
+        for _ in range(3):
+            quantize_block_colwise(x)
+        ms = time_kernel(lambda: quantize_block_colwise(x), 7, flush)
+        out["quantize_colwise"].append({"shape": [n, n], "us": ms * 1e3, "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / hbm_gbs})
+        del x, q, s
+    for (k, n) in ((4096, 4096), (4096, 11008), (11008, 4096)):
+        w = (torch.randn((n, k), device=dev, generator=torch.Generator(device=dev).manual_seed(n + k)) * 0.02).to(torch.bfloat16)
+        wq, ws = quantize_block_rowwise(w)
+        for m in (1, 16, 128, 2048, 8192):
+            x = torch.randn((m, k), device=dev, generator=torch.Generator(device=dev).manual_seed(m)).to(torch.bfloat16)
+            xq, xs = quantize_block_rowwise(x)
+            f = lambda: int8_matmul_block64_rowwise_dequantize(xq, wq.t(), xs, ws)
+            for _ in range(3):
+                f()
+            ms = time_kernel(f, 7, flush)
+            ops = 2.0 * m * n * k
+            nbytes = m * k + n * k + 4 * (m + n) * k / BLOCK + 2 * m * n
+            out["gemm"].append({"M": m, "K": k, "N": n, "us": ms * 1e3, "tops": ops / ms / 1e9,
+                                "gbs": nbytes / ms / 1e6, "frac_int8_nominal": ops / ms / 1e9 / INT8_NOMINAL_TOPS,
+                                "frac_hbm": nbytes / ms / 1e6 / hbm_gbs})
+        del w, wq, ws
+    return out
+
+
+def run_ours(args):
+    rank, world, local = dist_env()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU arm")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    import block_linear_config as cfg
+    from block_linear import BlockInt8Linear
+    from blockwise_int8_linear_b200 import _lib
+    from triton_functions import int8_matmul_block64_rowwise_dequantize, quantize_block_rowwise
+
+    cfg.GROUP_SIZE, cfg.INPUT_OUTPUT_TORCH_TYPE = BLOCK, torch.bfloat16
+    M, K, N = WORKLOADS[args.workload]
+    hbm_gbs, bf16_tf, peak_src = peaks()
+
+    # Synthetic data of the benchmark configuration: activations N(0,1), weights N(0, 0.02), both bf16.
+    # Three rotating buffer sets (x, y) so that consecutive steps do not find their inputs in the 126 MB L2.
+    NSETS = 3
+    gen = torch.Generator(device=dev).manual_seed(3000 + rank)
+    xs_dev = [torch.randn((M, K), device=dev, generator=gen).to(torch.bfloat16) for _ in range(NSETS)]
+    w = (torch.randn((N, K), device=dev, generator=torch.Generator(device=dev).manual_seed(3100)) * 0.02).to(torch.bfloat16)
+    wq, ws = quantize_block_rowwise(w)
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    flush = lambda: flush_buf.fill_(1)
+
+    def step(i, ev=None):
+        x = xs_dev[i % NSETS]
+        xq, sx = quantize_block_rowwise(x)
+        if ev is not None:
+            ev[0].record()
+        y = int8_matmul_block64_rowwise_dequantize(xq, wq.t(), sx, ws)
+        if ev is not None:
+            ev[1].record()
+        return y
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            torch.distributed.barrier()
+            torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    gemm_events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_start.record()
+    for i in range(args.steps):
+        step(i, gemm_events[i])
+    t_end.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = t_start.elapsed_time(t_end)
+    gemm_ms = sum(a.elapsed_time(b) for a, b in gemm_events) / args.steps
+    if world > 1:
+        t = torch.tensor([ms_total, gemm_ms], device=dev, dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms_total, gemm_ms = t.tolist()
+    ms_step = ms_total / args.steps
+    ops_step = 2.0 * M * N * K
+    value = world * ops_step / (ms_step * 1e-3) / 1e12
+    _lib.device_status()
+
+    # ---- end to end through the public API with host buffers ----
+    lin = BlockInt8Linear(K, N, bias=False, device=dev, dtype=torch.bfloat16).eval()
+    lin.weight.data = w
+    x_host = [xs_dev[i].cpu().pin_memory() for i in range(2)]
+    y_host = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step(i):
+        xd = x_host[i % 2].to(dev, non_blocking=True)
+        with torch.no_grad():
+            y = lin(xd)
+        y_host.copy_(y, non_blocking=True)
+
+    for i in range(max(3, args.warmup)):
+        e2e_step(i)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        e2e_step(i)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        e2e_ms = t.item()
+    e2e_value = world * ops_step / (e2e_ms * 1e-3) / 1e12
+    del lin, x_host
+
+    if rank != 0:
+        if world > 1:
+            torch.distributed.destroy_process_group()
+        return
+
+    # ---- rank 0: roofline, probe, extras, CPU baseline ----
+    achieved = ops_step / (gemm_ms * 1e-3) / 1e12
+    probe = None
+    try:
+        import ctypes
+        ms_p, sms = ctypes.c_float(0), ctypes.c_int(0)
+        iters = 1 << 16
+        _lib.check(_lib.lib().bi8_mma_peak_probe(iters, ctypes.byref(ms_p), ctypes.byref(sms)), "bi8_mma_peak_probe")
+        probe = sms.value * iters * 2.0 * 128 * 256 * 32 / (ms_p.value * 1e-3) / 1e12
+    except Exception as e:  # the probe is informational
+        probe = None
+        print(f"mma probe failed: {e}", file=sys.stderr)
+    peak = 2.0 * bf16_tf
+    roofline = {
+        "bound": "tensor", "kernel": "gemm_tc_kernel<64> (tcgen05 kind::i8)", "achieved": achieved, "peak": peak,
+        "unit": "TFLOP/s", "frac": achieved / peak,
+        "peak_source": f"2 x {peak_src} cuBLAS bf16 burst ({bf16_tf} TF/s); int8 multiply-add counted as 2 ops",
+        "frac_of_nominal_int8_4500": achieved / INT8_NOMINAL_TOPS,
+        "mma_issue_probe_tops": probe, "frac_of_mma_issue_probe": (achieved / probe) if probe else None,
+        "gemm_ms": gemm_ms, "algorithmic_ops_per_launch": ops_step,
+        "traffic": ncu_traffic(f"gemm_tc:{args.workload}"),
+    }
+    extra = None
+    if world == 1 and not args.no_extras:
+        extra = extras(dev, hbm_gbs, flush)
+        extra["hbm_peak_gbs"] = hbm_gbs
+        extra["hbm_peak_source"] = peak_src
+        extra["timing"] = "CUDA events, L2 flushed (256 MB fill) before every launch, median of 7"
+    cpu = None
+    if world == 1 and not args.no_cpu:
+        cpu, _ = cpu_baseline(args.workload)
+    line = {
+        "metric": "int8_block_gemm_tops", "value": value, "unit": "TOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8", "data": "synthetic",
+        "config": {"workload": args.workload, "M_per_gpu": M, "K": K, "N": N, "block": BLOCK, "in": "bf16", "out": "bf16",
+                   "step": "block-quantize x + int8 block GEMM with fused dequantize (weights pre-quantized)",
+                   "l2": f"{NSETS} rotating input/output sets of {(M * K * 2 + M * N * 2) >> 20} MiB each (larger than L2)",
+                   "parallelism": f"dp{world} over tokens, no collective"},
+        "roofline": roofline,
+        "e2e": {"value": e2e_value, "unit": "TOP/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": M * K * 2,
+                "d2h_bytes_per_step": M * N * 2, "api": "BlockInt8Linear.forward (eval) on pinned host buffers"},
+        "gpu_launches": world * args.steps * 2,
+        "clocks": clocks,
+    }
+    if cpu is not None:
+        line["cpu_baseline"] = cpu
+    if extra is not None:
+        line["extra"] = extra
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default=DEFAULT_WORKLOAD)
+    ap.add_argument("--no-extras", action="store_true", help="skip the quantize/dequantize/GEMM-shape sweep")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

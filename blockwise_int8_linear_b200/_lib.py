@@ -1,0 +1,92 @@
+"""ctypes binding of libbi8.so (declared in include/bi8.h).
+
+There is no fallback: if the library cannot be loaded, or a call returns an error status, an
+exception is raised.  Tensors are passed as raw device pointers plus sizes; the current torch
+CUDA stream is passed to every call.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libbi8.so")
+
+BI8_BF16, BI8_F32, BI8_F16 = 0, 1, 2
+GEMM_DEFAULT, GEMM_FORCE_GENERIC, GEMM_FORCE_TC, GEMM_NO_SEED = 0, 1, 2, 4
+
+_DTYPE_CODE = {torch.bfloat16: BI8_BF16, torch.float32: BI8_F32, torch.float16: BI8_F16}
+
+EXPORTS = [
+    "bi8_version", "bi8_last_error_string", "bi8_device_status", "bi8_quantize_rowwise", "bi8_quantize_colwise",
+    "bi8_dequantize_rowwise", "bi8_gemm_dequant", "bi8_gemm_workspace_bytes", "bi8_gemm_block_partials",
+    "bi8_linear_forward", "bi8_mma_peak_probe",
+]
+
+_lib = None
+
+
+class Bi8Error(RuntimeError):
+    """A libbi8 entry point returned a non-zero status."""
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m blockwise_int8_linear_b200.build` "
+                "(there is no non-CUDA fallback)")
+        L = ctypes.CDLL(LIB_PATH)
+        c = ctypes
+        vp, i64, i32, sz = c.c_void_p, c.c_int64, c.c_int, c.c_size_t
+        L.bi8_version.restype = i32
+        L.bi8_last_error_string.restype = c.c_char_p
+        L.bi8_device_status.argtypes = [c.POINTER(i32)]
+        L.bi8_quantize_rowwise.argtypes = [vp, i32, i64, vp, vp, i64, i64, i32, vp]
+        L.bi8_quantize_colwise.argtypes = [vp, i32, i64, vp, vp, i64, i64, i32, vp]
+        L.bi8_dequantize_rowwise.argtypes = [vp, vp, vp, i32, i64, i64, i32, vp]
+        L.bi8_gemm_dequant.argtypes = [vp, i64, vp, i64, vp, vp, vp, i32, vp, i64, i32, i64, i64, i64, i32, vp, sz, i32, vp]
+        L.bi8_gemm_workspace_bytes.argtypes = [i64, i64, i64, i32]
+        L.bi8_gemm_workspace_bytes.restype = sz
+        L.bi8_gemm_block_partials.argtypes = [vp, i64, vp, i64, vp, i64, i64, i64, i32, i32, vp]
+        L.bi8_linear_forward.argtypes = [vp, i32, i64, vp, vp, vp, i64, vp, vp, i32, vp, i64, i32, i64, i64, i64, i32, vp, sz,
+                                         i32, vp]
+        L.bi8_mma_peak_probe.argtypes = [i32, c.POINTER(c.c_float), c.POINTER(i32)]
+        for name in EXPORTS:
+            fn = getattr(L, name)
+            if name not in ("bi8_last_error_string", "bi8_gemm_workspace_bytes"):
+                fn.restype = i32
+        _lib = L
+    return _lib
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        msg = lib().bi8_last_error_string().decode(errors="replace")
+        raise Bi8Error(f"{what} failed with status {status}: {msg}")
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise ValueError(f"unsupported dtype {dtype}: expected bfloat16, float16 or float32") from None
+
+
+def ptr(t) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def stream_ptr() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def device_status() -> int:
+    """Synchronises and returns the device-side status word (0 = clean); raises on a recorded timeout."""
+    detail = ctypes.c_int(0)
+    rc = lib().bi8_device_status(ctypes.byref(detail))
+    check(rc, "bi8_device_status")
+    return rc

@@ -1,0 +1,183 @@
+"""The blockwise-int8 linear layer: autograd function, ``nn.Linear`` replacement and model patcher.
+
+Mirrors the reference's ``block_linear.py``: ``replace_linear_with_blockwise_int8`` (16-32),
+``fast_matmul`` (34-40), ``blockwise_int8_linear`` (69-112) and ``BlockInt8Linear`` (114-152).
+``BlockLinear`` and ``BlockLinearConfig`` are convenience aliases that the reference does not have.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from . import block_linear_config
+from .triton_functions import (
+    dequantize_block_rowwise,
+    int8_matmul_block64_rowwise_dequantize,
+    quantize_block_colwise,
+    quantize_block_rowwise,
+)
+
+__all__ = [
+    "replace_linear_with_blockwise_int8", "fast_matmul", "blockwise_int8_linear", "BlockInt8Linear", "BlockLinear",
+    "BlockLinearConfig",
+]
+
+
+def replace_linear_with_blockwise_int8(model: nn.Module) -> nn.Module:
+    """Swap every direct-child ``nn.Linear`` of ``model`` for a ``BlockInt8Linear`` sharing its weight and
+    bias storage (``block_linear.py:16-32``).  Not recursive: use ``model.apply(replace_linear_with_blockwise_int8)``
+    to patch a whole tree, as with the reference."""
+    names = [name for name, child in model.named_children() if type(child) is nn.Linear or
+             (isinstance(child, nn.Linear) and not isinstance(child, BlockInt8Linear))]
+    for name in names:
+        old = model._modules[name]
+        new = BlockInt8Linear(old.in_features, old.out_features, old.bias is not None, old.weight.device,
+                              old.weight.dtype, _skip_init=True)
+        new.weight.data = old.weight.data
+        if old.bias is not None:
+            new.bias.data = old.bias.data
+        new.train(old.training)
+        model._modules[name] = new
+    return model
+
+
+def fast_matmul(a, b):
+    """``a [M, K] @ b [K, N]`` with both operands quantized on the fly (``block_linear.py:34-40``, without its
+    debug prints)."""
+    b_int8, b_state = quantize_block_colwise(b)            # == quantize(b.t().contiguous())
+    a_int8, a_state = quantize_block_rowwise(a)
+    return int8_matmul_block64_rowwise_dequantize(a_int8, b_int8.t(), a_state, b_state)
+
+
+class blockwise_int8_linear(torch.autograd.Function):
+    """``y = x @ W^T + bias`` with every GEMM (forward, dX, dW) done in blockwise int8
+    (``block_linear.py:69-112``).  X and W are re-quantized on every call, as in the reference; the
+    transposed operands of the backward GEMMs are quantized straight from the row-major tensors by the
+    fused column-wise quantizer, which is bit-identical to ``t().contiguous()`` + row-wise quantize."""
+
+    @staticmethod
+    def forward(ctx, X_3D, W, bias):
+        X = X_3D.reshape(-1, X_3D.size(-1))
+        ctx.save_for_backward(X, W)
+        ctx.has_bias = bias is not None
+        X_int8, state_X = quantize_block_rowwise(X)
+        W_int8, state_W = quantize_block_rowwise(W)
+        out = int8_matmul_block64_rowwise_dequantize(X_int8, W_int8.t(), state_X, state_W, bias)
+        return out.view(*X_3D.size()[:-1], -1)
+
+    @staticmethod
+    def backward(ctx, G_3D):
+        G = G_3D.reshape(-1, G_3D.size(-1))
+        X, W = ctx.saved_tensors
+        grad_X = grad_W = grad_bias = None
+        if ctx.needs_input_grad[0]:
+            # contraction over N: both operands blocked along N (block_linear.py:92-95)
+            g_int8, g_state = quantize_block_rowwise(G)
+            Wt_int8, w_state = quantize_block_colwise(W)                     # [K, N], state [N/B, K]
+            grad_X = int8_matmul_block64_rowwise_dequantize(g_int8, Wt_int8.t(), g_state, w_state)
+            grad_X = grad_X.view(*G_3D.size()[:-1], -1)
+        if ctx.needs_input_grad[1]:
+            # contraction over the tokens: both operands blocked along M (block_linear.py:100-104)
+            x_int8, x_state = quantize_block_colwise(X)                      # [K, M], state [M/B, K]
+            gt_int8, gt_state = quantize_block_colwise(G)                    # [N, M], state [M/B, N]
+            grad_W = int8_matmul_block64_rowwise_dequantize(gt_int8, x_int8.t(), gt_state, x_state)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            grad_bias = G.sum(dim=0)
+        return grad_X, grad_W, grad_bias
+
+
+class BlockInt8Linear(nn.Linear):
+    """Drop-in ``nn.Linear`` (``block_linear.py:114-152``).
+
+    Training mode runs ``blockwise_int8_linear``.  Eval mode quantizes the weight once on the first forward
+    (buffers ``W_int8`` int8 ``[out, in]`` and ``state_W`` float32 ``[ceil(in/block), out]``, which become part of
+    ``state_dict()``), then quantizes the activation and runs the fused GEMM on every call."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, device=None, dtype=None,
+                 _skip_init: bool = False):
+        if _skip_init:
+            # the caller rebinds weight/bias storage right away: skip the random init of nn.Linear
+            nn.Module.__init__(self)
+            self.in_features, self.out_features = in_features, out_features
+            kw = {"device": device, "dtype": dtype}
+            self.weight = nn.Parameter(torch.empty((0,), **kw))
+            if bias:
+                self.bias = nn.Parameter(torch.empty((0,), **kw))
+            else:
+                self.register_parameter("bias", None)
+        else:
+            super().__init__(in_features, out_features, bias, device, dtype)
+
+    def prepare_for_eval(self):
+        W_int8, state_W = quantize_block_rowwise(self.weight.detach())
+        self.register_buffer("W_int8", W_int8)
+        self.register_buffer("state_W", state_W)
+
+    def dequantized_weight(self):
+        """The weight after a quantize/dequantize round trip, in ``INPUT_OUTPUT_TORCH_TYPE`` (the working part of
+        the reference's ``weight_quant_training``, ``block_linear.py:130-135``)."""
+        W_int8, state_W = quantize_block_rowwise(self.weight.detach())
+        return dequantize_block_rowwise(W_int8, state_W)
+
+    def infer(self, x):
+        if not hasattr(self, "W_int8"):
+            self.prepare_for_eval()
+        X = x.reshape(-1, x.size(-1))
+        X_int8, state_X = quantize_block_rowwise(X)
+        return int8_matmul_block64_rowwise_dequantize(
+            X_int8, self.W_int8.t(), state_X, self.state_W, self.bias
+        ).view(*x.size()[:-1], -1)
+
+    def forward(self, x):
+        if not self.training:
+            return self.infer(x)
+        return blockwise_int8_linear.apply(x, self.weight, self.bias)
+
+    def _load_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs):
+        # a checkpoint saved after the first eval forward carries W_int8/state_W: make room for them
+        for name in ("W_int8", "state_W"):
+            key = prefix + name
+            if key in state_dict and not hasattr(self, name):
+                self.register_buffer(name, torch.empty_like(state_dict[key], device=self.weight.device))
+        super()._load_from_state_dict(state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs)
+
+
+BlockLinear = BlockInt8Linear
+
+
+class BlockLinearConfig:
+    """Attribute-style view of the module-level knobs in ``block_linear_config`` (the reference has only the
+    globals, ``block_linear_config.py:3-5``).  Reading and assigning go straight to those globals; used as a
+    context manager it restores the previous values on exit."""
+
+    _FIELDS = {"group_size": "GROUP_SIZE", "scale_dtype": "SHARED_EXP_TORCH_TYPE", "io_dtype": "INPUT_OUTPUT_TORCH_TYPE"}
+
+    def __init__(self, group_size=None, io_dtype=None, scale_dtype=None):
+        object.__setattr__(self, "_pending", {k: v for k, v in
+                                              (("group_size", group_size), ("io_dtype", io_dtype), ("scale_dtype", scale_dtype))
+                                              if v is not None})
+        object.__setattr__(self, "_saved", None)
+
+    def __getattr__(self, name):
+        if name in self._FIELDS:
+            return getattr(block_linear_config, self._FIELDS[name])
+        raise AttributeError(name)
+
+    def __setattr__(self, name, value):
+        if name not in self._FIELDS:
+            raise AttributeError(name)
+        setattr(block_linear_config, self._FIELDS[name], value)
+
+    def apply(self):
+        for k, v in self._pending.items():
+            setattr(self, k, v)
+        return self
+
+    def __enter__(self):
+        object.__setattr__(self, "_saved", {k: getattr(self, k) for k in self._FIELDS})
+        return self.apply()
+
+    def __exit__(self, *exc):
+        for k, v in self._saved.items():
+            setattr(self, k, v)
+        return False

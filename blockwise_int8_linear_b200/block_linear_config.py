@@ -1,0 +1,13 @@
+"""Configuration knobs of the blockwise-int8 linear layer.
+
+Mirrors the reference's ``block_linear_config.py:3-5``: three module-level values that
+callers change by assignment (``block_linear_config.GROUP_SIZE = 64``).  All three are read
+at call time by every operation of this package, so one assignment takes effect everywhere
+(the reference froze the GEMM's block size at import, ``triton_functions.py:30,43-56``, which
+let the quantizer and the GEMM disagree after a later assignment).
+"""
+import torch
+
+GROUP_SIZE = 128                              # elements per quantisation block along the contraction axis
+SHARED_EXP_TORCH_TYPE = torch.float32         # dtype of the block scales; only float32 is supported
+INPUT_OUTPUT_TORCH_TYPE = torch.bfloat16      # dtype of GEMM / dequantize outputs: bfloat16, float16 or float32

@@ -1,0 +1,176 @@
+// extern "C" surface of libbi8.so: argument validation, dispatch, error text.  See include/bi8.h.
+#include "bi8_common.cuh"
+
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+
+namespace bi8 {
+
+namespace {
+thread_local char g_err[512] = "";
+
+// Per-device status word of the kernels' bounded waits: {code, detail}.
+__device__ int g_status[2];
+}  // namespace
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int* device_status_ptr() {
+    static int* ptrs[64] = {nullptr};
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        fail(BI8_ERR_CUDA, "cudaGetDevice failed");
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    if (!ptrs[dev]) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_status);
+        if (e != cudaSuccess) {
+            fail(BI8_ERR_CUDA, "cudaGetSymbolAddress(status): %s", cudaGetErrorString(e));
+            return nullptr;
+        }
+        ptrs[dev] = static_cast<int*>(p);
+    }
+    return ptrs[dev];
+}
+
+namespace {
+
+bool dtype_ok(int dt) { return dt == BI8_BF16 || dt == BI8_F32 || dt == BI8_F16; }
+int dtype_size(int dt) { return dt == BI8_F32 ? 4 : 2; }
+
+int check_gemm(const GemmArgs& g, bool partials) {
+    if (g.M < 0 || g.N < 0 || g.K < 0) return fail(BI8_ERR_SHAPE, "gemm: negative dimension (M=%lld N=%lld K=%lld)", (long long)g.M, (long long)g.N, (long long)g.K);
+    if (g.block < 1) return fail(BI8_ERR_BLOCK, "gemm: block size %d", g.block);
+    if (g.M == 0 || g.N == 0) return BI8_OK;
+    if (g.K > 0 && (!g.A || !g.Bt)) return fail(BI8_ERR_NULL, "gemm: null operand");
+    if (g.lda < g.K || g.ldb < g.K) return fail(BI8_ERR_SHAPE, "gemm: row pitch smaller than K");
+    if (partials) {
+        if (!g.partials && g.K > 0) return fail(BI8_ERR_NULL, "gemm_block_partials: null output");
+    } else {
+        if (!g.C) return fail(BI8_ERR_NULL, "gemm: null output");
+        if (g.K > 0 && (!g.sA || !g.sB)) return fail(BI8_ERR_NULL, "gemm: null scale tensor");
+        if (!dtype_ok(g.out_dtype)) return fail(BI8_ERR_DTYPE, "gemm: unknown output dtype code %d", g.out_dtype);
+        if (g.bias && !dtype_ok(g.bias_dtype)) return fail(BI8_ERR_DTYPE, "gemm: unknown bias dtype code %d", g.bias_dtype);
+        if (g.ldc < g.N) return fail(BI8_ERR_SHAPE, "gemm: ldc smaller than N");
+        if (!aligned(g.C, dtype_size(g.out_dtype))) return fail(BI8_ERR_ALIGN, "gemm: output not element aligned");
+    }
+    return BI8_OK;
+}
+
+int dispatch_gemm(const GemmArgs& g, cudaStream_t st) {
+    const char* why = "";
+    const bool tc_ok = g.K > 0 && gemm_tc_applicable(g, &why);
+    if (g.flags & BI8_GEMM_FORCE_TC) {
+        if (!tc_ok) return fail(BI8_ERR_ALIGN, "tensor-core GEMM not applicable: %s", why);
+        return launch_gemm_tc(g, st);
+    }
+    if ((g.flags & BI8_GEMM_FORCE_GENERIC) || !tc_ok || g.K == 0) return launch_gemm_generic(g, st);
+    return launch_gemm_tc(g, st);
+}
+
+}  // namespace
+}  // namespace bi8
+
+using namespace bi8;
+
+extern "C" {
+
+int bi8_version(void) { return BI8_VERSION; }
+
+const char* bi8_last_error_string(void) { return g_err; }
+
+int bi8_device_status(int* detail) {
+    int* p = device_status_ptr();
+    if (!p) return BI8_ERR_CUDA;
+    int host[2] = {0, 0};
+    BI8_CUDA_TRY(cudaDeviceSynchronize());
+    BI8_CUDA_TRY(cudaMemcpy(host, p, sizeof(host), cudaMemcpyDeviceToHost));
+    if (host[0] != 0) {
+        int zero[2] = {0, 0};
+        BI8_CUDA_TRY(cudaMemcpy(p, zero, sizeof(zero), cudaMemcpyHostToDevice));
+        if (detail) *detail = host[1];
+        return fail(host[0], "a device-side bounded wait gave up (wait code %d)", host[1]);
+    }
+    if (detail) *detail = 0;
+    return BI8_OK;
+}
+
+int bi8_quantize_rowwise(const void* x, int x_dtype, int64_t ldx, int8_t* q, float* s, int64_t M, int64_t K, int block,
+                         void* stream) {
+    if (!dtype_ok(x_dtype)) return fail(BI8_ERR_DTYPE, "quantize_rowwise: unknown dtype code %d", x_dtype);
+    if (block < 1) return fail(BI8_ERR_BLOCK, "quantize_rowwise: block size %d", block);
+    if (M < 0 || K < 0 || ldx < K) return fail(BI8_ERR_SHAPE, "quantize_rowwise: bad shape M=%lld K=%lld ldx=%lld", (long long)M, (long long)K, (long long)ldx);
+    if (M == 0 || K == 0) return BI8_OK;
+    if (!x || !q || !s) return fail(BI8_ERR_NULL, "quantize_rowwise: null pointer");
+    if (!aligned(x, dtype_size(x_dtype)) || !aligned(s, 4)) return fail(BI8_ERR_ALIGN, "quantize_rowwise: pointer not element aligned");
+    return launch_quantize_rowwise(x, x_dtype, ldx, q, s, M, K, block, static_cast<cudaStream_t>(stream));
+}
+
+int bi8_quantize_colwise(const void* x, int x_dtype, int64_t ldx, int8_t* q, float* s, int64_t R, int64_t C, int block,
+                         void* stream) {
+    if (!dtype_ok(x_dtype)) return fail(BI8_ERR_DTYPE, "quantize_colwise: unknown dtype code %d", x_dtype);
+    if (block < 1) return fail(BI8_ERR_BLOCK, "quantize_colwise: block size %d", block);
+    if (R < 0 || C < 0 || ldx < C) return fail(BI8_ERR_SHAPE, "quantize_colwise: bad shape R=%lld C=%lld ldx=%lld", (long long)R, (long long)C, (long long)ldx);
+    if (R == 0 || C == 0) return BI8_OK;
+    if (!x || !q || !s) return fail(BI8_ERR_NULL, "quantize_colwise: null pointer");
+    if (!aligned(x, dtype_size(x_dtype)) || !aligned(s, 4)) return fail(BI8_ERR_ALIGN, "quantize_colwise: pointer not element aligned");
+    return launch_quantize_colwise(x, x_dtype, ldx, q, s, R, C, block, static_cast<cudaStream_t>(stream));
+}
+
+int bi8_dequantize_rowwise(const int8_t* q, const float* s, void* out, int out_dtype, int64_t M, int64_t K, int block,
+                           void* stream) {
+    if (!dtype_ok(out_dtype)) return fail(BI8_ERR_DTYPE, "dequantize: unknown dtype code %d", out_dtype);
+    if (block < 1) return fail(BI8_ERR_BLOCK, "dequantize: block size %d", block);
+    if (M < 0 || K < 0) return fail(BI8_ERR_SHAPE, "dequantize: bad shape M=%lld K=%lld", (long long)M, (long long)K);
+    if (M == 0 || K == 0) return BI8_OK;
+    if (!q || !s || !out) return fail(BI8_ERR_NULL, "dequantize: null pointer");
+    if (!aligned(out, dtype_size(out_dtype)) || !aligned(s, 4)) return fail(BI8_ERR_ALIGN, "dequantize: pointer not element aligned");
+    return launch_dequantize_rowwise(q, s, out, out_dtype, M, K, block, static_cast<cudaStream_t>(stream));
+}
+
+size_t bi8_gemm_workspace_bytes(int64_t, int64_t, int64_t, int) { return 0; }
+
+int bi8_gemm_dequant(const int8_t* A, int64_t lda, const int8_t* Bt, int64_t ldb, const float* sA, const float* sB,
+                     const void* bias, int bias_dtype, void* C, int64_t ldc, int out_dtype, int64_t M, int64_t N, int64_t K,
+                     int block, void* workspace, size_t workspace_bytes, int flags, void* stream) {
+    (void)workspace;
+    (void)workspace_bytes;
+    GemmArgs g{A, lda, Bt, ldb, sA, sB, bias, bias_dtype, C, ldc, out_dtype, nullptr, M, N, K, block, flags};
+    int rc = check_gemm(g, false);
+    if (rc != BI8_OK || M == 0 || N == 0) return rc;
+    return dispatch_gemm(g, static_cast<cudaStream_t>(stream));
+}
+
+int bi8_gemm_block_partials(const int8_t* A, int64_t lda, const int8_t* Bt, int64_t ldb, int32_t* P, int64_t M, int64_t N,
+                            int64_t K, int block, int flags, void* stream) {
+    GemmArgs g{A, lda, Bt, ldb, nullptr, nullptr, nullptr, 0, nullptr, N, BI8_F32, P, M, N, K, block, flags};
+    int rc = check_gemm(g, true);
+    if (rc != BI8_OK || M == 0 || N == 0 || K == 0) return rc;
+    return dispatch_gemm(g, static_cast<cudaStream_t>(stream));
+}
+
+int bi8_linear_forward(const void* x, int x_dtype, int64_t ldx, int8_t* xq, float* sx, const int8_t* Wq, int64_t ldw,
+                       const float* sW, const void* bias, int bias_dtype, void* C, int64_t ldc, int out_dtype, int64_t M,
+                       int64_t N, int64_t K, int block, void* workspace, size_t workspace_bytes, int flags, void* stream) {
+    int rc = bi8_quantize_rowwise(x, x_dtype, ldx, xq, sx, M, K, block, stream);
+    if (rc != BI8_OK) return rc;
+    return bi8_gemm_dequant(xq, K, Wq, ldw, sx, sW, bias, bias_dtype, C, ldc, out_dtype, M, N, K, block, workspace,
+                            workspace_bytes, flags, stream);
+}
+
+int bi8_mma_peak_probe(int iters, float* ms, int* sm_count) {
+    if (!ms) return fail(BI8_ERR_NULL, "mma_peak_probe: null output");
+    return run_mma_peak_probe(iters, ms, sm_count);
+}
+
+}  // extern "C"

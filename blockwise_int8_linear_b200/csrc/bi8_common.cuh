@@ -1,0 +1,81 @@
+// Shared declarations of the bi8 library's translation units (not part of the public ABI).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/bi8.h"
+
+namespace bi8 {
+
+// Records the message returned by bi8_last_error_string() and returns `code`.
+int fail(int code, const char* fmt, ...);
+
+// Address of the per-device status word (two ints: code, detail), resolved once per device.
+int* device_status_ptr();
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+#define BI8_CUDA_TRY(expr)                                                                    \
+    do {                                                                                      \
+        cudaError_t e__ = (expr);                                                             \
+        if (e__ != cudaSuccess) return ::bi8::fail(BI8_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e__)); \
+    } while (0)
+
+// ---- launchers implemented in the other translation units -------------------------------------
+int launch_quantize_rowwise(const void* x, int dt, int64_t ldx, int8_t* q, float* s, int64_t M, int64_t K,
+                            int block, cudaStream_t st);
+int launch_quantize_colwise(const void* x, int dt, int64_t ldx, int8_t* q, float* s, int64_t R, int64_t C,
+                            int block, cudaStream_t st);
+int launch_dequantize_rowwise(const int8_t* q, const float* s, void* out, int dt, int64_t M, int64_t K,
+                              int block, cudaStream_t st);
+
+struct GemmArgs {
+    const int8_t* A;
+    int64_t lda;
+    const int8_t* Bt;
+    int64_t ldb;
+    const float* sA;
+    const float* sB;
+    const void* bias;
+    int bias_dtype;
+    void* C;
+    int64_t ldc;
+    int out_dtype;
+    int32_t* partials;  // non-null: write int32 block partial sums [nb, M, N] instead of C
+    int64_t M, N, K;
+    int block;
+    int flags;
+};
+bool gemm_tc_applicable(const GemmArgs& g, const char** why);
+int launch_gemm_tc(const GemmArgs& g, cudaStream_t st);
+int launch_gemm_generic(const GemmArgs& g, cudaStream_t st);
+int run_mma_peak_probe(int iters, float* ms, int* sm_count);
+
+// ---- small device helpers ----------------------------------------------------------------------
+__device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+// fp32 -> bf16 bits, round to nearest even (two values packed: lo in bits 0-15)
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+}  // namespace bi8

@@ -1,0 +1,658 @@
+// Int8 block GEMM with fused dequantize on the sm_100a tensor cores.
+//
+// Replaces the reference kernel at triton_functions.py:69-139 (path inside the reference project):
+//   P_j = A[:, jB:(j+1)B] . Bt[:, jB:(j+1)B]^T      exact int32 (line 115)
+//   acc += sB[j,n] * sA[j,m] * float(P_j) / 127^2   fp32, j ascending (line 120)
+//   C = cast(acc) (+ cast(bias))                    (lines 125-131)
+//
+// One persistent CTA per SM works on 128 x 256 output tiles.  Warp roles:
+//   warp 0      TMA producer: 128-byte-swizzled K-major tiles of A (128 rows) and Bt (256 rows), 128 K-bytes
+//               per stage, ring of kStages stages
+//   warp 1      issues tcgen05.mma kind::i8 (M128 N256 K32): the MMAs of one quantisation block accumulate
+//               into one of two 256-column s32 accumulators in tensor memory, then a commit hands that
+//               accumulator to the promotion warps
+//   warps 2-3   stage the block scales of the tile (sA: 128 rows, sB: 256 columns per block) in shared memory
+//   warps 4-11  promotion + epilogue: read an accumulator from tensor memory (each warp owns 32 rows x 128
+//               columns), fold it into fp32 accumulators held in registers, release the accumulator; after
+//               the last block convert, add bias and store
+// Registers are moved from warps 0-3 to warps 4-11 with setmaxnreg (128 fp32 accumulators per thread).
+//
+// Seeded conversion (default): the promotion warps refill a drained accumulator with the bit pattern of
+// 1.5*2^23 and every MMA accumulates on top of it.  Integer addition on that pattern is exact float
+// arithmetic while |P| < 2^22, so the word read back is the float 1.5*2^23 + P and
+//   t = fma(word, s, -1.5*2^23 * s) = fl(P * s)
+// needs no int->float conversion.  s = sA[j,m]/127^2 rounded to 22 significant bits makes 1.5*2^23*s exact.
+#include "bi8_common.cuh"
+#include "sm100_ptx.cuh"
+
+#include <cuda.h>
+
+#include <cstring>
+#include <mutex>
+
+namespace bi8 {
+namespace {
+
+using namespace ptx;
+
+constexpr int kBM = 128;                 // tile rows
+constexpr int kBN = 256;                 // tile columns
+constexpr int kBK = 128;                 // K bytes per stage (one 128-byte swizzle row)
+constexpr int kStages = 4;
+constexpr int kScaleStages = 4;
+constexpr int kThreadsTc = 384;
+constexpr int kEpiWarps = 8;
+constexpr uint32_t kABytes = kBM * kBK;  // 16 KiB
+constexpr uint32_t kBBytes = kBN * kBK;  // 32 KiB
+constexpr uint32_t kSeedBits = 0x4B400000u;   // float 1.5 * 2^23
+constexpr float kSeedF = 12582912.0f;
+
+// codes stored in the status word's detail when a bounded wait gives up
+enum WaitCode { W_EMPTY_AB = 1, W_FULL_AB = 2, W_ACC_EMPTY = 3, W_ACC_FULL = 4, W_SC_EMPTY = 5, W_SC_FULL = 6, W_PROBE = 7 };
+
+struct TcParams {
+    const float* sA;
+    const float* sB;
+    const void* bias;
+    void* C;
+    int32_t* partials;
+    int* status;
+    int64_t ldc;
+    int M, N, K, nb;
+    int tiles_m, tiles_n;
+    int out_dtype, bias_dtype;
+    int vec_store;      // C base and row pitch allow 16-byte stores
+    int vec_scales;     // sA, sB and their row lengths allow 16-byte loads
+};
+
+struct Smem {
+    // byte offsets from the 1024-aligned base of dynamic shared memory
+    __host__ __device__ static constexpr uint32_t a_off(int s) { return (uint32_t)s * (kABytes + kBBytes); }
+    __host__ __device__ static constexpr uint32_t b_off(int s) { return a_off(s) + kABytes; }
+    static constexpr uint32_t scale_off = kStages * (kABytes + kBBytes);
+};
+
+template <int QB>
+struct Geo {
+    static constexpr int BPS = kBK / QB;                        // quantisation blocks per stage
+    static constexpr int MMAS = QB / 32;                        // MMAs (K = 32) per block
+    static constexpr int SC_FLOATS = BPS * (kBM + kBN);         // scale floats per stage
+    static constexpr uint32_t bar_off = Smem::scale_off + kScaleStages * SC_FLOATS * 4;
+    // barrier slots (8 bytes each)
+    static constexpr int FULL_AB = 0, EMPTY_AB = kStages, ACC_FULL = 2 * kStages, ACC_EMPTY = 2 * kStages + 2,
+                         SC_FULL = 2 * kStages + 4, SC_EMPTY = 2 * kStages + 4 + kScaleStages,
+                         NBARS = 2 * kStages + 4 + 2 * kScaleStages;
+    static constexpr uint32_t misc_off = bar_off + NBARS * 8;   // tmem holder (4 B) + abort flag (4 B)
+    static constexpr uint32_t total = misc_off + 16;
+};
+
+__device__ __forceinline__ void report_timeout(int* status, volatile int* abort_flag, int code) {
+    *abort_flag = 1;
+    if (atomicCAS(status, 0, BI8_ERR_TIMEOUT) == 0) status[1] = code;
+}
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int& m0, int& n0) {
+    // consecutive tiles (CTAs that run together) share a column panel of Bt and sweep the rows of A
+    m0 = (tile % tiles_m) * kBM;
+    n0 = (tile / tiles_m) * kBN;
+}
+
+template <int QB, int MODE, bool SEED>
+__global__ void __launch_bounds__(kThreadsTc, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcParams p) {
+    using G = Geo<QB>;
+    extern __shared__ __align__(1024) unsigned char smem_dyn[];
+    // dynamic shared memory is only guaranteed 16-byte aligned: round up to the swizzle atom
+    const uint32_t raw = smem_u32(smem_dyn);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    unsigned char* base_ptr = smem_dyn + (base - raw);
+    float* sc_ring = reinterpret_cast<float*>(base_ptr + Smem::scale_off);
+    const uint32_t bars = base + G::bar_off;
+    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(base_ptr + G::misc_off);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + G::misc_off + 4);
+    auto bar = [&](int slot) -> uint32_t { return bars + 8u * (uint32_t)slot; };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int nks = (p.K + kBK - 1) / kBK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(bar(G::FULL_AB + s), 1);
+            mbar_init(bar(G::EMPTY_AB + s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar(G::ACC_FULL + b), 1);
+            mbar_init(bar(G::ACC_EMPTY + b), kEpiWarps);
+        }
+        for (int s = 0; s < kScaleStages; ++s) {
+            mbar_init(bar(G::SC_FULL + s), 2);
+            mbar_init(bar(G::SC_EMPTY + s), kEpiWarps);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == 2) {
+        tmem_alloc(smem_u32((const void*)tmem_holder), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    if (warp < 4) {
+        setmaxnreg_dec<88>();
+        if (warp == 0) {
+            // ---------------- TMA producer ----------------
+            if (lane == 0) {
+                int stage = 0;
+                uint32_t phase = 0;
+                int last_parity[kStages];
+#pragma unroll
+                for (int s = 0; s < kStages; ++s) last_parity[s] = -1;
+                bool ok = true;
+                for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                    int m0, n0;
+                    tile_coords(tile, p.tiles_m, m0, n0);
+                    for (int ks = 0; ks < nks; ++ks) {
+                        if (!mbar_wait(bar(G::EMPTY_AB + stage), phase ^ 1u, abort_flag)) {
+                            report_timeout(p.status, abort_flag, W_EMPTY_AB);
+                            ok = false;
+                            break;
+                        }
+                        mbar_expect_tx(bar(G::FULL_AB + stage), kABytes + kBBytes);
+                        tma_load_2d(base + Smem::a_off(stage), &tmA, bar(G::FULL_AB + stage), ks * kBK, m0);
+                        tma_load_2d(base + Smem::b_off(stage), &tmB, bar(G::FULL_AB + stage), ks * kBK, n0);
+#pragma unroll
+                        for (int s = 0; s < kStages; ++s)
+                            if (s == stage) last_parity[s] = (int)phase;
+                        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                    }
+                }
+                if (!ok) {
+                    // do not leave while our own copies may still land in this CTA's shared memory
+#pragma unroll
+                    for (int s = 0; s < kStages; ++s) {
+                        if (last_parity[s] >= 0) {
+                            int dummy = 0;
+                            (void)mbar_wait(bar(G::FULL_AB + s), (uint32_t)last_parity[s], &dummy, 100000000ull);
+                        }
+                    }
+                }
+            }
+        } else if (warp == 1) {
+            // ---------------- MMA issuer ----------------
+            if (lane == 0) {
+                constexpr uint32_t idesc = umma_idesc_i8(kBM, kBN);
+                int stage = 0, accbuf = 0;
+                uint32_t phase = 0, accphase = 0;
+                bool ok = true;
+                for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                    for (int ks = 0; ks < nks && ok; ++ks) {
+                        if (!mbar_wait(bar(G::FULL_AB + stage), phase, abort_flag)) {
+                            report_timeout(p.status, abort_flag, W_FULL_AB);
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        const uint64_t adesc = umma_desc_k_sw128(base + Smem::a_off(stage));
+                        const uint64_t bdesc = umma_desc_k_sw128(base + Smem::b_off(stage));
+#pragma unroll
+                        for (int blk = 0; blk < G::BPS; ++blk) {
+                            if (ks * G::BPS + blk >= p.nb) break;
+                            if (!mbar_wait(bar(G::ACC_EMPTY + accbuf), accphase, abort_flag)) {
+                                report_timeout(p.status, abort_flag, W_ACC_EMPTY);
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after();
+#pragma unroll
+                            for (int i = 0; i < G::MMAS; ++i) {
+                                const uint64_t koff = (uint64_t)((blk * G::MMAS + i) * 32 / 16);
+                                mma_i8(tmem_base + (uint32_t)accbuf * kBN, adesc + koff, bdesc + koff, idesc,
+                                       (SEED || i > 0) ? 1u : 0u);
+                            }
+                            tc_commit(bar(G::ACC_FULL + accbuf));
+                            accbuf ^= 1;
+                            if (accbuf == 0) accphase ^= 1u;
+                        }
+                        tc_commit(bar(G::EMPTY_AB + stage));
+                        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                    }
+                }
+            }
+        } else {
+            // ---------------- scale loaders: warp 2 stages sA (128 rows per block), warp 3 sB (256 columns) ----------
+            const bool is_a = (warp == 2);
+            const float* src = is_a ? p.sA : p.sB;
+            const int extent = is_a ? p.M : p.N;          // row length of the scale tensor
+            const int width = is_a ? kBM : kBN;           // floats per block taken by this warp
+            const int dst_off = is_a ? 0 : kBM;
+            int sstage = 0;
+            uint32_t sphase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                int m0, n0;
+                tile_coords(tile, p.tiles_m, m0, n0);
+                const int x0 = is_a ? m0 : n0;
+                for (int ks = 0; ks < nks; ++ks) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar(G::SC_EMPTY + sstage), sphase ^ 1u, abort_flag));
+                    if (!ok) {
+                        if (lane == 0) report_timeout(p.status, abort_flag, W_SC_EMPTY);
+                        break;
+                    }
+                    float* dst = sc_ring + sstage * G::SC_FLOATS + dst_off;
+                    if (p.vec_scales) {
+                        // all loads of the stage are issued before the first store
+                        constexpr int MAXV = G::BPS * kBN / 4 / 32;          // float4 per lane for sB
+                        const int nv = G::BPS * width / 4;                   // float4 in this warp's part
+                        float4 v[MAXV];
+#pragma unroll
+                        for (int i = 0; i < MAXV; ++i) {
+                            const int idx = lane + 32 * i;
+                            v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (idx < nv) {
+                                const int blk = idx / (width / 4), c4 = (idx % (width / 4)) * 4;
+                                const int j = ks * G::BPS + blk;
+                                if (src != nullptr && j < p.nb && x0 + c4 < extent)
+                                    v[i] = __ldg(reinterpret_cast<const float4*>(src + (int64_t)j * extent + x0 + c4));
+                            }
+                        }
+#pragma unroll
+                        for (int i = 0; i < MAXV; ++i) {
+                            const int idx = lane + 32 * i;
+                            if (idx < nv) {
+                                const int blk = idx / (width / 4), c4 = (idx % (width / 4)) * 4;
+                                *reinterpret_cast<float4*>(dst + blk * (kBM + kBN) + c4) = v[i];
+                            }
+                        }
+                    } else {
+                        for (int idx = lane; idx < G::BPS * width; idx += 32) {
+                            const int blk = idx / width, c = idx % width;
+                            const int j = ks * G::BPS + blk;
+                            float v = 0.0f;
+                            if (src != nullptr && j < p.nb && x0 + c < extent) v = __ldg(src + (int64_t)j * extent + x0 + c);
+                            dst[blk * (kBM + kBN) + c] = v;
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar(G::SC_FULL + sstage));
+                    if (++sstage == kScaleStages) { sstage = 0; sphase ^= 1u; }
+                }
+            }
+        }
+    } else {
+        // ---------------- promotion + epilogue (warps 4..11) ----------------
+        setmaxnreg_inc<208>();
+        const int quarter = warp & 3;            // tensor-memory lanes 32*quarter .. +31 belong to this warp
+        const int half = (warp - 4) >> 2;        // columns 128*half .. +127 of the tile
+        const int row = quarter * 32 + lane;
+        const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * 128);
+        const float div = 1.0f / (127.0f * 127.0f);
+
+        if (SEED) {
+#pragma unroll
+            for (int b = 0; b < 2; ++b)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tmem_fill32(t_lane + (uint32_t)(b * kBN + c * 32), kSeedBits);
+            tmem_wait_st();
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+            mbar_arrive(bar(G::ACC_EMPTY + 0));
+            mbar_arrive(bar(G::ACC_EMPTY + 1));
+        }
+
+        int accbuf = 0, sstage = 0;
+        uint32_t accphase = 0, sphase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            int m0, n0;
+            tile_coords(tile, p.tiles_m, m0, n0);
+            const int m = m0 + row;
+            const int nbase = n0 + half * 128;
+            float acc[128];
+#pragma unroll
+            for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
+
+            for (int ks = 0; ks < nks && ok; ++ks) {
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(G::SC_FULL + sstage), sphase, abort_flag));
+                if (!ok) {
+                    if (lane == 0) report_timeout(p.status, abort_flag, W_SC_FULL);
+                    break;
+                }
+                const float* sc = sc_ring + sstage * G::SC_FLOATS;
+#pragma unroll
+                for (int blk = 0; blk < G::BPS; ++blk) {
+                    const int j = ks * G::BPS + blk;
+                    if (j >= p.nb) break;
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar(G::ACC_FULL + accbuf), accphase, abort_flag));
+                    if (!ok) {
+                        if (lane == 0) report_timeout(p.status, abort_flag, W_ACC_FULL);
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t t_acc = t_lane + (uint32_t)(accbuf * kBN);
+                    float sxd = __fmul_rn(sc[blk * (kBM + kBN) + row], div);
+                    float negc = 0.0f;
+                    if (SEED) {
+                        sxd = __uint_as_float((__float_as_uint(sxd) + 2u) & 0xFFFFFFFCu);   // 22 significant bits
+                        negc = -__fmul_rn(kSeedF, sxd);                                      // exact
+                    }
+                    const float4* swv = reinterpret_cast<const float4*>(sc + blk * (kBM + kBN) + kBM + half * 128);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t pv[32];
+                        tmem_ld32(t_acc + (uint32_t)(c * 32), pv);
+                        tmem_wait_ld();
+                        if (MODE == 1) {
+                            if (m < p.M) {
+                                int32_t* dst = p.partials + ((int64_t)j * p.M + m) * p.N + nbase + c * 32;
+#pragma unroll
+                                for (int i = 0; i < 32; ++i)
+                                    if (nbase + c * 32 + i < p.N)
+                                        dst[i] = SEED ? (int32_t)(pv[i] - kSeedBits) : (int32_t)pv[i];
+                            }
+                        } else {
+#pragma unroll
+                            for (int i4 = 0; i4 < 8; ++i4) {
+                                const float4 w = swv[c * 8 + i4];
+                                const float ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                                for (int u = 0; u < 4; ++u) {
+                                    const int i = i4 * 4 + u;
+                                    float t;
+                                    if (SEED) t = __fmaf_rn(__uint_as_float(pv[i]), sxd, negc);
+                                    else t = __fmul_rn((float)(int32_t)pv[i], sxd);
+                                    acc[c * 32 + i] = __fmaf_rn(ws[u], t, acc[c * 32 + i]);
+                                }
+                            }
+                        }
+                    }
+                    if (SEED) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) tmem_fill32(t_acc + (uint32_t)(c * 32), kSeedBits);
+                        tmem_wait_st();
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar(G::ACC_EMPTY + accbuf));
+                    accbuf ^= 1;
+                    if (accbuf == 0) accphase ^= 1u;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(G::SC_EMPTY + sstage));
+                if (++sstage == kScaleStages) { sstage = 0; sphase ^= 1u; }
+            }
+            if (!ok) break;
+
+            if (MODE == 0 && m < p.M) {
+                const bool has_bias = p.bias != nullptr;
+                auto bias_at = [&](int n) -> float {
+                    if (p.bias_dtype == BI8_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n]);
+                    if (p.bias_dtype == BI8_F16) return __half2float(static_cast<const __half*>(p.bias)[n]);
+                    return static_cast<const float*>(p.bias)[n];
+                };
+                if (p.out_dtype == BI8_F32) {
+                    float* crow = static_cast<float*>(p.C) + (int64_t)m * p.ldc;
+#pragma unroll
+                    for (int g = 0; g < 32; ++g) {
+                        const int n = nbase + g * 4;
+                        float v[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            v[u] = acc[g * 4 + u];
+                            if (has_bias && n + u < p.N) v[u] = __fadd_rn(v[u], bias_at(n + u));
+                        }
+                        if (p.vec_store && n + 4 <= p.N) {
+                            *reinterpret_cast<float4*>(crow + n) = make_float4(v[0], v[1], v[2], v[3]);
+                        } else {
+#pragma unroll
+                            for (int u = 0; u < 4; ++u)
+                                if (n + u < p.N) crow[n + u] = v[u];
+                        }
+                    }
+                } else {
+                    const bool bf = p.out_dtype == BI8_BF16;
+                    uint16_t* crow = static_cast<uint16_t*>(p.C) + (int64_t)m * p.ldc;
+#pragma unroll
+                    for (int g = 0; g < 16; ++g) {
+                        const int n = nbase + g * 8;
+                        uint32_t w[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            float lo = acc[g * 8 + 2 * u], hi = acc[g * 8 + 2 * u + 1];
+                            uint32_t pk = bf ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
+                            if (has_bias) {
+                                // the reference adds the bias after the cast, in the output type (lines 127-131)
+                                float blo = (n + 2 * u < p.N) ? bias_at(n + 2 * u) : 0.0f;
+                                float bhi = (n + 2 * u + 1 < p.N) ? bias_at(n + 2 * u + 1) : 0.0f;
+                                if (bf) {
+                                    uint32_t bb = pack_bf16x2(blo, bhi);
+                                    pk = pack_bf16x2(__fadd_rn(bf16lo(pk), bf16lo(bb)), __fadd_rn(bf16hi(pk), bf16hi(bb)));
+                                } else {
+                                    __half2 a2 = *reinterpret_cast<__half2*>(&pk);
+                                    __half2 b2 = __floats2half2_rn(blo, bhi);
+                                    float2 af = __half22float2(a2), bfv = __half22float2(b2);
+                                    pk = pack_f16x2(__fadd_rn(af.x, bfv.x), __fadd_rn(af.y, bfv.y));
+                                }
+                            }
+                            w[u] = pk;
+                        }
+                        if (p.vec_store && n + 8 <= p.N) {
+                            *reinterpret_cast<uint4*>(crow + n) = make_uint4(w[0], w[1], w[2], w[3]);
+                        } else {
+#pragma unroll
+                            for (int u = 0; u < 8; ++u)
+                                if (n + u < p.N) crow[n + u] = (uint16_t)((w[u / 2] >> (16 * (u % 2))) & 0xffffu);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 2) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// Issue-rate probe: back-to-back M128 N256 K32 int8 MMAs on zeroed shared memory, no loads, no epilogue.
+__global__ void __launch_bounds__(128, 1) mma_peak_probe_kernel(int iters, int* status) {
+    extern __shared__ __align__(1024) unsigned char smem_dyn[];
+    const uint32_t raw = smem_u32(smem_dyn);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    unsigned char* base_ptr = smem_dyn + (base - raw);
+    __shared__ __align__(8) uint64_t done_bar;
+    __shared__ uint32_t holder;
+    __shared__ int abort_flag;
+    for (uint32_t i = threadIdx.x; i < (kABytes + kBBytes) / 16; i += blockDim.x)
+        reinterpret_cast<uint4*>(base_ptr)[i] = make_uint4(0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u);
+    const int warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&done_bar), 1);
+        abort_flag = 0;
+        mbar_fence_init();
+    }
+    fence_proxy_async_smem();
+    if (warp == 0) {
+        tmem_alloc(smem_u32(&holder), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *(volatile uint32_t*)&holder;
+    if (threadIdx.x == 32) {
+        constexpr uint32_t idesc = umma_idesc_i8(kBM, kBN);
+        const uint64_t adesc = umma_desc_k_sw128(base), bdesc = umma_desc_k_sw128(base + kABytes);
+        for (int i = 0; i < iters; ++i) {
+            const uint64_t koff = (uint64_t)((i & 3) * 2);
+            mma_i8(tmem_base + (uint32_t)((i >> 2) & 1) * kBN, adesc + koff, bdesc + koff, idesc, (i >= 8) ? 1u : 0u);
+        }
+        tc_commit(smem_u32(&done_bar));
+        if (!mbar_wait(smem_u32(&done_bar), 0u, &abort_flag, 5000000000ull)) report_timeout(status, &abort_flag, W_PROBE);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ---- host side --------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    });
+    return fn;
+}
+
+// int8 [rows, K] row-major with row pitch ld bytes -> boxes of 128 K-bytes x box_rows rows, 128-byte swizzle
+int make_operand_map(CUtensorMap* map, const int8_t* ptr, int64_t rows, int64_t K, int64_t ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(BI8_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t gstride[1] = {(cuuint64_t)ld};
+    cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(ptr), gdim, gstride, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(BI8_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return BI8_OK;
+}
+
+struct DeviceInfo {
+    int sms = 0;
+    bool ok = false;
+};
+DeviceInfo device_info() {
+    static DeviceInfo cache[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return DeviceInfo{};
+    if (!cache[dev].ok) {
+        int sms = 0, major = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return DeviceInfo{};
+        if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return DeviceInfo{};
+        cache[dev].sms = sms;
+        cache[dev].ok = (major == 10);
+    }
+    return cache[dev];
+}
+
+template <int QB, int MODE, bool SEED>
+int launch_one(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int grid, cudaStream_t st) {
+    constexpr size_t smem = Geo<QB>::total + 1024;
+    BI8_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<QB, MODE, SEED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    gemm_tc_kernel<QB, MODE, SEED><<<grid, kThreadsTc, smem, st>>>(ma, mb, p);
+    BI8_CUDA_TRY(cudaGetLastError());
+    return BI8_OK;
+}
+
+template <int QB>
+int launch_qb(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int grid, bool partials, bool seed,
+              cudaStream_t st) {
+    if (partials) return seed ? launch_one<QB, 1, true>(ma, mb, p, grid, st) : launch_one<QB, 1, false>(ma, mb, p, grid, st);
+    return seed ? launch_one<QB, 0, true>(ma, mb, p, grid, st) : launch_one<QB, 0, false>(ma, mb, p, grid, st);
+}
+
+}  // namespace
+
+bool gemm_tc_applicable(const GemmArgs& g, const char** why) {
+    auto no = [&](const char* w) {
+        if (why) *why = w;
+        return false;
+    };
+    if (g.block != 32 && g.block != 64 && g.block != 128) return no("block size is not 32, 64 or 128");
+    if (g.M >= (1ll << 31) - 256 || g.N >= (1ll << 31) - 256 || g.K >= (1ll << 31) - 256) return no("a dimension exceeds 2^31");
+    if (!aligned(g.A, 16) || !aligned(g.Bt, 16)) return no("operand base address is not 16-byte aligned");
+    if (g.lda % 16 != 0 || g.ldb % 16 != 0) return no("operand row pitch is not a multiple of 16 bytes");
+    if (!device_info().ok) return no("device is not compute capability 10.x");
+    return true;
+}
+
+int launch_gemm_tc(const GemmArgs& g, cudaStream_t st) {
+    const DeviceInfo di = device_info();
+    if (!di.ok) return fail(BI8_ERR_CUDA, "tensor-core GEMM needs a compute capability 10.x device");
+    CUtensorMap ma, mb;
+    int rc = make_operand_map(&ma, g.A, g.M, g.K, g.lda, kBM);
+    if (rc != BI8_OK) return rc;
+    rc = make_operand_map(&mb, g.Bt, g.N, g.K, g.ldb, kBN);
+    if (rc != BI8_OK) return rc;
+    TcParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.sA = g.sA;
+    p.sB = g.sB;
+    p.bias = g.bias;
+    p.C = g.C;
+    p.partials = g.partials;
+    p.status = device_status_ptr();
+    if (!p.status) return BI8_ERR_CUDA;
+    p.ldc = g.ldc;
+    p.M = (int)g.M;
+    p.N = (int)g.N;
+    p.K = (int)g.K;
+    p.nb = (int)((g.K + g.block - 1) / g.block);
+    p.tiles_m = (int)((g.M + kBM - 1) / kBM);
+    p.tiles_n = (int)((g.N + kBN - 1) / kBN);
+    p.out_dtype = g.out_dtype;
+    p.bias_dtype = g.bias_dtype;
+    const int esz = g.out_dtype == BI8_F32 ? 4 : 2;
+    p.vec_store = (g.C != nullptr && aligned(g.C, 16) && (g.ldc * esz) % 16 == 0) ? 1 : 0;
+    p.vec_scales = (g.partials == nullptr && aligned(g.sA, 16) && aligned(g.sB, 16) && g.M % 4 == 0 && g.N % 4 == 0) ? 1 : 0;
+    const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
+    if (tiles >= (1ll << 31)) return fail(BI8_ERR_SHAPE, "too many output tiles");
+    const int grid = (int)(tiles < di.sms ? tiles : di.sms);
+    const bool partials = g.partials != nullptr;
+    const bool seed = (g.flags & BI8_GEMM_NO_SEED) == 0;
+    switch (g.block) {
+        case 32: return launch_qb<32>(ma, mb, p, grid, partials, seed, st);
+        case 64: return launch_qb<64>(ma, mb, p, grid, partials, seed, st);
+        case 128: return launch_qb<128>(ma, mb, p, grid, partials, seed, st);
+    }
+    return fail(BI8_ERR_BLOCK, "tensor-core GEMM supports block 32, 64, 128 (got %d)", g.block);
+}
+
+int run_mma_peak_probe(int iters, float* ms, int* sm_count) {
+    const DeviceInfo di = device_info();
+    if (!di.ok) return fail(BI8_ERR_CUDA, "probe needs a compute capability 10.x device");
+    if (iters < 16 || iters > (1 << 22)) return fail(BI8_ERR_LIMIT, "iters must be in [16, 2^22]");
+    int* status = device_status_ptr();
+    if (!status) return BI8_ERR_CUDA;
+    const size_t smem = kABytes + kBBytes + 1024;
+    BI8_CUDA_TRY(cudaFuncSetAttribute(mma_peak_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    cudaEvent_t e0, e1;
+    BI8_CUDA_TRY(cudaEventCreate(&e0));
+    BI8_CUDA_TRY(cudaEventCreate(&e1));
+    mma_peak_probe_kernel<<<di.sms, 128, smem>>>(iters, status);   // warm-up
+    BI8_CUDA_TRY(cudaEventRecord(e0));
+    mma_peak_probe_kernel<<<di.sms, 128, smem>>>(iters, status);
+    BI8_CUDA_TRY(cudaEventRecord(e1));
+    BI8_CUDA_TRY(cudaEventSynchronize(e1));
+    BI8_CUDA_TRY(cudaEventElapsedTime(ms, e0, e1));
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (sm_count) *sm_count = di.sms;
+    return BI8_OK;
+}
+
+}  // namespace bi8

@@ -1,0 +1,493 @@
+// Block quantize / dequantize kernels (HBM-bound).
+//
+// Semantics follow the reference's kernels (paths inside the reference project):
+//   quantize    triton_functions.py:382-406   scale = max|x| over the block (fp32),
+//                                             q = rint(127 * (x / scale)), fp32 divide then fp32 multiply, RNE
+//   dequantize  triton_functions.py:467-490   out = (scale * q) * fl32(1/127)
+//   colwise     block_linear.py:93-94,100-103 transpose copy followed by the row-wise quantizer
+//
+// Data movement: every warp instruction of the vector kernels reads or writes one contiguous run of a
+// row (32-byte or 16-byte per lane), the block absmax is an xor-shuffle reduction inside the lanes that
+// share a block, and the transposed scale tensor [K/block, rows] is staged through shared memory so that
+// its stores (and, for dequantize, its loads) are contiguous along the row index.
+#include "bi8_common.cuh"
+
+#include <cstdlib>
+
+namespace bi8 {
+namespace {
+
+constexpr int kTileRows = 32;
+constexpr int kThreads = 256;
+constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23: adding it rounds to integer (RNE) in the low mantissa bits
+
+__device__ __forceinline__ void ld_nc_v8(const void* p, uint32_t (&r)[8]) {
+    asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "l"(p));
+}
+__device__ __forceinline__ void st_v8(void* p, const uint32_t (&r)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(r[0]), "r"(r[1]), "r"(r[2]),
+                 "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+
+// two packed 16-bit floats -> two fp32
+template <typename T>
+__device__ __forceinline__ void unpack2(uint32_t w, float& lo, float& hi);
+template <>
+__device__ __forceinline__ void unpack2<__nv_bfloat16>(uint32_t w, float& lo, float& hi) {
+    lo = bf16lo(w);
+    hi = bf16hi(w);
+}
+template <>
+__device__ __forceinline__ void unpack2<__half>(uint32_t w, float& lo, float& hi) {
+    float2 f = __half22float2(*reinterpret_cast<__half2*>(&w));
+    lo = f.x;
+    hi = f.y;
+}
+
+// Quantizer of one block: scale and the reciprocal used by the exact-division shortcut.
+//
+// For operands with at most 11 significant bits (bf16, fp16) the correctly rounded fp32 quotient a/b is
+//   q0 = a*r;  e = fma(-b, q0, a);  q1 = fma(e, r, q0)        with r = RN(1/b):
+// e is exact, q0 + e/b is the exact quotient, and the quotient of two such short operands is either
+// representable or at least 2^-13 ulp away from a rounding boundary, far more than the error of e*r.
+// For fp32 operands, and for scales outside [2^-100, 2^100], the IEEE division is used directly.
+struct BlockQ {
+    float scale;
+    float rcp;
+    bool fast;
+    __device__ __forceinline__ void set(float amax, bool short_mantissa) {
+        scale = amax;
+        fast = short_mantissa && amax > 7.8886090522101181e-31f && amax < 1.2676506002282294e30f;
+        rcp = fast ? __frcp_rn(amax) : 0.0f;
+    }
+    // returns fl32(127 * fl32(x / scale)) + magic, whose low byte is the int8 result
+    __device__ __forceinline__ uint32_t q(float x) const {
+        if (fast) {
+            float q0 = __fmul_rn(x, rcp);
+            float e = __fmaf_rn(-scale, q0, x);
+            float y = __fmaf_rn(e, rcp, q0);
+            return __float_as_uint(__fadd_rn(__fmul_rn(127.0f, y), kMagic));
+        }
+        if (scale == 0.0f) return 0u;                 // 0/0: the reference stores 0
+        float z = __fmul_rn(127.0f, __fdiv_rn(x, scale));
+        if (!(z == z)) return 0u;                     // NaN converts to 0 in the int8 store
+        return __float_as_uint(__fadd_rn(z, kMagic));
+    }
+};
+
+__device__ __forceinline__ uint32_t pack4(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    // low bytes of a,b,c,d -> one word (a in byte 0)
+    uint32_t ab = __byte_perm(a, b, 0x0040);
+    uint32_t cd = __byte_perm(c, d, 0x0040);
+    return __byte_perm(ab, cd, 0x5410);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Row-wise quantize, vector path.  T is a 16-bit float type.  VEC elements per lane (16: one 32-byte
+// load and one 16-byte store per lane; 8: 16-byte load, 8-byte store).  A CTA covers 32 rows x 32*VEC
+// columns; warp w handles rows w, w+8, w+16, w+24 and issues the four loads before any arithmetic.
+template <typename T, int B, int VEC>
+__global__ void __launch_bounds__(kThreads) quantize_rowwise_vec_kernel(
+    const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ q, float* __restrict__ s, int M, int K, int nb,
+    int col_tiles) {
+    constexpr int WCOLS = 32 * VEC;         // columns per warp pass
+    constexpr int LPB = B / VEC;            // lanes sharing one block
+    constexpr int BPT = WCOLS / B;          // blocks per tile row
+    constexpr int NW = VEC / 2;             // 32-bit words loaded per lane
+    static_assert(B % VEC == 0 && LPB >= 1 && LPB <= 32, "block must be a multiple of the lane vector");
+    __shared__ float s_scale[BPT][kTileRows];
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int ct = blockIdx.x % col_tiles, rt = blockIdx.x / col_tiles;
+    const int col = ct * WCOLS + lane * VEC;
+    const bool col_ok = col < K;            // K % VEC == 0 on this path: a lane is all in or all out
+
+    uint32_t raw[4][NW];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int row = rt * kTileRows + warp + 8 * i;
+        if (col_ok && row < M) {
+            const T* p = x + (int64_t)row * ldx + col;
+            if constexpr (VEC == 16) {
+                ld_nc_v8(p, raw[i]);
+            } else {
+                uint4 v = ld_nc_v4(p);
+                raw[i][0] = v.x; raw[i][1] = v.y; raw[i][2] = v.z; raw[i][3] = v.w;
+            }
+        } else {
+#pragma unroll
+            for (int w = 0; w < NW; ++w) raw[i][w] = 0u;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int row = rt * kTileRows + warp + 8 * i;
+        float v[VEC];
+        float amax = 0.0f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+            unpack2<T>(raw[i][w], v[2 * w], v[2 * w + 1]);
+            amax = fmaxf(amax, fmaxf(fabsf(v[2 * w]), fabsf(v[2 * w + 1])));
+        }
+#pragma unroll
+        for (int off = 1; off < LPB; off <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        BlockQ bq;
+        bq.set(amax, true);
+        uint32_t out[VEC / 4];
+#pragma unroll
+        for (int w = 0; w < VEC / 4; ++w)
+            out[w] = pack4(bq.q(v[4 * w]), bq.q(v[4 * w + 1]), bq.q(v[4 * w + 2]), bq.q(v[4 * w + 3]));
+        if (col_ok && row < M) {
+            int8_t* o = q + (int64_t)row * K + col;
+            if constexpr (VEC == 16) {
+                *reinterpret_cast<uint4*>(o) = make_uint4(out[0], out[1], out[2], out[3]);
+            } else {
+                *reinterpret_cast<uint2*>(o) = make_uint2(out[0], out[1]);
+            }
+        }
+        if ((lane % LPB) == 0) s_scale[lane / LPB][warp + 8 * i] = amax;
+    }
+    __syncthreads();
+    for (int t = threadIdx.x; t < BPT * kTileRows; t += kThreads) {
+        const int j = t / kTileRows, r = t % kTileRows;
+        const int jb = ct * BPT + j, row = rt * kTileRows + r;
+        if (jb < nb && row < M) s[(int64_t)jb * M + row] = s_scale[j][r];
+    }
+}
+
+// Row-wise quantize, any type / block / alignment: one warp per (row, block).
+template <typename T>
+__global__ void __launch_bounds__(kThreads) quantize_rowwise_generic_kernel(
+    const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ q, float* __restrict__ s, int64_t M, int64_t K, int B,
+    int64_t nb) {
+    const int lane = threadIdx.x & 31;
+    const int64_t task = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+    if (task >= M * nb) return;
+    const int64_t row = task / nb, j = task % nb;
+    const int64_t lo = j * B, hi = (lo + B < K) ? lo + B : K;
+    const T* xr = x + row * ldx;
+    float amax = 0.0f;
+    for (int64_t k = lo + lane; k < hi; k += 32) amax = fmaxf(amax, fabsf(to_f32<T>(xr[k])));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    BlockQ bq;
+    bq.set(amax, sizeof(T) == 2);
+    for (int64_t k = lo + lane; k < hi; k += 32) q[row * K + k] = (int8_t)(bq.q(to_f32<T>(xr[k])) & 0xffu);
+    if (lane == 0) s[j * M + row] = amax;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Column-wise quantize (fused transpose): x [R,C] -> q [C,R], s [ceil(R/B), C].  A CTA stages a tile of
+// NBLK*B rows x 128 columns in shared memory with 16-byte row-contiguous loads; then one thread owns one
+// (block, column): B values read down the column (bank-conflict free: lanes are consecutive columns),
+// absmax, quantize, and B bytes written as 16-byte pieces of output row c.
+template <typename T, int B>
+__global__ void __launch_bounds__(kThreads) quantize_colwise_vec_kernel(
+    const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ q, float* __restrict__ s, int R, int C, int col_tiles) {
+    constexpr int TC = 128;
+    constexpr int NBLK = kThreads / TC;     // blocks (along rows of x) per tile
+    constexpr int TR = NBLK * B;
+    constexpr int PITCH = TC + 2;           // 16-bit elements; +2 keeps column reads conflict free
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    uint16_t* tile = reinterpret_cast<uint16_t*>(smem_raw);
+
+    const int ct = blockIdx.x % col_tiles, rt = blockIdx.x / col_tiles;
+    const int c0 = ct * TC, r0 = rt * TR;
+    // load: each row of the tile is 16 lanes x 16 bytes
+    constexpr int VPR = TC / 8;
+    for (int v = threadIdx.x; v < TR * VPR; v += kThreads) {
+        const int r = v / VPR, cv = (v % VPR) * 8;
+        uint4 d = make_uint4(0u, 0u, 0u, 0u);
+        if (r0 + r < R && c0 + cv < C) d = ld_nc_v4(x + (int64_t)(r0 + r) * ldx + c0 + cv);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(tile + r * PITCH + cv);   // 4-byte aligned (PITCH even)
+        dst[0] = d.x; dst[1] = d.y; dst[2] = d.z; dst[3] = d.w;
+    }
+    __syncthreads();
+    const int c = threadIdx.x % TC, blk = threadIdx.x / TC;
+    const uint16_t* colp = tile + (blk * B) * PITCH + c;
+    float amax = 0.0f;
+#pragma unroll 16
+    for (int r = 0; r < B; ++r) {
+        T e = *reinterpret_cast<const T*>(colp + r * PITCH);
+        amax = fmaxf(amax, fabsf(to_f32<T>(e)));
+    }
+    BlockQ bq;
+    bq.set(amax, true);
+    const int rb = r0 + blk * B;            // first row of this block
+    const bool live = (c0 + c < C) && (rb < R);
+    if (live) {
+        int8_t* o = q + (int64_t)(c0 + c) * R + rb;
+        const bool full = (rb + B <= R) && ((R & 15) == 0);
+#pragma unroll
+        for (int g = 0; g < B / 16; ++g) {
+            uint32_t w[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint16_t* p = colp + (g * 16 + u * 4) * PITCH;
+                w[u] = pack4(bq.q(to_f32<T>(*reinterpret_cast<const T*>(p))),
+                             bq.q(to_f32<T>(*reinterpret_cast<const T*>(p + PITCH))),
+                             bq.q(to_f32<T>(*reinterpret_cast<const T*>(p + 2 * PITCH))),
+                             bq.q(to_f32<T>(*reinterpret_cast<const T*>(p + 3 * PITCH))));
+            }
+            if (full) {
+                *reinterpret_cast<uint4*>(o + g * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+            } else {
+#pragma unroll
+                for (int u = 0; u < 16; ++u)
+                    if (rb + g * 16 + u < R) o[g * 16 + u] = (int8_t)((w[u / 4] >> (8 * (u % 4))) & 0xffu);
+            }
+        }
+        s[(int64_t)(rb / B) * C + c0 + c] = amax;
+    }
+}
+
+// Column-wise quantize, any type / block / alignment: one thread per (block, column).
+template <typename T>
+__global__ void __launch_bounds__(kThreads) quantize_colwise_generic_kernel(
+    const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ q, float* __restrict__ s, int64_t R, int64_t C, int B,
+    int64_t nb) {
+    const int64_t task = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (task >= nb * C) return;
+    const int64_t j = task / C, c = task % C;
+    const int64_t lo = j * B, hi = (lo + B < R) ? lo + B : R;
+    float amax = 0.0f;
+    for (int64_t r = lo; r < hi; ++r) amax = fmaxf(amax, fabsf(to_f32<T>(x[r * ldx + c])));
+    BlockQ bq;
+    bq.set(amax, sizeof(T) == 2);
+    for (int64_t r = lo; r < hi; ++r) q[c * R + r] = (int8_t)(bq.q(to_f32<T>(x[r * ldx + c])) & 0xffu);
+    s[j * C + c] = amax;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Dequantize, vector path: a lane owns 16 consecutive int8 (one 16-byte load) and writes 16 outputs.
+// The CTA tile is 32 rows x 512 columns; its scales [512/B][32] are loaded row-contiguously first.
+template <typename TO>
+__device__ __forceinline__ void store16(TO* o, const float (&f)[16]);
+template <>
+__device__ __forceinline__ void store16<__nv_bfloat16>(__nv_bfloat16* o, const float (&f)[16]) {
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = pack_bf16x2(f[2 * i], f[2 * i + 1]);
+    st_v8(o, w);
+}
+template <>
+__device__ __forceinline__ void store16<__half>(__half* o, const float (&f)[16]) {
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = pack_f16x2(f[2 * i], f[2 * i + 1]);
+    st_v8(o, w);
+}
+template <>
+__device__ __forceinline__ void store16<float>(float* o, const float (&f)[16]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        *reinterpret_cast<float4*>(o + 4 * i) = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
+}
+
+template <typename TO, int B>
+__global__ void __launch_bounds__(kThreads) dequantize_rowwise_vec_kernel(
+    const int8_t* __restrict__ q, const float* __restrict__ s, TO* __restrict__ out, int M, int K, int nb,
+    int col_tiles) {
+    constexpr int WCOLS = 512;
+    constexpr int BPT = WCOLS / B;
+    constexpr int LPB = B / 16;
+    __shared__ float s_scale[BPT][kTileRows];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int ct = blockIdx.x % col_tiles, rt = blockIdx.x / col_tiles;
+    const int col = ct * WCOLS + lane * 16;
+    const bool col_ok = col < K;            // K % 16 == 0 on this path
+
+    uint4 raw[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int row = rt * kTileRows + warp + 8 * i;
+        raw[i] = (col_ok && row < M) ? ld_nc_v4(q + (int64_t)row * K + col) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    for (int t = threadIdx.x; t < BPT * kTileRows; t += kThreads) {
+        const int j = t / kTileRows, r = t % kTileRows;
+        const int jb = ct * BPT + j, row = rt * kTileRows + r;
+        s_scale[j][r] = (jb < nb && row < M) ? s[(int64_t)jb * M + row] : 0.0f;
+    }
+    __syncthreads();
+    const float inv127 = 1.0f / 127.0f;     // fl32(1/127), the constant the reference passes (line 499)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int row = rt * kTileRows + warp + 8 * i;
+        if (!(col_ok && row < M)) continue;
+        const float sc = s_scale[lane / LPB][warp + 8 * i];
+        const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+        float f[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            const int v = (int)(int8_t)((w[e / 4] >> (8 * (e % 4))) & 0xffu);
+            f[e] = __fmul_rn(__fmul_rn(sc, (float)v), inv127);
+        }
+        store16<TO>(out + (int64_t)row * K + col, f);
+    }
+}
+
+template <typename TO>
+__device__ __forceinline__ TO from_f32(float v);
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+
+template <typename TO>
+__global__ void __launch_bounds__(kThreads) dequantize_rowwise_generic_kernel(
+    const int8_t* __restrict__ q, const float* __restrict__ s, TO* __restrict__ out, int64_t M, int64_t K, int B) {
+    const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (i >= M * K) return;
+    const int64_t m = i / K, k = i % K;
+    const float inv127 = 1.0f / 127.0f;
+    out[i] = from_f32<TO>(__fmul_rn(__fmul_rn(s[(k / B) * M + m], (float)q[i]), inv127));
+}
+
+bool use_v8() {
+    static const bool on = (std::getenv("BI8_NO_V8") == nullptr);
+    return on;
+}
+
+template <typename T>
+int quantize_rowwise_t(const T* x, int64_t ldx, int8_t* q, float* s, int64_t M, int64_t K, int block, cudaStream_t st) {
+    const int64_t nb = (K + block - 1) / block;
+    const bool small = sizeof(T) == 2 && M < (1ll << 31) && K < (1ll << 31);
+    const bool v16 = small && use_v8() && K % 16 == 0 && ldx % 16 == 0 && aligned(x, 32) && aligned(q, 16);
+    const bool v8 = small && K % 8 == 0 && ldx % 8 == 0 && aligned(x, 16) && aligned(q, 8);
+    const int64_t row_tiles = (M + kTileRows - 1) / kTileRows;
+#define BI8_QROW(BB, VV)                                                                                   \
+    do {                                                                                                   \
+        const int64_t ctiles = (K + 32 * VV - 1) / (32 * VV);                                              \
+        if (row_tiles * ctiles >= (1ll << 31)) break;                                                      \
+        quantize_rowwise_vec_kernel<T, BB, VV><<<(unsigned)(row_tiles * ctiles), kThreads, 0, st>>>(        \
+            x, ldx, q, s, (int)M, (int)K, (int)nb, (int)ctiles);                                           \
+        BI8_CUDA_TRY(cudaGetLastError());                                                                  \
+        return BI8_OK;                                                                                     \
+    } while (0)
+    if constexpr (sizeof(T) == 2) {
+        if (v16) {
+            if (block == 32) BI8_QROW(32, 16);
+            if (block == 64) BI8_QROW(64, 16);
+            if (block == 128) BI8_QROW(128, 16);
+            if (block == 256) BI8_QROW(256, 16);
+        }
+        if (v8) {
+            if (block == 32) BI8_QROW(32, 8);
+            if (block == 64) BI8_QROW(64, 8);
+            if (block == 128) BI8_QROW(128, 8);
+            if (block == 256) BI8_QROW(256, 8);
+        }
+    }
+#undef BI8_QROW
+    const int64_t tasks = M * nb;
+    const int64_t grid = (tasks + kThreads / 32 - 1) / (kThreads / 32);
+    if (grid >= (1ll << 31)) return fail(BI8_ERR_SHAPE, "quantize_rowwise: %lld blocks exceed the grid limit", (long long)tasks);
+    quantize_rowwise_generic_kernel<T><<<(unsigned)grid, kThreads, 0, st>>>(x, ldx, q, s, M, K, block, nb);
+    BI8_CUDA_TRY(cudaGetLastError());
+    return BI8_OK;
+}
+
+template <typename T, int B>
+int colwise_vec(const T* x, int64_t ldx, int8_t* q, float* s, int64_t R, int64_t C, cudaStream_t st) {
+    constexpr int TC = 128, NBLK = kThreads / TC, TR = NBLK * B;
+    const int64_t ctiles = (C + TC - 1) / TC, rtiles = (R + TR - 1) / TR;
+    if (ctiles * rtiles >= (1ll << 31)) return fail(BI8_ERR_SHAPE, "quantize_colwise: grid too large");
+    const size_t smem = (size_t)TR * (TC + 2) * 2;
+    static bool attr_done = false;          // per instantiation; idempotent
+    if (!attr_done) {
+        BI8_CUDA_TRY(cudaFuncSetAttribute(quantize_colwise_vec_kernel<T, B>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_done = true;
+    }
+    quantize_colwise_vec_kernel<T, B><<<(unsigned)(ctiles * rtiles), kThreads, smem, st>>>(x, ldx, q, s, (int)R, (int)C, (int)ctiles);
+    BI8_CUDA_TRY(cudaGetLastError());
+    return BI8_OK;
+}
+
+template <typename T>
+int quantize_colwise_t(const T* x, int64_t ldx, int8_t* q, float* s, int64_t R, int64_t C, int block, cudaStream_t st) {
+    if constexpr (sizeof(T) == 2) {
+        const bool vec = R < (1ll << 31) && C < (1ll << 31) && C % 8 == 0 && ldx % 8 == 0 && aligned(x, 16) && aligned(q, 16);
+        if (vec) {
+            if (block == 32) return colwise_vec<T, 32>(x, ldx, q, s, R, C, st);
+            if (block == 64) return colwise_vec<T, 64>(x, ldx, q, s, R, C, st);
+            if (block == 128) return colwise_vec<T, 128>(x, ldx, q, s, R, C, st);
+        }
+    }
+    const int64_t nb = (R + block - 1) / block;
+    const int64_t grid = (nb * C + kThreads - 1) / kThreads;
+    if (grid >= (1ll << 31)) return fail(BI8_ERR_SHAPE, "quantize_colwise: grid too large");
+    quantize_colwise_generic_kernel<T><<<(unsigned)grid, kThreads, 0, st>>>(x, ldx, q, s, R, C, block, nb);
+    BI8_CUDA_TRY(cudaGetLastError());
+    return BI8_OK;
+}
+
+template <typename TO>
+int dequantize_t(const int8_t* q, const float* s, TO* out, int64_t M, int64_t K, int block, cudaStream_t st) {
+    const int64_t nb = (K + block - 1) / block;
+    const bool vec = use_v8() && M < (1ll << 31) && K < (1ll << 31) && K % 16 == 0 && aligned(q, 16) && aligned(out, 32);
+    const int64_t row_tiles = (M + kTileRows - 1) / kTileRows, ctiles = (K + 511) / 512;
+    if (vec && row_tiles * ctiles < (1ll << 31)) {
+#define BI8_DEQ(BB)                                                                                         \
+    if (block == BB) {                                                                                      \
+        dequantize_rowwise_vec_kernel<TO, BB><<<(unsigned)(row_tiles * ctiles), kThreads, 0, st>>>(           \
+            q, s, out, (int)M, (int)K, (int)nb, (int)ctiles);                                               \
+        BI8_CUDA_TRY(cudaGetLastError());                                                                   \
+        return BI8_OK;                                                                                      \
+    }
+        BI8_DEQ(32) BI8_DEQ(64) BI8_DEQ(128) BI8_DEQ(256)
+#undef BI8_DEQ
+    }
+    const int64_t grid = (M * K + kThreads - 1) / kThreads;
+    if (grid >= (1ll << 31)) return fail(BI8_ERR_SHAPE, "dequantize: grid too large");
+    dequantize_rowwise_generic_kernel<TO><<<(unsigned)grid, kThreads, 0, st>>>(q, s, out, M, K, block);
+    BI8_CUDA_TRY(cudaGetLastError());
+    return BI8_OK;
+}
+
+}  // namespace
+
+int launch_quantize_rowwise(const void* x, int dt, int64_t ldx, int8_t* q, float* s, int64_t M, int64_t K, int block,
+                            cudaStream_t st) {
+    switch (dt) {
+        case BI8_BF16: return quantize_rowwise_t(static_cast<const __nv_bfloat16*>(x), ldx, q, s, M, K, block, st);
+        case BI8_F16: return quantize_rowwise_t(static_cast<const __half*>(x), ldx, q, s, M, K, block, st);
+        case BI8_F32: return quantize_rowwise_t(static_cast<const float*>(x), ldx, q, s, M, K, block, st);
+    }
+    return fail(BI8_ERR_DTYPE, "quantize_rowwise: unknown dtype code %d", dt);
+}
+
+int launch_quantize_colwise(const void* x, int dt, int64_t ldx, int8_t* q, float* s, int64_t R, int64_t C, int block,
+                            cudaStream_t st) {
+    switch (dt) {
+        case BI8_BF16: return quantize_colwise_t(static_cast<const __nv_bfloat16*>(x), ldx, q, s, R, C, block, st);
+        case BI8_F16: return quantize_colwise_t(static_cast<const __half*>(x), ldx, q, s, R, C, block, st);
+        case BI8_F32: return quantize_colwise_t(static_cast<const float*>(x), ldx, q, s, R, C, block, st);
+    }
+    return fail(BI8_ERR_DTYPE, "quantize_colwise: unknown dtype code %d", dt);
+}
+
+int launch_dequantize_rowwise(const int8_t* q, const float* s, void* out, int dt, int64_t M, int64_t K, int block,
+                              cudaStream_t st) {
+    switch (dt) {
+        case BI8_BF16: return dequantize_t(q, s, static_cast<__nv_bfloat16*>(out), M, K, block, st);
+        case BI8_F16: return dequantize_t(q, s, static_cast<__half*>(out), M, K, block, st);
+        case BI8_F32: return dequantize_t(q, s, static_cast<float*>(out), M, K, block, st);
+    }
+    return fail(BI8_ERR_DTYPE, "dequantize: unknown dtype code %d", dt);
+}
+
+}  // namespace bi8

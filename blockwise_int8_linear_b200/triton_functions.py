@@ -1,0 +1,210 @@
+"""Functional operations of the blockwise-int8 linear layer.
+
+Same names, signatures, return values and layouts as the reference's ``triton_functions.py``
+(``quantize_block_rowwise`` 411-423, ``dequantize_block_rowwise`` 492-500,
+``int8_matmul_block64_rowwise_dequantize`` 142-168, ``fast_matmulT`` 511-514); the module keeps
+the reference's name although nothing here uses Triton: every function validates its arguments,
+allocates its outputs with torch and calls one entry point of ``libbi8.so`` on the current CUDA
+stream.  There is no CPU path and no fallback.
+
+Layouts: quantized tensors are int8 ``[rows, K]``; block scales ("state") are float32
+``[ceil(K/block), rows]``.  ``block`` is ``block_linear_config.GROUP_SIZE`` read at call time
+unless ``fblock_size`` is given.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from . import block_linear_config
+
+__all__ = [
+    "ceil_div", "quantize_block_rowwise", "quantize_block_colwise", "dequantize_block_rowwise",
+    "int8_matmul_block64_rowwise_dequantize", "int8_matmul_block_partials", "fast_matmulT",
+]
+
+
+def ceil_div(n, d):
+    return -(n // -d)
+
+
+def _block(fblock_size=None) -> int:
+    b = int(fblock_size or block_linear_config.GROUP_SIZE)
+    if b < 1:
+        raise ValueError(f"block size must be positive, got {b}")
+    return b
+
+
+def _scale_dtype():
+    if block_linear_config.SHARED_EXP_TORCH_TYPE != torch.float32:
+        raise ValueError("block scales are float32 only (block_linear_config.SHARED_EXP_TORCH_TYPE)")
+    return torch.float32
+
+
+def _rows_contiguous(t: torch.Tensor) -> torch.Tensor:
+    """2-D tensor whose last dimension is contiguous and whose row pitch covers a row."""
+    if t.shape[1] != 1 and t.stride(1) != 1:
+        return t.contiguous()
+    if t.shape[0] > 1 and t.stride(0) < t.shape[1]:
+        return t.contiguous()
+    return t
+
+
+def _pitch(t: torch.Tensor) -> int:
+    return t.stride(0) if t.shape[0] > 1 else max(t.shape[1], 1)
+
+
+class _on_device:
+    """Makes the tensor's device current for the duration of a library call (no-op when it already is)."""
+
+    def __init__(self, t: torch.Tensor):
+        self.idx = t.device.index
+        self.prev = None
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if self.idx is not None and self.idx != cur:
+            self.prev = cur
+            torch.cuda.set_device(self.idx)
+
+    def __exit__(self, *exc):
+        if self.prev is not None:
+            torch.cuda.set_device(self.prev)
+        return False
+
+
+def quantize_block_rowwise(x: torch.Tensor, fblock_size=None):
+    """Quantize each row of ``x [M, K]`` in blocks of ``block`` elements (``triton_functions.py:411-423``).
+
+    Returns ``(q, state)``: ``q`` int8 ``[M, K]``; ``state`` float32 ``[ceil(K/block), M]`` holding
+    ``max|x|`` of each block.  ``q = rint(127 * (x / state))`` (fp32 divide, fp32 multiply, round half to
+    even); an all-zero block gives state 0 and q 0."""
+    block = _block(fblock_size)
+    m, k = x.shape
+    assert x.is_cuda
+    x = _rows_contiguous(x)
+    code = _lib.dtype_code(x.dtype)
+    output = torch.empty((m, k), device=x.device, dtype=torch.int8)
+    output_maxs = torch.empty((ceil_div(k, block), m), device=x.device, dtype=_scale_dtype())
+    with _on_device(x):
+        rc = _lib.lib().bi8_quantize_rowwise(_lib.ptr(x), code, _pitch(x), _lib.ptr(output), _lib.ptr(output_maxs), m, k,
+                                             block, _lib.stream_ptr())
+    _lib.check(rc, "bi8_quantize_rowwise")
+    return output, output_maxs
+
+
+def quantize_block_colwise(x: torch.Tensor, fblock_size=None):
+    """``quantize_block_rowwise(x.t().contiguous())`` without materialising the transpose
+    (the pattern at ``block_linear.py:93-94`` and ``100-103``).  ``x`` is ``[R, C]``; returns int8 ``[C, R]``
+    and state ``[ceil(R/block), C]``, bit-identical to the two-step form."""
+    block = _block(fblock_size)
+    r, c = x.shape
+    assert x.is_cuda
+    x = _rows_contiguous(x)
+    code = _lib.dtype_code(x.dtype)
+    output = torch.empty((c, r), device=x.device, dtype=torch.int8)
+    output_maxs = torch.empty((ceil_div(r, block), c), device=x.device, dtype=_scale_dtype())
+    with _on_device(x):
+        rc = _lib.lib().bi8_quantize_colwise(_lib.ptr(x), code, _pitch(x), _lib.ptr(output), _lib.ptr(output_maxs), r, c,
+                                             block, _lib.stream_ptr())
+    _lib.check(rc, "bi8_quantize_colwise")
+    return output, output_maxs
+
+
+def dequantize_block_rowwise(x: torch.Tensor, state_x: torch.Tensor, fblock_size=None):
+    """``(state * q) * (1/127)`` cast to ``INPUT_OUTPUT_TORCH_TYPE`` (``triton_functions.py:492-500``)."""
+    block = _block(fblock_size)
+    m, k = x.shape
+    assert x.is_cuda
+    if x.dtype != torch.int8:
+        raise ValueError(f"expected an int8 tensor, got {x.dtype}")
+    if tuple(state_x.shape) != (ceil_div(k, block), m) or state_x.dtype != torch.float32:
+        raise ValueError(f"state must be float32 [{ceil_div(k, block)}, {m}] for block {block}, got "
+                         f"{state_x.dtype} {tuple(state_x.shape)}")
+    x = x.contiguous()
+    state_x = state_x.contiguous()
+    out_dtype = block_linear_config.INPUT_OUTPUT_TORCH_TYPE
+    output = torch.empty((m, k), device=x.device, dtype=out_dtype)
+    with _on_device(x):
+        rc = _lib.lib().bi8_dequantize_rowwise(_lib.ptr(x), _lib.ptr(state_x), _lib.ptr(output), _lib.dtype_code(out_dtype),
+                                               m, k, block, _lib.stream_ptr())
+    _lib.check(rc, "bi8_dequantize_rowwise")
+    return output
+
+
+def _gemm_operands(a: torch.Tensor, b: torch.Tensor):
+    # same fix-ups as the reference (triton_functions.py:149-152), then bring both operands to the
+    # K-contiguous form the library takes: a [M, K] row pitch lda, bt = b^T [N, K] row pitch ldb
+    if a.stride(0) > 1 and a.stride(1) > 1:
+        a = a.contiguous()
+    if b.stride(0) > 1 and b.stride(1) > 1:
+        b = b.contiguous()
+    assert a.shape[1] == b.shape[0], "incompatible dimensions"
+    if a.dtype != torch.int8 or b.dtype != torch.int8:
+        raise ValueError(f"operands must be int8, got {a.dtype} and {b.dtype}")
+    a = _rows_contiguous(a)
+    bt = _rows_contiguous(b.t())
+    return a, bt
+
+
+def int8_matmul_block64_rowwise_dequantize(a, b, state_x, state_w, bias=None, *, flags: int = 0):
+    """Block GEMM with fused dequantize (``triton_functions.py:142-168``).
+
+    ``a`` int8 ``[M, K]``; ``b`` int8 ``[K, N]`` (on the layer's path the ``.t()`` view of a row-major
+    ``[N, K]`` tensor); ``state_x [ceil(K/block), M]``, ``state_w [ceil(K/block), N]`` float32; optional
+    ``bias [N]``.  Returns a new ``[M, N]`` tensor of ``INPUT_OUTPUT_TORCH_TYPE``:
+    ``sum_j state_w[j,n] * state_x[j,m] * (a_j . b_j) / 127**2`` accumulated in fp32, cast, then
+    ``+ bias`` in the output type.  ``flags`` selects a kernel variant (see ``include/bi8.h``)."""
+    block = _block()
+    assert a.is_cuda
+    a, bt = _gemm_operands(a, b)
+    m, k = a.shape
+    n = bt.shape[0]
+    nb = ceil_div(k, block)
+    for name, st, rows in (("state_x", state_x, m), ("state_w", state_w, n)):
+        if tuple(st.shape) != (nb, rows) or st.dtype != torch.float32:
+            raise ValueError(f"{name} must be float32 [{nb}, {rows}] for block {block}, got {st.dtype} {tuple(st.shape)}")
+    state_x = state_x.contiguous()
+    state_w = state_w.contiguous()
+    out_dtype = block_linear_config.INPUT_OUTPUT_TORCH_TYPE
+    c = torch.empty((m, n), device=a.device, dtype=out_dtype)
+    bias_code = 0
+    if bias is not None:
+        if bias.numel() != n:
+            raise ValueError(f"bias must have {n} elements, got {bias.numel()}")
+        bias = bias.reshape(n).contiguous()
+        if bias.dtype not in (torch.bfloat16, torch.float16, torch.float32):
+            bias = bias.float()
+        bias_code = _lib.dtype_code(bias.dtype)
+    L = _lib.lib()
+    with _on_device(a):
+        ws_bytes = L.bi8_gemm_workspace_bytes(m, n, k, block)
+        ws = torch.empty(ws_bytes, device=a.device, dtype=torch.uint8) if ws_bytes else None
+        rc = L.bi8_gemm_dequant(_lib.ptr(a), _pitch(a), _lib.ptr(bt), _pitch(bt), _lib.ptr(state_x), _lib.ptr(state_w),
+                                _lib.ptr(bias), bias_code, _lib.ptr(c), n, _lib.dtype_code(out_dtype), m, n, k, block,
+                                _lib.ptr(ws), ws_bytes, flags, _lib.stream_ptr())
+    _lib.check(rc, "bi8_gemm_dequant")
+    return c
+
+
+def int8_matmul_block_partials(a, b, fblock_size=None, *, flags: int = 0):
+    """Exact int32 block partial sums ``P[j] = a[:, jB:(j+1)B] @ b[jB:(j+1)B, :]`` as ``[ceil(K/B), M, N]``,
+    produced by the same loads and tensor-core instructions as the GEMM (``triton_functions.py:115``)."""
+    block = _block(fblock_size)
+    assert a.is_cuda
+    a, bt = _gemm_operands(a, b)
+    m, k = a.shape
+    n = bt.shape[0]
+    out = torch.zeros((ceil_div(k, block), m, n), device=a.device, dtype=torch.int32)
+    with _on_device(a):
+        rc = _lib.lib().bi8_gemm_block_partials(_lib.ptr(a), _pitch(a), _lib.ptr(bt), _pitch(bt), _lib.ptr(out), m, n, k,
+                                                block, flags, _lib.stream_ptr())
+    _lib.check(rc, "bi8_gemm_block_partials")
+    return out
+
+
+def fast_matmulT(a, b):
+    """``a [M, K] @ b[N, K]^T`` with both operands quantized on the fly (``triton_functions.py:511-514``)."""
+    a_int8, a_state = quantize_block_rowwise(a)
+    b_int8, b_state = quantize_block_rowwise(b)
+    return int8_matmul_block64_rowwise_dequantize(a_int8, b_int8.t(), a_state, b_state)

@@ -1,0 +1,126 @@
+/* bi8 — blockwise-int8 linear hot path for NVIDIA B200 (sm_100a), C ABI.
+ *
+ * One shared library, libbi8.so, replaces the three device kernels of the reference project and
+ * their Python launch wrappers.  Every entry point takes plain device pointers, sizes and a
+ * cudaStream_t (passed as void*), enqueues its work on that stream and returns an int status
+ * without synchronising.  Unless a function's comment says otherwise the library owns no device
+ * memory: inputs, outputs and workspaces are allocated by the caller.
+ *
+ * Layout contract (the reference's):
+ *   quantized values  int8  [rows, K]          row-major, K contiguous
+ *   block scales      fp32  [ceil(K/block), rows]   ("state" tensors; transposed on purpose)
+ *   a block is `block` consecutive elements of one row; the K tail counts as zeros.
+ *
+ * Reference interfaces replaced (paths inside the reference project):
+ *   triton_functions.py:411-423  quantize_block_rowwise            -> bi8_quantize_rowwise
+ *   triton_functions.py:492-500  dequantize_block_rowwise          -> bi8_dequantize_rowwise
+ *   triton_functions.py:142-168  int8_matmul_block64_rowwise_dequantize -> bi8_gemm_dequant
+ *   block_linear.py:93-94,100-103  X.t().contiguous() + quantize   -> bi8_quantize_colwise
+ */
+#ifndef BI8_H_
+#define BI8_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define BI8_API __attribute__((visibility("default")))
+#else
+#define BI8_API
+#endif
+
+#define BI8_VERSION 100
+
+/* status codes (0 = ok, negative = error; text via bi8_last_error_string) */
+#define BI8_OK 0
+#define BI8_ERR_DTYPE (-1)      /* unsupported element type code */
+#define BI8_ERR_BLOCK (-2)      /* block size < 1 */
+#define BI8_ERR_ALIGN (-3)      /* pointer / stride alignment the entry point cannot handle */
+#define BI8_ERR_SHAPE (-4)      /* negative or inconsistent sizes */
+#define BI8_ERR_CUDA (-5)       /* a CUDA runtime / driver call failed */
+#define BI8_ERR_TIMEOUT (-6)    /* a device-side bounded wait gave up (read by bi8_device_status) */
+#define BI8_ERR_WORKSPACE (-7)  /* workspace missing or too small */
+#define BI8_ERR_NULL (-8)       /* required pointer is null */
+#define BI8_ERR_LIMIT (-9)      /* size beyond a documented fixed limit */
+
+/* element type codes for floating-point tensors */
+#define BI8_BF16 0
+#define BI8_F32 1
+#define BI8_F16 2
+
+/* flags for bi8_gemm_dequant */
+#define BI8_GEMM_DEFAULT 0
+#define BI8_GEMM_FORCE_GENERIC 1   /* CUDA-core kernel even where the tensor-core kernel applies */
+#define BI8_GEMM_FORCE_TC 2        /* fail with BI8_ERR_ALIGN instead of falling back */
+#define BI8_GEMM_NO_SEED 4         /* tensor-core kernel: convert partial sums with cvt instead of seeded TMEM */
+
+BI8_API int bi8_version(void);
+
+/* Text of the last error raised on the calling thread ("" if none). */
+BI8_API const char* bi8_last_error_string(void);
+
+/* Reads and clears the device-side status word of the current device (synchronises the device).
+ * 0 = no kernel reported a problem; otherwise BI8_ERR_TIMEOUT (a bounded mbarrier wait gave up;
+ * *detail receives the kernel-specific code of the first wait that gave up). */
+BI8_API int bi8_device_status(int* detail);
+
+/* Replaces quantize_block_rowwise (triton_functions.py:411-423, kernel 382-406).
+ * x [M,K] of x_dtype, row stride ldx elements, K contiguous.  Writes q [M,K] int8 (contiguous) and
+ * s [ceil(K/block), M] fp32.  scale = max|x| over the block (fp32); q = rint(127*(x/scale)) with an
+ * IEEE fp32 divide, a separate fp32 multiply and round-half-even; an all-zero block gives scale 0, q 0. */
+BI8_API int bi8_quantize_rowwise(const void* x, int x_dtype, int64_t ldx, int8_t* q, float* s,
+                         int64_t M, int64_t K, int block, void* stream);
+
+/* Replaces "t = x.t().contiguous(); quantize_block_rowwise(t)" (block_linear.py:93-94, 100-103) in one
+ * pass.  x [R,C] of x_dtype, row stride ldx.  Writes q [C,R] int8 (the transpose, contiguous) and
+ * s [ceil(R/block), C]: blocks run down the columns of x.  Bit-identical to the two-step form. */
+BI8_API int bi8_quantize_colwise(const void* x, int x_dtype, int64_t ldx, int8_t* q, float* s,
+                         int64_t R, int64_t C, int block, void* stream);
+
+/* Replaces dequantize_block_rowwise (triton_functions.py:492-500, kernel 467-490).
+ * out[m,k] = cast((s[k/block, m] * float(q[m,k])) * fl32(1/127)), out [M,K] contiguous of out_dtype. */
+BI8_API int bi8_dequantize_rowwise(const int8_t* q, const float* s, void* out, int out_dtype,
+                           int64_t M, int64_t K, int block, void* stream);
+
+/* Replaces int8_matmul_block64_rowwise_dequantize (triton_functions.py:142-168, kernel 69-139).
+ *   C[m,n] = cast( sum_j  sB[j,n] * sA[j,m] * float(P_j[m,n]) / 127^2 )  (+ cast(bias[n]) in the output type)
+ *   P_j = A[:, j*block:(j+1)*block] . Bt[:, j*block:(j+1)*block]^T   exactly, in int32.
+ * A  [M,K] int8, row stride lda.  Bt [N,K] int8, row stride ldb — the reference's `b` operand is the
+ * transposed view Bt^T with strides (1, ldb).  sA [ceil(K/block), M], sB [ceil(K/block), N] fp32.
+ * bias [N] of bias_dtype or NULL.  C [M,N] of out_dtype, row stride ldc.
+ * workspace: bi8_gemm_workspace_bytes(M,N,K,block) bytes of device memory (may be NULL when that is 0).
+ * The int32 partial sums are exact; the fp32 accumulation multiplies the three factors in a different
+ * order than the reference (a few fp32 ulps per term). */
+BI8_API int bi8_gemm_dequant(const int8_t* A, int64_t lda, const int8_t* Bt, int64_t ldb,
+                     const float* sA, const float* sB, const void* bias, int bias_dtype,
+                     void* C, int64_t ldc, int out_dtype, int64_t M, int64_t N, int64_t K, int block,
+                     void* workspace, size_t workspace_bytes, int flags, void* stream);
+
+BI8_API size_t bi8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int block);
+
+/* Diagnostic twin of bi8_gemm_dequant (same loads and tensor-core instructions): writes the exact
+ * int32 partial sums P [ceil(K/block), M, N] instead of the scaled result (triton_functions.py:115). */
+BI8_API int bi8_gemm_block_partials(const int8_t* A, int64_t lda, const int8_t* Bt, int64_t ldb, int32_t* P,
+                            int64_t M, int64_t N, int64_t K, int block, int flags, void* stream);
+
+/* Forward of the layer in one call (block_linear.py:78-80 / 141-143): quantizes x [M,K] (x_dtype, row
+ * stride ldx) into the caller's scratch (xq [M,K] int8, sx [ceil(K/block),M] fp32) and runs the GEMM
+ * against pre-quantized weights.  Same results as bi8_quantize_rowwise + bi8_gemm_dequant. */
+BI8_API int bi8_linear_forward(const void* x, int x_dtype, int64_t ldx, int8_t* xq, float* sx,
+                       const int8_t* Wq, int64_t ldw, const float* sW, const void* bias, int bias_dtype,
+                       void* C, int64_t ldc, int out_dtype, int64_t M, int64_t N, int64_t K, int block,
+                       void* workspace, size_t workspace_bytes, int flags, void* stream);
+
+/* Back-to-back tcgen05.mma kind::i8 issue rate of the current device: runs `iters` 128x256x32 MMAs per SM
+ * with no loads or epilogue and returns the elapsed milliseconds in *ms (synchronises).  Used by the
+ * benchmark to state the measured dense INT8 peak next to the nominal one. */
+BI8_API int bi8_mma_peak_probe(int iters, float* ms, int* sm_count);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BI8_H_ */

@@ -1,0 +1,219 @@
+"""Int8 block GEMM with fused dequantize on the GPU against the CPU oracle.
+
+Stated tolerances:
+* int32 block partial sums: exact.
+* CUDA-core (generic) kernel, fp32 output: bit-exact against the oracle (same operation order as the reference).
+* tensor-core kernel, fp32 output: |c - oracle| <= 8 * 2^-24 * sum_j |term_j| + 1e-30 per element (the kernel multiplies the
+  three factors of a term in a different order, and in seeded mode rounds sA/127^2 to 22 bits: at most ~3 fp32
+  roundings per term instead of the reference's 3 in another order).
+* tensor-core kernel, bf16 output: at most 1 bf16 step away from the oracle's bf16 result, >= 99 % identical.
+"""
+import pytest
+import torch
+
+from oracle import blockwise_int8_oracle as O
+from tests.gpu_util import DEV, assert_clean_device, bf16_ulp_distance, quantized_pair, set_config
+from tests.helpers import golden_names, load_golden
+
+pytestmark = pytest.mark.gpu
+
+GENERIC, TC, NO_SEED = 1, 2, 4
+FP32_TOL = 8 * 2.0 ** -24
+
+
+def _gemm(xq, wq, xs, ws, bias=None, flags=0):
+    from triton_functions import int8_matmul_block64_rowwise_dequantize as mm
+    return mm(xq.to(DEV), wq.to(DEV).t(), xs.to(DEV), ws.to(DEV), None if bias is None else bias.to(DEV), flags=flags)
+
+
+def _check_fp32(c, xq, wq, xs, ws, block, bias=None):
+    acc = O.gemm_acc(xq, wq.t(), xs, ws, block)
+    mag = O.gemm_term_abs_sum(xq, wq.t(), xs, ws, block)
+    if bias is not None:
+        acc = acc + bias.float()
+        mag = mag + bias.float().abs()
+    err = (c.cpu() - acc).abs()
+    bad = err > (FP32_TOL * mag + 1e-30)
+    assert not bad.any(), f"{bad.sum().item()} elements beyond tolerance, worst ratio {(err / (mag + 1e-30)).max().item() / 2.0 ** -24:.2f} x 2^-24"
+
+
+def _check_bf16(c, xq, wq, xs, ws, block, bias=None):
+    ref = O.gemm(xq, wq.t(), xs, ws, bias, block, torch.bfloat16)
+    d = bf16_ulp_distance(c.cpu(), ref)
+    assert d.max().item() <= 1, f"max distance {d.max().item()} bf16 steps"
+    same = (d == 0).float().mean().item()
+    assert same >= 0.99, f"only {same:.4f} identical"
+
+
+SHAPES = [
+    # (M, K, N, block)
+    (128, 128, 256, 64),      # one tile, one stage
+    (128, 512, 256, 64),      # one tile, ring wraps
+    (256, 1024, 512, 64),     # several tiles
+    (300, 640, 600, 64),      # M, N tails, persistent loop
+    (1, 4096, 512, 64),       # single row
+    (16, 1024, 1024, 64),
+    (130, 192, 264, 64),      # K = 1.5 stages: second stage half out of range
+    (64, 4096, 300, 64),
+    (200, 256, 136, 32),
+    (200, 416, 136, 32),      # K tail inside a stage, block 32
+    (72, 1024, 520, 128),
+    (72, 400, 520, 128),      # last block partial (K % 128 = 16)
+    (129, 272, 75, 64),       # odd N: scalar scale loads and stores
+]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("flags", [TC, GENERIC])
+def test_block_partials_exact(shape, flags):
+    from triton_functions import int8_matmul_block_partials
+    m, k, n, block = shape
+    xq, xs, wq, ws = quantized_pair(m, k, n, block, seed=m + k + n)
+    p = int8_matmul_block_partials(xq.to(DEV), wq.to(DEV).t(), block, flags=flags)
+    ref = O.gemm_block_partials(xq, wq.t(), block)
+    assert torch.equal(p.cpu(), ref)
+    if flags == TC:
+        p2 = int8_matmul_block_partials(xq.to(DEV), wq.to(DEV).t(), block, flags=TC | NO_SEED)
+        assert torch.equal(p2.cpu(), ref)
+    assert_clean_device()
+
+
+def test_partials_extreme_values():
+    """All operands at +-127: |P| reaches 127*127*block, the largest value a block can produce."""
+    from triton_functions import int8_matmul_block_partials
+    for block in (32, 64, 128):
+        m, k, n = 128, 2 * block, 256
+        a = torch.full((m, k), 127, dtype=torch.int8)
+        b = torch.full((n, k), -127, dtype=torch.int8)
+        b[::2] = 127
+        p = int8_matmul_block_partials(a.to(DEV), b.to(DEV).t(), block, flags=TC)
+        assert torch.equal(p.cpu(), O.gemm_block_partials(a, b.t(), block))
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_generic_kernel_bit_exact_fp32(shape):
+    m, k, n, block = shape
+    set_config(block, torch.float32)
+    xq, xs, wq, ws = quantized_pair(m, k, n, block, seed=3 * m + k + n)
+    bias = torch.randn(n, generator=torch.Generator().manual_seed(n))
+    c = _gemm(xq, wq, xs, ws, bias, flags=GENERIC)
+    ref = O.gemm(xq, wq.t(), xs, ws, bias, block, torch.float32)
+    assert torch.equal(c.cpu(), ref)
+    set_config(64)
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("mode", [TC, TC | NO_SEED])
+def test_tensor_core_kernel_fp32(shape, mode):
+    m, k, n, block = shape
+    set_config(block, torch.float32)
+    xq, xs, wq, ws = quantized_pair(m, k, n, block, seed=5 * m + k + n)
+    c = _gemm(xq, wq, xs, ws, flags=mode)
+    assert c.dtype == torch.float32 and tuple(c.shape) == (m, n)
+    _check_fp32(c, xq, wq, xs, ws, block)
+    bias = torch.randn(n, generator=torch.Generator().manual_seed(n)).to(torch.bfloat16)
+    _check_fp32(_gemm(xq, wq, xs, ws, bias, flags=mode), xq, wq, xs, ws, block, bias)
+    assert_clean_device()
+    set_config(64)
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_tensor_core_kernel_bf16(shape):
+    m, k, n, block = shape
+    set_config(block, torch.bfloat16)
+    xq, xs, wq, ws = quantized_pair(m, k, n, block, seed=7 * m + k + n)
+    bias = torch.randn(n, generator=torch.Generator().manual_seed(n)).to(torch.bfloat16)
+    for b in (None, bias):
+        c = _gemm(xq, wq, xs, ws, b, flags=TC)
+        assert c.dtype == torch.bfloat16
+        _check_bf16(c, xq, wq, xs, ws, block, b)
+    set_config(64)
+
+
+def test_default_dispatch_matches_forced_paths():
+    set_config(64, torch.float32)
+    xq, xs, wq, ws = quantized_pair(160, 512, 384, 64, seed=99)
+    assert torch.equal(_gemm(xq, wq, xs, ws), _gemm(xq, wq, xs, ws, flags=TC))
+    # K = 150: rows are not 16-byte aligned, the default path is the CUDA-core kernel
+    xq, xs, wq, ws = quantized_pair(20, 150, 24, 64, seed=98)
+    assert torch.equal(_gemm(xq, wq, xs, ws), _gemm(xq, wq, xs, ws, flags=GENERIC))
+    from blockwise_int8_linear_b200._lib import Bi8Error
+    with pytest.raises(Bi8Error):
+        _gemm(xq, wq, xs, ws, flags=TC)
+    set_config(64)
+
+
+@pytest.mark.parametrize("name", golden_names("ops_"))
+def test_golden_gemm(name):
+    g = load_golden(name)
+    set_config(g["block"], torch.float32)
+    bias = g.get("bias")
+    c = _gemm(g["xq"], g["wq"], g["xs"], g["ws"], bias, flags=GENERIC)
+    assert torch.equal(c.cpu(), g["c_f32"])
+    c = _gemm(g["xq"], g["wq"], g["xs"], g["ws"], bias)
+    _check_fp32(c, g["xq"], g["wq"], g["xs"], g["ws"], g["block"], bias)
+    set_config(64)
+
+
+def test_operand_layouts():
+    """b given as a contiguous [K, N] tensor and a given as a transposed view: handled like the reference (149-152)."""
+    from triton_functions import int8_matmul_block64_rowwise_dequantize as mm
+    set_config(64, torch.float32)
+    xq, xs, wq, ws = quantized_pair(96, 256, 160, 64, seed=21)
+    ref = _gemm(xq, wq, xs, ws)
+    b_kn = wq.t().contiguous().to(DEV)                    # [K, N] row-major
+    assert torch.equal(mm(xq.to(DEV), b_kn, xs.to(DEV), ws.to(DEV)), ref)
+    a_t = xq.t().contiguous().to(DEV).t()                 # [M, K] view with strides (1, M)
+    assert torch.equal(mm(a_t, wq.to(DEV).t(), xs.to(DEV), ws.to(DEV)), ref)
+    with pytest.raises(AssertionError, match="incompatible dimensions"):
+        mm(xq.to(DEV), wq.to(DEV)[:, :128].t(), xs.to(DEV), ws.to(DEV))
+    with pytest.raises(ValueError):
+        mm(xq.to(DEV), wq.to(DEV).t(), xs.to(DEV)[:2], ws.to(DEV))
+    set_config(64)
+
+
+@pytest.mark.parametrize("kn", [(4096, 4096), (4096, 11008), (11008, 4096)])
+@pytest.mark.parametrize("m", [1, 16, 128, 2048])
+def test_llama_projection_shapes(kn, m):
+    """BASELINE config: activations N(0,1) quantized on the fly, weights N(0, 0.02) pre-quantized, block 64, bf16 out."""
+    from triton_functions import quantize_block_rowwise
+    k, n = kn
+    set_config(64, torch.bfloat16)
+    x = O.synthetic((m, k), 3000 + m, outlier_frac=0.0)
+    w = O.synthetic((n, k), 3100 + n % 97, std=0.02, outlier_frac=0.0)
+    wq, ws = O.quantize(w, 64)
+    xq_g, xs_g = quantize_block_rowwise(x.to(DEV))
+    xq, xs = O.quantize(x, 64)
+    assert torch.equal(xq_g.cpu(), xq) and torch.equal(xs_g.cpu(), xs)
+    c = _gemm(xq, wq, xs, ws)
+    rows = slice(0, min(m, 256))
+    _check_bf16(c[rows], xq[rows], wq, xs[:, rows], ws, 64)
+    assert_clean_device()
+
+
+def test_largest_projection_shape_properties():
+    """M = 8192, K = 4096, N = 11008: the oracle is evaluated on a sample of rows; the rest is covered by a
+    size-independent property (row blocks of the same input give the same output rows)."""
+    from triton_functions import quantize_block_rowwise
+    set_config(64, torch.bfloat16)
+    m, k, n = 8192, 4096, 11008
+    x = O.synthetic((256, k), 3333, outlier_frac=0.0)
+    w = O.synthetic((n, k), 3334, std=0.02, outlier_frac=0.0)
+    wq, ws = O.quantize(w, 64)
+    xg = x.to(DEV).repeat(m // 256, 1)                     # 32 copies of the same 256 rows
+    xq_g, xs_g = quantize_block_rowwise(xg)
+    from triton_functions import int8_matmul_block64_rowwise_dequantize as mm
+    c = mm(xq_g, wq.to(DEV).t(), xs_g, ws.to(DEV))
+    xq, xs = O.quantize(x, 64)
+    _check_bf16(c[:256], xq, wq, xs, ws, 64)
+    assert torch.equal(c.view(m // 256, 256, n), c[:256].unsqueeze(0).expand(m // 256, 256, n))
+    assert_clean_device()
+
+
+def test_zero_sized():
+    from triton_functions import int8_matmul_block64_rowwise_dequantize as mm
+    set_config(64)
+    a = torch.empty((0, 128), dtype=torch.int8, device=DEV)
+    b = torch.zeros((256, 128), dtype=torch.int8, device=DEV)
+    c = mm(a, b.t(), torch.empty((2, 0), device=DEV), torch.ones((2, 256), device=DEV))
+    assert tuple(c.shape) == (0, 256)

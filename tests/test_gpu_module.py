@@ -1,0 +1,147 @@
+"""The module layer on the GPU: autograd function, BlockInt8Linear, replace_linear_with_blockwise_int8."""
+import pytest
+import torch
+import torch.nn as nn
+
+from oracle import blockwise_int8_oracle as O
+from tests.gpu_util import DEV, assert_clean_device, bf16_ulp_distance, set_config
+from tests.helpers import golden_names, load_golden
+
+pytestmark = pytest.mark.gpu
+
+
+def _close_fp32(got, ref, rel=2e-5):
+    scale = ref.abs().max().item() + 1e-30
+    assert (got.cpu() - ref).abs().max().item() <= rel * scale, (got.cpu() - ref).abs().max().item() / scale
+
+
+@pytest.mark.parametrize("name", golden_names("autograd_"))
+def test_autograd_against_reference_run(name):
+    """fp32 I/O (the configuration of the reference's own smoke script): forward, dX, dW, dbias against the values
+    produced by the reference's autograd function."""
+    from block_linear import blockwise_int8_linear
+    g = load_golden(name)
+    set_config(g["block"], torch.float32)
+    x = g["x"].to(DEV).requires_grad_(True)
+    w = g["w"].to(DEV).requires_grad_(True)
+    b = g["b"].to(DEV).requires_grad_(True) if "b" in g else None
+    y = blockwise_int8_linear.apply(x, w, b)
+    y.backward(g["gy"].to(DEV))
+    _close_fp32(y.detach(), g["y"])
+    _close_fp32(x.grad, g["gx"])
+    _close_fp32(w.grad, g["gw"])
+    if b is not None:
+        assert torch.allclose(b.grad.cpu(), g["gb"], rtol=1e-5, atol=1e-5)
+    assert_clean_device()
+    set_config(64)
+
+
+def test_training_step_bf16_vs_oracle():
+    from block_linear import BlockInt8Linear
+    set_config(64, torch.bfloat16)
+    torch.manual_seed(0)
+    lin = BlockInt8Linear(256, 384, bias=True, device=DEV, dtype=torch.bfloat16)
+    x = O.synthetic((4, 96, 256), 41).to(DEV).requires_grad_(True)
+    gy = O.synthetic((4, 96, 384), 42, outlier_frac=0).to(DEV)
+    lin.train()
+    y = lin(x)
+    y.backward(gy)
+    w, b = lin.weight.detach().cpu(), lin.bias.detach().cpu()
+    y_ref = O.linear_forward(x.detach().cpu(), w, b, 64)
+    gx_ref, gw_ref, gb_ref = O.linear_backward(x.detach().cpu(), w, gy.cpu(), 64)
+    for got, ref in ((y.detach(), y_ref), (x.grad, gx_ref), (lin.weight.grad, gw_ref)):
+        d = bf16_ulp_distance(got.cpu().reshape(ref.shape), ref)
+        assert d.max().item() <= 1 and (d == 0).float().mean().item() >= 0.99
+    assert torch.allclose(lin.bias.grad.float().cpu(), gb_ref.float(), rtol=2e-2, atol=2e-2)
+    assert_clean_device()
+
+
+def test_eval_path_and_state_dict():
+    from block_linear import BlockInt8Linear
+    set_config(64, torch.bfloat16)
+    torch.manual_seed(1)
+    lin = BlockInt8Linear(512, 320, bias=True, device=DEV, dtype=torch.bfloat16).eval()
+    x = O.synthetic((3, 40, 512), 43).to(DEV)
+    with torch.no_grad():
+        y = lin(x)
+    assert tuple(y.shape) == (3, 40, 320) and y.dtype == torch.bfloat16
+    y_ref = O.linear_forward(x.cpu(), lin.weight.detach().cpu(), lin.bias.detach().cpu(), 64)
+    d = bf16_ulp_distance(y.cpu(), y_ref)
+    assert d.max().item() <= 1 and (d == 0).float().mean().item() >= 0.99
+    sd = lin.state_dict()
+    assert sd["W_int8"].dtype == torch.int8 and tuple(sd["W_int8"].shape) == (320, 512)
+    assert sd["state_W"].dtype == torch.float32 and tuple(sd["state_W"].shape) == (8, 320)
+    wq_ref, ws_ref = O.quantize(lin.weight.detach().cpu(), 64)
+    assert torch.equal(sd["W_int8"].cpu(), wq_ref) and torch.equal(sd["state_W"].cpu(), ws_ref)
+    fresh = BlockInt8Linear(512, 320, bias=True, device=DEV, dtype=torch.bfloat16).eval()
+    fresh.load_state_dict(sd)
+    with torch.no_grad():
+        assert torch.equal(fresh(x), y)
+
+
+def test_replace_linear_in_model():
+    from block_linear import BlockInt8Linear, replace_linear_with_blockwise_int8
+    set_config(64, torch.bfloat16)
+
+    class MLP(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.up = nn.Linear(128, 256)
+            self.act = nn.GELU()
+            self.down = nn.Linear(256, 128, bias=False)
+            self.inner = nn.Sequential(nn.Linear(128, 128))
+
+        def forward(self, x):
+            return self.inner(self.down(self.act(self.up(x))))
+
+    torch.manual_seed(2)
+    m = MLP().to(DEV).to(torch.bfloat16)
+    w_up = m.up.weight
+    replace_linear_with_blockwise_int8(m)
+    assert isinstance(m.up, BlockInt8Linear) and isinstance(m.down, BlockInt8Linear)
+    assert not isinstance(m.inner[0], BlockInt8Linear)            # direct children only, like the reference
+    assert m.up.weight.data_ptr() == w_up.data_ptr()              # storage shared
+    m.apply(replace_linear_with_blockwise_int8)
+    assert isinstance(m.inner[0], BlockInt8Linear)
+    x = torch.randn(8, 128, device=DEV, dtype=torch.bfloat16)
+    ref = (x.float() @ m.up.weight.float().t() + m.up.bias.float())
+    m.train()
+    out = m.up(x)
+    assert ((out.float() - ref).norm() / ref.norm()).item() < 0.05
+    loss = m(x).float().pow(2).mean()
+    loss.backward()
+    assert m.up.weight.grad is not None and torch.isfinite(m.up.weight.grad.float()).all()
+    m.eval()
+    with torch.no_grad():
+        y = m(x)
+    assert torch.isfinite(y.float()).all()
+    assert_clean_device()
+
+
+def test_config0_single_forward():
+    """BASELINE config: x [256,1024], W [1024,1024] bf16 with outliers, block 64; checked against the fp32 product."""
+    from block_linear import BlockInt8Linear
+    set_config(64, torch.bfloat16)
+    x = O.synthetic((256, 1024), 1234)
+    w = O.synthetic((1024, 1024), 1235)
+    lin = BlockInt8Linear(1024, 1024, bias=False, device=DEV, dtype=torch.bfloat16).eval()
+    lin.weight.data.copy_(w.to(DEV))
+    with torch.no_grad():
+        y = lin(x.to(DEV))
+    ref = x.float() @ w.float().t()
+    rel = ((y.float().cpu() - ref).norm() / ref.norm()).item()
+    assert rel < 0.03, rel
+    d = bf16_ulp_distance(y.cpu(), O.linear_forward(x, w, None, 64))
+    assert d.max().item() <= 1 and (d == 0).float().mean().item() >= 0.99
+
+
+def test_fast_matmul_helpers():
+    from block_linear import fast_matmul
+    from triton_functions import fast_matmulT
+    set_config(64, torch.bfloat16)
+    a = O.synthetic((64, 256), 51)
+    b = O.synthetic((128, 256), 52)
+    ref = O.linear_forward(a, b, None, 64)
+    d1 = bf16_ulp_distance(fast_matmulT(a.to(DEV), b.to(DEV)).cpu(), ref)
+    d2 = bf16_ulp_distance(fast_matmul(a.to(DEV), b.t().contiguous().to(DEV)).cpu(), ref)
+    assert d1.max().item() <= 1 and d2.max().item() <= 1

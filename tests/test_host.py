@@ -1,0 +1,124 @@
+"""Host-side checks that need no GPU: the library loads, exports what the header declares, validates its
+arguments before touching CUDA, and the Python surface mirrors the reference's names."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def L():
+    from blockwise_int8_linear_b200 import build, _lib
+    build.build()
+    return _lib.lib()
+
+
+def test_library_exports_every_declared_symbol(L):
+    header = open(os.path.join(ROOT, "include", "bi8.h")).read()
+    declared = sorted(set(re.findall(r"BI8_API[^;]*?\b(bi8_\w+)\s*\(", header)))
+    assert len(declared) >= 11
+    for name in declared:
+        assert hasattr(L, name), name
+    from blockwise_int8_linear_b200 import _lib
+    assert sorted(_lib.EXPORTS) == [d for d in declared if d in _lib.EXPORTS]
+    assert set(declared) - set(_lib.EXPORTS) <= {"bi8_gemm_dequant_static"}
+    assert L.bi8_version() == 100
+
+
+def test_argument_validation_happens_before_cuda(L):
+    vp = ctypes.c_void_p
+    one = vp(256)          # a non-null, aligned, never dereferenced address
+    err = lambda: L.bi8_last_error_string().decode()
+    assert L.bi8_quantize_rowwise(one, 7, 64, one, one, 4, 64, 64, None) == -1 and "dtype" in err()
+    assert L.bi8_quantize_rowwise(one, 0, 64, one, one, 4, 64, 0, None) == -2
+    assert L.bi8_quantize_rowwise(one, 0, 32, one, one, 4, 64, 64, None) == -4      # pitch < K
+    assert L.bi8_quantize_rowwise(None, 0, 64, one, one, 4, 64, 64, None) == -8
+    assert L.bi8_quantize_rowwise(vp(257), 0, 64, one, one, 4, 64, 64, None) == -3
+    assert L.bi8_quantize_rowwise(None, 0, 64, None, None, 0, 64, 64, None) == 0      # empty: nothing to do
+    assert L.bi8_quantize_colwise(one, 0, 8, one, one, 4, 64, 64, None) == -4
+    assert L.bi8_dequantize_rowwise(one, one, one, 9, 4, 64, 64, None) == -1
+    assert L.bi8_dequantize_rowwise(one, one, None, 0, 4, 64, 64, None) == -8
+    g = lambda **kw: L.bi8_gemm_dequant(kw.get("A", one), kw.get("lda", 64), one, 64, one, one, None, 0, kw.get("C", one),
+                                        kw.get("ldc", 64), kw.get("dt", 0), kw.get("M", 8), 64, 64, kw.get("block", 64),
+                                        None, 0, 0, None)
+    assert g(M=-1) == -4
+    assert g(block=0) == -2
+    assert g(A=None) == -8
+    assert g(lda=8) == -4
+    assert g(dt=5) == -1
+    assert g(C=None) == -8
+    assert g(ldc=8) == -4
+    assert g(M=0) == 0
+    assert L.bi8_gemm_workspace_bytes(128, 128, 128, 64) == 0
+
+
+def test_python_surface_mirrors_reference_names():
+    import block_linear
+    import block_linear_config
+    import triton_functions
+    import blockwise_int8_linear_b200 as pkg
+
+    assert block_linear_config is pkg.block_linear_config
+    for name in ("quantize_block_rowwise", "dequantize_block_rowwise", "int8_matmul_block64_rowwise_dequantize",
+                 "fast_matmulT", "ceil_div"):
+        assert callable(getattr(triton_functions, name))
+    for name in ("replace_linear_with_blockwise_int8", "fast_matmul", "blockwise_int8_linear", "BlockInt8Linear"):
+        assert hasattr(block_linear, name)
+    assert block_linear.BlockLinear is block_linear.BlockInt8Linear
+    assert issubclass(block_linear.BlockInt8Linear, torch.nn.Linear)
+    # defaults of the reference (block_linear_config.py:3-5)
+    import importlib
+    fresh = importlib.reload(block_linear_config)
+    assert fresh.GROUP_SIZE == 128 and fresh.SHARED_EXP_TORCH_TYPE == torch.float32
+    assert fresh.INPUT_OUTPUT_TORCH_TYPE == torch.bfloat16
+
+
+def test_config_knobs_are_read_at_call_time():
+    import block_linear_config as cfg
+    from blockwise_int8_linear_b200.block_linear import BlockLinearConfig
+    from blockwise_int8_linear_b200 import triton_functions as tf
+
+    old = cfg.GROUP_SIZE
+    cfg.GROUP_SIZE = 64
+    assert tf._block() == 64 and tf._block(32) == 32
+    with BlockLinearConfig(group_size=32, io_dtype=torch.float32) as c:
+        assert cfg.GROUP_SIZE == 32 and c.group_size == 32 and cfg.INPUT_OUTPUT_TORCH_TYPE == torch.float32
+    assert cfg.GROUP_SIZE == 64 and cfg.INPUT_OUTPUT_TORCH_TYPE == torch.bfloat16
+    cfg.SHARED_EXP_TORCH_TYPE = torch.float16
+    with pytest.raises(ValueError):
+        tf._scale_dtype()
+    cfg.SHARED_EXP_TORCH_TYPE = torch.float32
+    cfg.GROUP_SIZE = old
+
+
+def test_cpu_tensors_are_rejected_like_the_reference():
+    import triton_functions as tf
+    with pytest.raises(AssertionError):
+        tf.quantize_block_rowwise(torch.zeros(4, 64, dtype=torch.bfloat16))
+    with pytest.raises(AssertionError):
+        tf.dequantize_block_rowwise(torch.zeros(4, 64, dtype=torch.int8), torch.zeros(1, 4))
+
+
+def test_replace_linear_on_cpu_module_structure():
+    import torch.nn as nn
+    from block_linear import BlockInt8Linear, replace_linear_with_blockwise_int8
+
+    m = nn.Sequential(nn.Linear(8, 16), nn.ReLU(), nn.Linear(16, 4, bias=False))
+    w0 = m[0].weight.data_ptr()
+    replace_linear_with_blockwise_int8(m)
+    assert isinstance(m[0], BlockInt8Linear) and isinstance(m[2], BlockInt8Linear)
+    assert m[0].weight.data_ptr() == w0 and m[2].bias is None
+    assert m[0].in_features == 8 and m[0].out_features == 16 and tuple(m[0].weight.shape) == (16, 8)
+
+
+def test_product_code_does_not_import_the_oracle():
+    pkg = os.path.join(ROOT, "blockwise_int8_linear_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in text, f"{f} mentions the oracle"

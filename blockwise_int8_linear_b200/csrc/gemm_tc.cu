@@ -12,10 +12,11 @@
 //               into one of two 256-column s32 accumulators in tensor memory, then a commit hands that
 //               accumulator to the promotion warps
 //   warps 2-3   stage the block scales of the tile (sA: 128 rows, sB: 256 columns per block) in shared memory
-//   warps 4-11  promotion + epilogue: read an accumulator from tensor memory (each warp owns 32 rows x 128
+//   warps 4-19  promotion + epilogue: read an accumulator from tensor memory (each warp owns 32 rows x 64
 //               columns), fold it into fp32 accumulators held in registers, release the accumulator; after
 //               the last block convert, add bias and store
-// Registers are moved from warps 0-3 to warps 4-11 with setmaxnreg (128 fp32 accumulators per thread).
+// Registers are moved from warps 0-3 to warps 4-19 with setmaxnreg (64 fp32 accumulators per thread); four
+// promotion warps per scheduler cover each other's tensor-memory load latency.
 //
 // Seeded conversion (default): the promotion warps refill a drained accumulator with the bit pattern of
 // 1.5*2^23 and every MMA accumulates on top of it.  Integer addition on that pattern is exact float
@@ -27,6 +28,7 @@
 
 #include <cuda.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -40,8 +42,9 @@ constexpr int kBN = 256;                 // tile columns
 constexpr int kBK = 128;                 // K bytes per stage (one 128-byte swizzle row)
 constexpr int kStages = 4;
 constexpr int kScaleStages = 4;
-constexpr int kThreadsTc = 384;
-constexpr int kEpiWarps = 8;
+constexpr int kEpiWarps = 16;             // 4 lane quarters x 4 column slices of 64
+constexpr int kThreadsTc = (4 + kEpiWarps) * 32;
+constexpr int kEpiCols = kBN / (kEpiWarps / 4);   // columns owned by one promotion warp
 constexpr uint32_t kABytes = kBM * kBK;  // 16 KiB
 constexpr uint32_t kBBytes = kBN * kBK;  // 32 KiB
 constexpr uint32_t kSeedBits = 0x4B400000u;   // float 1.5 * 2^23
@@ -63,6 +66,7 @@ struct TcParams {
     int out_dtype, bias_dtype;
     int vec_store;      // C base and row pitch allow 16-byte stores
     int vec_scales;     // sA, sB and their row lengths allow 16-byte loads
+    int debug;          // timing experiments only (env BI8_DEBUG): 1 skip FMAs, 2 skip TMEM loads, 4 skip re-seed, 8 skip MMAs
 };
 
 struct Smem {
@@ -107,6 +111,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const uint32_t base = (raw + 1023u) & ~1023u;
     unsigned char* base_ptr = smem_dyn + (base - raw);
     float* sc_ring = reinterpret_cast<float*>(base_ptr + Smem::scale_off);
+    const uint32_t sc_ring_u32 = base + Smem::scale_off;
     const uint32_t bars = base + G::bar_off;
     volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(base_ptr + G::misc_off);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + G::misc_off + 4);
@@ -126,7 +131,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             mbar_init(bar(G::ACC_EMPTY + b), kEpiWarps);
         }
         for (int s = 0; s < kScaleStages; ++s) {
-            mbar_init(bar(G::SC_FULL + s), 2);
+            mbar_init(bar(G::SC_FULL + s), 64);      // every lane of the two scale warps
             mbar_init(bar(G::SC_EMPTY + s), kEpiWarps);
         }
         *abort_flag = 0;
@@ -142,8 +147,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
 
+    // setmaxnreg moves registers inside the CTA's launch-time allocation (kThreadsTc * 96): the totals after
+    // the moves must not exceed it, or setmaxnreg.inc blocks forever.
+    static_assert(128 * 24 + (kThreadsTc - 128) * 112 <= kThreadsTc * 96, "register budget exceeds the launch allocation");
     if (warp < 4) {
-        setmaxnreg_dec<88>();
+        setmaxnreg_dec<24>();
         if (warp == 0) {
             // ---------------- TMA producer ----------------
             if (lane == 0) {
@@ -162,9 +170,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             ok = false;
                             break;
                         }
-                        mbar_expect_tx(bar(G::FULL_AB + stage), kABytes + kBBytes);
-                        tma_load_2d(base + Smem::a_off(stage), &tmA, bar(G::FULL_AB + stage), ks * kBK, m0);
-                        tma_load_2d(base + Smem::b_off(stage), &tmB, bar(G::FULL_AB + stage), ks * kBK, n0);
+                        if (p.debug & 64) {
+                            mbar_arrive(bar(G::FULL_AB + stage));
+                        } else {
+                            mbar_expect_tx(bar(G::FULL_AB + stage), kABytes + kBBytes);
+                            tma_load_2d(base + Smem::a_off(stage), &tmA, bar(G::FULL_AB + stage), ks * kBK, m0);
+                            tma_load_2d(base + Smem::b_off(stage), &tmB, bar(G::FULL_AB + stage), ks * kBK, n0);
+                        }
 #pragma unroll
                         for (int s = 0; s < kStages; ++s)
                             if (s == stage) last_parity[s] = (int)phase;
@@ -202,7 +214,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
                         for (int blk = 0; blk < G::BPS; ++blk) {
                             if (ks * G::BPS + blk >= p.nb) break;
-                            if (!mbar_wait(bar(G::ACC_EMPTY + accbuf), accphase, abort_flag)) {
+                            if (!(p.debug & 16) && !mbar_wait(bar(G::ACC_EMPTY + accbuf), accphase, abort_flag)) {
                                 report_timeout(p.status, abort_flag, W_ACC_EMPTY);
                                 ok = false;
                                 break;
@@ -211,7 +223,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
                             for (int i = 0; i < G::MMAS; ++i) {
                                 const uint64_t koff = (uint64_t)((blk * G::MMAS + i) * 32 / 16);
-                                mma_i8(tmem_base + (uint32_t)accbuf * kBN, adesc + koff, bdesc + koff, idesc,
+                                if (!(p.debug & 8)) mma_i8(tmem_base + (uint32_t)accbuf * kBN, adesc + koff, bdesc + koff, idesc,
                                        (SEED || i > 0) ? 1u : 0u);
                             }
                             tc_commit(bar(G::ACC_FULL + accbuf));
@@ -238,65 +250,56 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 tile_coords(tile, p.tiles_m, m0, n0);
                 const int x0 = is_a ? m0 : n0;
                 for (int ks = 0; ks < nks; ++ks) {
-                    ok = __all_sync(0xffffffffu, mbar_wait(bar(G::SC_EMPTY + sstage), sphase ^ 1u, abort_flag));
+                    ok = (p.debug & 32) ? true : __all_sync(0xffffffffu, mbar_wait(bar(G::SC_EMPTY + sstage), sphase ^ 1u, abort_flag));
                     if (!ok) {
                         if (lane == 0) report_timeout(p.status, abort_flag, W_SC_EMPTY);
                         break;
                     }
-                    float* dst = sc_ring + sstage * G::SC_FLOATS + dst_off;
-                    if (p.vec_scales) {
-                        // all loads of the stage are issued before the first store
-                        constexpr int MAXV = G::BPS * kBN / 4 / 32;          // float4 per lane for sB
-                        const int nv = G::BPS * width / 4;                   // float4 in this warp's part
-                        float4 v[MAXV];
-#pragma unroll
-                        for (int i = 0; i < MAXV; ++i) {
-                            const int idx = lane + 32 * i;
-                            v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                            if (idx < nv) {
-                                const int blk = idx / (width / 4), c4 = (idx % (width / 4)) * 4;
-                                const int j = ks * G::BPS + blk;
-                                if (src != nullptr && j < p.nb && x0 + c4 < extent)
-                                    v[i] = __ldg(reinterpret_cast<const float4*>(src + (int64_t)j * extent + x0 + c4));
-                            }
-                        }
-#pragma unroll
-                        for (int i = 0; i < MAXV; ++i) {
-                            const int idx = lane + 32 * i;
-                            if (idx < nv) {
-                                const int blk = idx / (width / 4), c4 = (idx % (width / 4)) * 4;
-                                *reinterpret_cast<float4*>(dst + blk * (kBM + kBN) + c4) = v[i];
-                            }
+                    // asynchronous copies: the warp does not wait for the data, so the loads of several stages are
+                    // in flight at once; each lane's arrival on the stage's barrier fires when its copies have landed
+                    const uint32_t dst = sc_ring_u32 + (uint32_t)((sstage * G::SC_FLOATS + dst_off) * 4);
+                    if (src == nullptr) {
+                        // partial-sum dump: no scales, the ring content is never used
+                    } else if (p.vec_scales) {
+                        const int nv = G::BPS * width / 4;                   // 16-byte pieces in this warp's part
+                        for (int idx = lane; idx < nv; idx += 32) {
+                            const int blk = idx / (width / 4), c4 = (idx % (width / 4)) * 4;
+                            const int j = ks * G::BPS + blk;
+                            const bool live = j < p.nb && x0 + c4 < extent;
+                            const float* g = live ? src + (int64_t)j * extent + x0 + c4 : src;
+                            cp_async_16(dst + (uint32_t)((blk * (kBM + kBN) + c4) * 4), g, live ? 16u : 0u);
                         }
                     } else {
                         for (int idx = lane; idx < G::BPS * width; idx += 32) {
                             const int blk = idx / width, c = idx % width;
                             const int j = ks * G::BPS + blk;
-                            float v = 0.0f;
-                            if (src != nullptr && j < p.nb && x0 + c < extent) v = __ldg(src + (int64_t)j * extent + x0 + c);
-                            dst[blk * (kBM + kBN) + c] = v;
+                            const bool live = j < p.nb && x0 + c < extent;
+                            const float* g = live ? src + (int64_t)j * extent + x0 + c : src;
+                            cp_async_4(dst + (uint32_t)((blk * (kBM + kBN) + c) * 4), g, live ? 4u : 0u);
                         }
                     }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar(G::SC_FULL + sstage));
+                    cp_async_arrive(bar(G::SC_FULL + sstage));
                     if (++sstage == kScaleStages) { sstage = 0; sphase ^= 1u; }
                 }
             }
         }
     } else {
-        // ---------------- promotion + epilogue (warps 4..11) ----------------
-        setmaxnreg_inc<208>();
+        // ---------------- promotion + epilogue (warps 4..19) ----------------
+        setmaxnreg_inc<112>();
         const int quarter = warp & 3;            // tensor-memory lanes 32*quarter .. +31 belong to this warp
-        const int half = (warp - 4) >> 2;        // columns 128*half .. +127 of the tile
+        const int slice = (warp - 4) >> 2;       // columns kEpiCols*slice .. of the tile
         const int row = quarter * 32 + lane;
-        const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * 128);
+        const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(slice * kEpiCols);
         const float div = 1.0f / (127.0f * 127.0f);
+        uint32_t seedv[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) seedv[i] = opaque_u32(kSeedBits);
 
         if (SEED) {
 #pragma unroll
             for (int b = 0; b < 2; ++b)
 #pragma unroll
-                for (int c = 0; c < 4; ++c) tmem_fill32(t_lane + (uint32_t)(b * kBN + c * 32), kSeedBits);
+                for (int c = 0; c < kEpiCols / 8; ++c) tmem_st8(t_lane + (uint32_t)(b * kBN + c * 8), seedv);
             tmem_wait_st();
         }
         tc_fence_before();
@@ -313,13 +316,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             int m0, n0;
             tile_coords(tile, p.tiles_m, m0, n0);
             const int m = m0 + row;
-            const int nbase = n0 + half * 128;
-            float acc[128];
+            const int nbase = n0 + slice * kEpiCols;
+            // kEpiCols fp32 accumulators per thread, kept as packed pairs for fma.rn.f32x2
+            uint64_t acc2[kEpiCols / 2];
 #pragma unroll
-            for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
+            for (int i = 0; i < kEpiCols / 2; ++i) acc2[i] = 0ull;
 
             for (int ks = 0; ks < nks && ok; ++ks) {
-                ok = __all_sync(0xffffffffu, mbar_wait(bar(G::SC_FULL + sstage), sphase, abort_flag));
+                ok = (p.debug & 32) ? true : __all_sync(0xffffffffu, mbar_wait(bar(G::SC_FULL + sstage), sphase, abort_flag));
                 if (!ok) {
                     if (lane == 0) report_timeout(p.status, abort_flag, W_SC_FULL);
                     break;
@@ -329,53 +333,67 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 for (int blk = 0; blk < G::BPS; ++blk) {
                     const int j = ks * G::BPS + blk;
                     if (j >= p.nb) break;
-                    ok = __all_sync(0xffffffffu, mbar_wait(bar(G::ACC_FULL + accbuf), accphase, abort_flag));
+                    ok = (p.debug & 16) ? true : __all_sync(0xffffffffu, mbar_wait(bar(G::ACC_FULL + accbuf), accphase, abort_flag));
                     if (!ok) {
                         if (lane == 0) report_timeout(p.status, abort_flag, W_ACC_FULL);
                         break;
                     }
                     tc_fence_after();
                     const uint32_t t_acc = t_lane + (uint32_t)(accbuf * kBN);
-                    float sxd = __fmul_rn(sc[blk * (kBM + kBN) + row], div);
-                    float negc = 0.0f;
-                    if (SEED) {
-                        sxd = __uint_as_float((__float_as_uint(sxd) + 2u) & 0xFFFFFFFCu);   // 22 significant bits
-                        negc = -__fmul_rn(kSeedF, sxd);                                      // exact
-                    }
-                    const float4* swv = reinterpret_cast<const float4*>(sc + blk * (kBM + kBN) + kBM + half * 128);
+                    if (MODE == 1) {
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t pv[32];
-                        tmem_ld32(t_acc + (uint32_t)(c * 32), pv);
-                        tmem_wait_ld();
-                        if (MODE == 1) {
+                        for (int c = 0; c < kEpiCols / 16; ++c) {
+                            uint32_t pv[16];
+                            tmem_ld16(t_acc + (uint32_t)(c * 16), pv);
+                            tmem_wait_ld();
+                            if (SEED) { tmem_st8(t_acc + (uint32_t)(c * 16), seedv); tmem_st8(t_acc + (uint32_t)(c * 16 + 8), seedv); }
                             if (m < p.M) {
-                                int32_t* dst = p.partials + ((int64_t)j * p.M + m) * p.N + nbase + c * 32;
+                                int32_t* dst = p.partials + ((int64_t)j * p.M + m) * p.N + nbase + c * 16;
 #pragma unroll
-                                for (int i = 0; i < 32; ++i)
-                                    if (nbase + c * 32 + i < p.N)
+                                for (int i = 0; i < 16; ++i)
+                                    if (nbase + c * 16 + i < p.N)
                                         dst[i] = SEED ? (int32_t)(pv[i] - kSeedBits) : (int32_t)pv[i];
                             }
-                        } else {
+                        }
+                        if (SEED) tmem_wait_st();
+                    } else {
+                        float sxd = __fmul_rn(sc[blk * (kBM + kBN) + row], div);
+                        float negc = 0.0f;
+                        if (SEED) {
+                            sxd = __uint_as_float((__float_as_uint(sxd) + 2u) & 0xFFFFFFFCu);   // 22 significant bits
+                            negc = -__fmul_rn(kSeedF, sxd);                                      // exact
+                        }
+                        const uint64_t sxd2 = pack_f32x2(sxd, sxd), negc2 = pack_f32x2(negc, negc);
+                        const ulonglong2* swv =
+                            reinterpret_cast<const ulonglong2*>(sc + blk * (kBM + kBN) + kBM + slice * kEpiCols);
+                        // chunks of 8 columns, double buffered: while chunk c is folded into the accumulators the load
+                        // of chunk c+1 and the re-seed of chunk c are in flight
+                        uint32_t pa[8], pb[8];
+                        tmem_ld8(t_acc, pa);
 #pragma unroll
-                            for (int i4 = 0; i4 < 8; ++i4) {
-                                const float4 w = swv[c * 8 + i4];
-                                const float ws[4] = {w.x, w.y, w.z, w.w};
+                        for (int c = 0; c < kEpiCols / 8; ++c) {
+                            uint32_t(&cur)[8] = (c & 1) ? pb : pa;
+                            uint32_t(&nxt)[8] = (c & 1) ? pa : pb;
+                            tmem_wait_ld();
+                            if (c + 1 < kEpiCols / 8 && !(p.debug & 2)) tmem_ld8(t_acc + (uint32_t)((c + 1) * 8), nxt);
+                            if (SEED && !(p.debug & 4)) tmem_st8(t_acc + (uint32_t)(c * 8), seedv);
+                            if (p.debug & 1) continue;
 #pragma unroll
-                                for (int u = 0; u < 4; ++u) {
-                                    const int i = i4 * 4 + u;
-                                    float t;
-                                    if (SEED) t = __fmaf_rn(__uint_as_float(pv[i]), sxd, negc);
-                                    else t = __fmul_rn((float)(int32_t)pv[i], sxd);
-                                    acc[c * 32 + i] = __fmaf_rn(ws[u], t, acc[c * 32 + i]);
+                            for (int q = 0; q < 2; ++q) {
+                                const ulonglong2 w = swv[c * 2 + q];
+                                uint64_t t0, t1;
+                                if (SEED) {
+                                    t0 = fma_f32x2(pack_u32x2(cur[4 * q], cur[4 * q + 1]), sxd2, negc2);
+                                    t1 = fma_f32x2(pack_u32x2(cur[4 * q + 2], cur[4 * q + 3]), sxd2, negc2);
+                                } else {
+                                    t0 = fma_f32x2(pack_f32x2((float)(int32_t)cur[4 * q], (float)(int32_t)cur[4 * q + 1]), sxd2, 0ull);
+                                    t1 = fma_f32x2(pack_f32x2((float)(int32_t)cur[4 * q + 2], (float)(int32_t)cur[4 * q + 3]), sxd2, 0ull);
                                 }
+                                acc2[c * 4 + q * 2] = fma_f32x2(w.x, t0, acc2[c * 4 + q * 2]);
+                                acc2[c * 4 + q * 2 + 1] = fma_f32x2(w.y, t1, acc2[c * 4 + q * 2 + 1]);
                             }
                         }
-                    }
-                    if (SEED) {
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) tmem_fill32(t_acc + (uint32_t)(c * 32), kSeedBits);
-                        tmem_wait_st();
+                        if (SEED) tmem_wait_st();
                     }
                     tc_fence_before();
                     __syncwarp();
@@ -390,6 +408,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (!ok) break;
 
             if (MODE == 0 && m < p.M) {
+                float acc[kEpiCols];
+#pragma unroll
+                for (int i = 0; i < kEpiCols / 2; ++i) unpack_f32x2(acc2[i], acc[2 * i], acc[2 * i + 1]);
                 const bool has_bias = p.bias != nullptr;
                 auto bias_at = [&](int n) -> float {
                     if (p.bias_dtype == BI8_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n]);
@@ -399,7 +420,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 if (p.out_dtype == BI8_F32) {
                     float* crow = static_cast<float*>(p.C) + (int64_t)m * p.ldc;
 #pragma unroll
-                    for (int g = 0; g < 32; ++g) {
+                    for (int g = 0; g < kEpiCols / 4; ++g) {
                         const int n = nbase + g * 4;
                         float v[4];
 #pragma unroll
@@ -419,7 +440,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const bool bf = p.out_dtype == BI8_BF16;
                     uint16_t* crow = static_cast<uint16_t*>(p.C) + (int64_t)m * p.ldc;
 #pragma unroll
-                    for (int g = 0; g < 16; ++g) {
+                    for (int g = 0; g < kEpiCols / 8; ++g) {
                         const int n = nbase + g * 8;
                         uint32_t w[4];
 #pragma unroll
@@ -619,6 +640,10 @@ int launch_gemm_tc(const GemmArgs& g, cudaStream_t st) {
     const int esz = g.out_dtype == BI8_F32 ? 4 : 2;
     p.vec_store = (g.C != nullptr && aligned(g.C, 16) && (g.ldc * esz) % 16 == 0) ? 1 : 0;
     p.vec_scales = (g.partials == nullptr && aligned(g.sA, 16) && aligned(g.sB, 16) && g.M % 4 == 0 && g.N % 4 == 0) ? 1 : 0;
+    {
+        const char* dbg = std::getenv("BI8_DEBUG");
+        p.debug = dbg ? std::atoi(dbg) : 0;
+    }
     const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
     if (tiles >= (1ll << 31)) return fail(BI8_ERR_SHAPE, "too many output tiles");
     const int grid = (int)(tiles < di.sms ? tiles : di.sms);

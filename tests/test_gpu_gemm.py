@@ -3,10 +3,15 @@
 Stated tolerances:
 * int32 block partial sums: exact.
 * CUDA-core (generic) kernel, fp32 output: bit-exact against the oracle (same operation order as the reference).
-* tensor-core kernel, fp32 output: |c - oracle| <= 8 * 2^-24 * sum_j |term_j| + 1e-30 per element (the kernel multiplies the
-  three factors of a term in a different order, and in seeded mode rounds sA/127^2 to 22 bits: at most ~3 fp32
-  roundings per term instead of the reference's 3 in another order).
-* tensor-core kernel, bf16 output: at most 1 bf16 step away from the oracle's bf16 result, >= 99 % identical.
+* tensor-core kernel, fp32 output: |c - oracle| <= 12 * 2^-24 * sum_j |term_j| per element.  The kernel multiplies the three
+  factors of a term in another order than the reference and, in seeded mode, rounds sA/127^2 to 22 bits: up to 4 roundings of
+  2^-24 per term against the reference's 3, so the two sides differ by at most 7 * 2^-24 |term_j| per term, plus the
+  difference of the two fp32 running sums (each rounding of a partial sum is bounded by 2^-24 * sum_j |term_j|; they mostly
+  cancel between the two sides).  Observed worst case over the test shapes: 6.7 * 2^-24 * sum_j |term_j|.
+* tensor-core kernel, bf16 output: the bf16 value is the RNE cast of that fp32 accumulator, so
+  |c - oracle_fp32| <= 12 * 2^-24 * sum_j |term_j| + half a bf16 step of |c|; and >= 99 % of the elements are bit-identical
+  to the oracle's bf16 result.  (Where the terms cancel, "within one bf16 step of the oracle's bf16 value" is not a meaningful
+  bound: a tiny result has tiny steps, while its error is set by the magnitude of the terms.)
 """
 import pytest
 import torch
@@ -18,7 +23,7 @@ from tests.helpers import golden_names, load_golden
 pytestmark = pytest.mark.gpu
 
 GENERIC, TC, NO_SEED = 1, 2, 4
-FP32_TOL = 8 * 2.0 ** -24
+FP32_TOL = 12 * 2.0 ** -24
 
 
 def _gemm(xq, wq, xs, ws, bias=None, flags=0):
@@ -37,12 +42,23 @@ def _check_fp32(c, xq, wq, xs, ws, block, bias=None):
     assert not bad.any(), f"{bad.sum().item()} elements beyond tolerance, worst ratio {(err / (mag + 1e-30)).max().item() / 2.0 ** -24:.2f} x 2^-24"
 
 
-def _check_bf16(c, xq, wq, xs, ws, block, bias=None):
-    ref = O.gemm(xq, wq.t(), xs, ws, bias, block, torch.bfloat16)
-    d = bf16_ulp_distance(c.cpu(), ref)
-    assert d.max().item() <= 1, f"max distance {d.max().item()} bf16 steps"
-    same = (d == 0).float().mean().item()
-    assert same >= 0.99, f"only {same:.4f} identical"
+def _check_bf16(c, xq, wq, xs, ws, block, bias=None, identical=0.99):
+    acc = O.gemm_acc(xq, wq.t(), xs, ws, block)
+    mag = O.gemm_term_abs_sum(xq, wq.t(), xs, ws, block)
+    ref = acc.to(torch.bfloat16)
+    if bias is not None:
+        ref = ref + bias.to(torch.bfloat16)
+        mag = mag + bias.float().abs()
+    cf = c.float().cpu()
+    # half a bf16 step of the stored value, plus half a step of the intermediate cast when a bias is added after it
+    half_step = cf.abs() * 2.0 ** -8
+    if bias is not None:
+        half_step = half_step + acc.abs() * 2.0 ** -8
+    err = (cf - (acc if bias is None else acc + bias.float())).abs()
+    bad = err > (FP32_TOL * mag + half_step + 1e-30)
+    assert not bad.any(), f"{bad.sum().item()} elements beyond tolerance"
+    same = (bf16_ulp_distance(c.cpu(), ref) == 0).float().mean().item()
+    assert same >= identical, f"only {same:.4f} identical"
 
 
 SHAPES = [

@@ -25,36 +25,51 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+// Shared-memory loads through 32-bit shared addresses (a generic pointer costs two registers and an address
+// conversion; the promotion loop has none to spare).
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void lds_2xb64(uint32_t addr, uint64_t& a, uint64_t& b) {
+    asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "r"(addr));
+}
+__device__ __forceinline__ uint32_t lds_volatile_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ void sts_u32(uint32_t addr, uint32_t v) {
+    asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+
+// One try_wait with a suspend-time hint: the hardware parks the thread (no issue slots spent) until the phase
+// completes or roughly `hint_ns` have passed.  Without the hint the default suspension is so short that a
+// waiting warp polls continuously and competes with the working warps for issue slots.
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity, uint32_t hint_ns = 200000u) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
         : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ uint64_t globaltimer_ns() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
 
-// Bounded wait on an mbarrier phase.  Gives up after `limit_ns` of wall time, or as soon as another
-// thread of the CTA has raised *abort_flag (a volatile word in shared memory); returns false then.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          uint64_t limit_ns = 2000000000ull) {
+// Bounded wait on an mbarrier phase.  After every failed (suspended) poll the thread looks at the CTA's abort
+// flag (a word in shared memory, given by its shared address, raised by whichever thread gives up first) and at the SM cycle
+// counter; it gives up after `limit_cycles` (default 4e9, about two seconds) and returns false.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t abort_flag_smem,
+                                          long long limit_cycles = 4000000000ll) {
     if (mbar_try(bar, parity)) return true;
-    const uint64_t t0 = globaltimer_ns();
-    uint32_t spins = 0;
+    const long long t0 = clock64();
     while (true) {
         if (mbar_try(bar, parity)) return true;
-        if (((++spins) & 63u) == 0u) {
-            if (*abort_flag != 0) return false;
-            if (globaltimer_ns() - t0 > limit_ns) return false;
-        }
+        if (lds_volatile_u32(abort_flag_smem) != 0u) return false;
+        if (clock64() - t0 > limit_cycles) return false;
     }
 }
 

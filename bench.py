@@ -77,7 +77,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE,
+                                          "-lms", "25", "-i", str(self.gpu)], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -371,7 +371,7 @@ def run_ours(args):
         print(f"mma probe failed: {e}", file=sys.stderr)
     peak = 2.0 * bf16_tf
     roofline = {
-        "bound": "tensor", "kernel": "gemm_tc_kernel<64> (tcgen05 kind::i8)", "achieved": achieved, "peak": peak,
+        "bound": "tensor", "kernel": "gemm_tc_kernel<64,0,seeded> (tcgen05 kind::i8, 128x160 tiles)", "achieved": achieved, "peak": peak,
         "unit": "TFLOP/s", "frac": achieved / peak,
         "peak_source": f"2 x {peak_src} cuBLAS bf16 burst ({bf16_tf} TF/s); int8 multiply-add counted as 2 ops",
         "frac_of_nominal_int8_4500": achieved / INT8_NOMINAL_TOPS,
@@ -414,8 +414,8 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default=DEFAULT_WORKLOAD)
     ap.add_argument("--no-extras", action="store_true", help="skip the quantize/dequantize/GEMM-shape sweep")

@@ -5,17 +5,18 @@
 //   acc += sB[j,n] * sA[j,m] * float(P_j) / 127^2   fp32, j ascending (line 120)
 //   C = cast(acc) (+ cast(bias))                    (lines 125-131)
 //
-// One persistent CTA per SM works on 128 x 192 output tiles.  Warp roles:
-//   warp 0      TMA producer: 128-byte-swizzled K-major tiles of A (128 rows) and Bt (192 rows), 128 K-bytes
+// One persistent CTA per SM works on 128 x 160 output tiles.  Warp roles:
+//   warp 0      TMA producer: 128-byte-swizzled K-major tiles of A (128 rows) and Bt (160 rows), 128 K-bytes
 //               per stage, ring of kStages stages
-//   warp 1      issues tcgen05.mma kind::i8 (M128 N192 K32): the MMAs of one quantisation block accumulate
-//               into one of two s32 accumulators in tensor memory, then a commit hands that
+//   warp 1      issues tcgen05.mma kind::i8 (M128 N160 K32): the MMAs of one quantisation block accumulate
+//               into one of three s32 accumulators in tensor memory (the hand-off latency of a block is
+//               several times its MMA time, so more than two blocks have to be in flight), then a commit hands that
 //               accumulator to the promotion warps
-//   warps 2-3   stage the block scales of the tile (sA: 128 rows, sB: 192 columns per block) in shared memory
-//   warps 4-19  promotion + epilogue: read an accumulator from tensor memory (each warp owns 32 rows x 48
+//   warps 2-3   stage the block scales of the tile (sA: 128 rows, sB: 160 columns per block) in shared memory
+//   warps 4-19  promotion + epilogue: read an accumulator from tensor memory (each warp owns 32 rows x 40
 //               columns), fold it into fp32 accumulators held in registers, release the accumulator; after
 //               the last block convert, add bias and store
-// Registers are moved from warps 0-3 to warps 4-19 with setmaxnreg (48 fp32 accumulators per thread); four
+// Registers are moved from warps 0-3 to warps 4-19 with setmaxnreg (40 fp32 accumulators per thread); four
 // promotion warps per scheduler cover each other's tensor-memory load latency.
 //
 // Seeded conversion (default): the promotion warps refill a drained accumulator with the bit pattern of
@@ -38,17 +39,18 @@ namespace {
 using namespace ptx;
 
 constexpr int kBM = 128;                 // tile rows
-constexpr int kBN = 192;                 // tile columns (48 per promotion warp: accumulators fit the register budget)
-constexpr int kAccStride = 256;          // tensor-memory columns between the two s32 accumulators
+constexpr int kBN = 160;                 // tile columns (40 per promotion warp: accumulators fit the register budget)
+constexpr int kAccBufs = 3;              // s32 accumulators in tensor memory (3 x 160 of the 512 columns)
+constexpr int kAccStride = kBN;          // tensor-memory columns between consecutive accumulators
 constexpr int kProbeN = 256;             // N of the issue-rate probe's MMAs
 constexpr int kBK = 128;                 // K bytes per stage (one 128-byte swizzle row)
-constexpr int kStages = 4;
+constexpr int kStages = 5;
 constexpr int kScaleStages = 4;
 constexpr int kEpiWarps = 16;             // 4 lane quarters x 4 column slices of 64
 constexpr int kThreadsTc = (4 + kEpiWarps) * 32;
 constexpr int kEpiCols = kBN / (kEpiWarps / 4);   // columns owned by one promotion warp
 constexpr uint32_t kABytes = kBM * kBK;  // 16 KiB
-constexpr uint32_t kBBytes = kBN * kBK;  // 24 KiB
+constexpr uint32_t kBBytes = kBN * kBK;  // 20 KiB
 constexpr uint32_t kSeedBits = 0x4B400000u;   // float 1.5 * 2^23
 constexpr float kSeedF = 12582912.0f;
 
@@ -84,9 +86,9 @@ struct Geo {
     static constexpr int SC_FLOATS = BPS * (kBM + kBN);         // scale floats per stage
     static constexpr uint32_t bar_off = Smem::scale_off + kScaleStages * SC_FLOATS * 4;
     // barrier slots (8 bytes each)
-    static constexpr int FULL_AB = 0, EMPTY_AB = kStages, ACC_FULL = 2 * kStages, ACC_EMPTY = 2 * kStages + 2,
-                         SC_FULL = 2 * kStages + 4, SC_EMPTY = 2 * kStages + 4 + kScaleStages,
-                         NBARS = 2 * kStages + 4 + 2 * kScaleStages;
+    static constexpr int FULL_AB = 0, EMPTY_AB = kStages, ACC_FULL = 2 * kStages, ACC_EMPTY = 2 * kStages + kAccBufs,
+                         SC_FULL = 2 * kStages + 2 * kAccBufs, SC_EMPTY = 2 * kStages + 2 * kAccBufs + kScaleStages,
+                         NBARS = 2 * kStages + 2 * kAccBufs + 2 * kScaleStages;
     static constexpr uint32_t misc_off = bar_off + NBARS * 8;   // tmem holder (4 B) + abort flag (4 B)
     static constexpr uint32_t total = misc_off + 16;
 };
@@ -127,7 +129,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             mbar_init(bar(G::FULL_AB + s), 1);
             mbar_init(bar(G::EMPTY_AB + s), 1);
         }
-        for (int b = 0; b < 2; ++b) {
+        for (int b = 0; b < kAccBufs; ++b) {
             mbar_init(bar(G::ACC_FULL + b), 1);
             mbar_init(bar(G::ACC_EMPTY + b), kEpiWarps);
         }
@@ -229,8 +231,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             tc_commit(bar(G::ACC_FULL + accbuf));
                         }
                         __syncwarp();
-                        accbuf ^= 1;
-                        if (accbuf == 0) accphase ^= 1u;
+                        if (++accbuf == kAccBufs) { accbuf = 0; accphase ^= 1u; }
                     }
                     if (!ok) break;
                     if (lane == 0) tc_commit(bar(G::EMPTY_AB + stage));
@@ -239,7 +240,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 }
             }
         } else {
-            // ---------------- scale loaders: warp 2 stages sA (128 rows per block), warp 3 sB (256 columns) ----------
+            // ---------------- scale loaders: warp 2 stages sA (128 rows per block), warp 3 sB (160 columns) ----------
             const bool is_a = (warp == 2);
             const float* src = is_a ? p.sA : p.sB;
             const int extent = is_a ? p.M : p.N;          // row length of the scale tensor
@@ -300,7 +301,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
         if (SEED) {
 #pragma unroll
-            for (int b = 0; b < 2; ++b)
+            for (int b = 0; b < kAccBufs; ++b)
 #pragma unroll
                 for (int c = 0; c < kEpiCols / 8; ++c) tmem_st8(t_lane + (uint32_t)(b * kAccStride + c * 8), seedv);
             tmem_wait_st();
@@ -308,8 +309,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         tc_fence_before();
         __syncwarp();
         if (lane == 0) {
-            mbar_arrive(bar(G::ACC_EMPTY + 0));
-            mbar_arrive(bar(G::ACC_EMPTY + 1));
+#pragma unroll
+            for (int b = 0; b < kAccBufs; ++b) mbar_arrive(bar(G::ACC_EMPTY + b));
         }
 
         int accbuf = 0, sstage = 0;
@@ -346,79 +347,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const uint32_t t_acc = t_lane + (uint32_t)(accbuf * kAccStride);
                     if (MODE == 1) {
 #pragma unroll
-                        for (int c = 0; c < kEpiCols / 16; ++c) {
-                            uint32_t pv[16];
-                            tmem_ld16(t_acc + (uint32_t)(c * 16), pv);
+                        for (int c = 0; c < kEpiCols / 8; ++c) {
+                            uint32_t pv[8];
+                            tmem_ld8(t_acc + (uint32_t)(c * 8), pv);
                             tmem_wait_ld();
-                            if (SEED) { tmem_st8(t_acc + (uint32_t)(c * 16), seedv); tmem_st8(t_acc + (uint32_t)(c * 16 + 8), seedv); }
+                            if (SEED) tmem_st8(t_acc + (uint32_t)(c * 8), seedv);
                             if (m < p.M) {
-                                int32_t* dst = p.partials + ((int64_t)j * p.M + m) * p.N + nbase + c * 16;
+                                int32_t* dst = p.partials + ((int64_t)j * p.M + m) * p.N + nbase + c * 8;
 #pragma unroll
-                                for (int i = 0; i < 16; ++i)
-                                    if (nbase + c * 16 + i < p.N)
+                                for (int i = 0; i < 8; ++i)
+                                    if (nbase + c * 8 + i < p.N)
                                         dst[i] = SEED ? (int32_t)(pv[i] - kSeedBits) : (int32_t)pv[i];
                             }
                         }
                         if (SEED) tmem_wait_st();
-                    } else if (MODE == 5 || MODE == 6 || MODE == 7) {   // (MODE 8 takes the production branch below)
-                        // timing experiments: 5 = packed FMAs without the scale loads, 6 = scalar FMAs with scale loads,
-                        // 7 = only the second FMA (no t computation)
-                        float sxd = __fmul_rn(sc[blk * (kBM + kBN) + row], div);
-                        sxd = __uint_as_float((__float_as_uint(sxd) + 2u) & 0xFFFFFFFCu);
-                        const float negc = -__fmul_rn(kSeedF, sxd);
-                        const uint64_t sxd2 = pack_f32x2(sxd, sxd), negc2 = pack_f32x2(negc, negc);
-                        const ulonglong2* swv =
-                            reinterpret_cast<const ulonglong2*>(sc + blk * (kBM + kBN) + kBM + slice * kEpiCols);
-                        const float4* swf = reinterpret_cast<const float4*>(swv);
-#pragma unroll
-                        for (int c = 0; c < kEpiCols / 16; ++c) {
-                            uint32_t cur[16];
-                            tmem_ld16(t_acc + (uint32_t)(c * 16), cur);
-                            tmem_wait_ld();
-                            tmem_st8(t_acc + (uint32_t)(c * 16), seedv);
-                            tmem_st8(t_acc + (uint32_t)(c * 16 + 8), seedv);
-#pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                if (MODE == 5) {
-                                    uint64_t t0 = fma_f32x2(pack_u32x2(cur[4 * q], cur[4 * q + 1]), sxd2, negc2);
-                                    uint64_t t1 = fma_f32x2(pack_u32x2(cur[4 * q + 2], cur[4 * q + 3]), sxd2, negc2);
-                                    acc2[c * 8 + q * 2] = fma_f32x2(sxd2, t0, acc2[c * 8 + q * 2]);
-                                    acc2[c * 8 + q * 2 + 1] = fma_f32x2(sxd2, t1, acc2[c * 8 + q * 2 + 1]);
-                                } else if (MODE == 7) {
-                                    const ulonglong2 w = swv[c * 4 + q];
-                                    acc2[c * 8 + q * 2] = fma_f32x2(w.x, pack_u32x2(cur[4 * q], cur[4 * q + 1]), acc2[c * 8 + q * 2]);
-                                    acc2[c * 8 + q * 2 + 1] = fma_f32x2(w.y, pack_u32x2(cur[4 * q + 2], cur[4 * q + 3]), acc2[c * 8 + q * 2 + 1]);
-                                } else {
-                                    const float4 w = swf[c * 4 + q];
-                                    float a0, a1, a2, a3;
-                                    unpack_f32x2(acc2[c * 8 + q * 2], a0, a1);
-                                    unpack_f32x2(acc2[c * 8 + q * 2 + 1], a2, a3);
-                                    a0 = __fmaf_rn(w.x, __fmaf_rn(__uint_as_float(cur[4 * q]), sxd, negc), a0);
-                                    a1 = __fmaf_rn(w.y, __fmaf_rn(__uint_as_float(cur[4 * q + 1]), sxd, negc), a1);
-                                    a2 = __fmaf_rn(w.z, __fmaf_rn(__uint_as_float(cur[4 * q + 2]), sxd, negc), a2);
-                                    a3 = __fmaf_rn(w.w, __fmaf_rn(__uint_as_float(cur[4 * q + 3]), sxd, negc), a3);
-                                    acc2[c * 8 + q * 2] = pack_f32x2(a0, a1);
-                                    acc2[c * 8 + q * 2 + 1] = pack_f32x2(a2, a3);
-                                }
-                            }
-                        }
-                        tmem_wait_st();
-                    } else if (MODE == 2) {
-                        // timing experiment: hand the accumulator straight back
-                    } else if (MODE == 3 || MODE == 4) {
-                        // timing experiment: tensor-memory traffic only
-#pragma unroll
-                        for (int c = 0; c < kEpiCols / 16; ++c) {
-                            uint32_t cur[16];
-                            tmem_ld16(t_acc + (uint32_t)(c * 16), cur);
-                            tmem_wait_ld();
-                            if (MODE == 4) {
-                                tmem_st8(t_acc + (uint32_t)(c * 16), seedv);
-                                tmem_st8(t_acc + (uint32_t)(c * 16 + 8), seedv);
-                            }
-                            acc2[c] ^= pack_u32x2(cur[0], cur[15]);
-                        }
-                        if (MODE == 4) tmem_wait_st();
                     } else {
                         float sxd = __fmul_rn(lds_f32(sc_u32 + (uint32_t)((blk * (kBM + kBN) + row) * 4)), div);
                         float negc = 0.0f;
@@ -428,22 +370,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         }
                         const uint64_t sxd2 = pack_f32x2(sxd, sxd), negc2 = pack_f32x2(negc, negc);
                         const uint32_t sw_u32 = sc_u32 + (uint32_t)((blk * (kBM + kBN) + kBM + slice * kEpiCols) * 4);
-                        // 16 columns per step: one load, two 8-column re-seed stores (8 resident seed registers),
-                        // four 16-byte scale loads, sixteen packed FMAs.  The four promotion warps of a scheduler
-                        // cover each other's tensor-memory latency (about 20-35 cycles per load).
+                        // 8 columns per step: one load, one re-seed store (8 resident seed registers), two 16-byte scale
+                        // loads, eight packed FMAs; the next load is issued before the current chunk is folded.
+                        uint32_t pa[8], pb[8];
+                        tmem_ld8(t_acc, pa);
 #pragma unroll
-                        for (int c = 0; c < kEpiCols / 16; ++c) {
-                            uint32_t cur[16];
-                            tmem_ld16(t_acc + (uint32_t)(c * 16), cur);
+                        for (int c = 0; c < kEpiCols / 8; ++c) {
+                            uint32_t(&cur)[8] = (c & 1) ? pb : pa;
+                            uint32_t(&nxt)[8] = (c & 1) ? pa : pb;
                             tmem_wait_ld();
-                            if (SEED) {
-                                tmem_st8(t_acc + (uint32_t)(c * 16), seedv);
-                                tmem_st8(t_acc + (uint32_t)(c * 16 + 8), seedv);
-                            }
+                            if (c + 1 < kEpiCols / 8) tmem_ld8(t_acc + (uint32_t)((c + 1) * 8), nxt);
+                            if (SEED) tmem_st8(t_acc + (uint32_t)(c * 8), seedv);
 #pragma unroll
-                            for (int q = 0; q < 4; ++q) {
+                            for (int q = 0; q < 2; ++q) {
                                 uint64_t w0, w1;
-                                lds_2xb64(sw_u32 + (uint32_t)((c * 4 + q) * 16), w0, w1);
+                                lds_2xb64(sw_u32 + (uint32_t)((c * 2 + q) * 16), w0, w1);
                                 uint64_t t0, t1;
                                 if (SEED) {
                                     t0 = fma_f32x2(pack_u32x2(cur[4 * q], cur[4 * q + 1]), sxd2, negc2);
@@ -452,8 +393,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                     t0 = fma_f32x2(pack_f32x2((float)(int32_t)cur[4 * q], (float)(int32_t)cur[4 * q + 1]), sxd2, 0ull);
                                     t1 = fma_f32x2(pack_f32x2((float)(int32_t)cur[4 * q + 2], (float)(int32_t)cur[4 * q + 3]), sxd2, 0ull);
                                 }
-                                acc2[c * 8 + q * 2] = fma_f32x2(w0, t0, acc2[c * 8 + q * 2]);
-                                acc2[c * 8 + q * 2 + 1] = fma_f32x2(w1, t1, acc2[c * 8 + q * 2 + 1]);
+                                acc2[c * 4 + q * 2] = fma_f32x2(w0, t0, acc2[c * 4 + q * 2]);
+                                acc2[c * 4 + q * 2 + 1] = fma_f32x2(w1, t1, acc2[c * 4 + q * 2 + 1]);
                             }
                         }
                         if (SEED) tmem_wait_st();
@@ -461,8 +402,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar(G::ACC_EMPTY + accbuf));
-                    accbuf ^= 1;
-                    if (accbuf == 0) accphase ^= 1u;
+                    if (++accbuf == kAccBufs) { accbuf = 0; accphase ^= 1u; }
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(G::SC_EMPTY + sstage));
@@ -470,13 +410,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             if (!ok) break;
 
-            if (MODE >= 2) {
-                // timing experiments: keep the accumulators observable without storing the tile
-                uint64_t x = 0;
-#pragma unroll
-                for (int i = 0; i < kEpiCols / 2; ++i) x ^= acc2[i];
-                if (x == 0x123456789abcull) p.status[1] = 1;
-            }
             if (MODE == 0 && m < p.M) {
                 float acc[kEpiCols];
 #pragma unroll
@@ -661,14 +594,7 @@ int launch_one(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, 
 
 template <int QB>
 int launch_qb(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int grid, bool partials, bool seed,
-              cudaStream_t st, int experiment = 0) {
-    if (QB == 64 && experiment == 2) return launch_one<64, 2, true>(ma, mb, p, grid, st);
-    if (QB == 64 && experiment == 3) return launch_one<64, 3, true>(ma, mb, p, grid, st);
-    if (QB == 64 && experiment == 4) return launch_one<64, 4, true>(ma, mb, p, grid, st);
-    if (QB == 64 && experiment == 5) return launch_one<64, 5, true>(ma, mb, p, grid, st);
-    if (QB == 64 && experiment == 6) return launch_one<64, 6, true>(ma, mb, p, grid, st);
-    if (QB == 64 && experiment == 7) return launch_one<64, 7, true>(ma, mb, p, grid, st);
-    if (QB == 64 && experiment == 1) return launch_one<64, 8, true>(ma, mb, p, grid, st);
+              cudaStream_t st) {
     if (partials) return seed ? launch_one<QB, 1, true>(ma, mb, p, grid, st) : launch_one<QB, 1, false>(ma, mb, p, grid, st);
     return seed ? launch_one<QB, 0, true>(ma, mb, p, grid, st) : launch_one<QB, 0, false>(ma, mb, p, grid, st);
 }
@@ -724,7 +650,7 @@ int launch_gemm_tc(const GemmArgs& g, cudaStream_t st) {
     const bool seed = (g.flags & BI8_GEMM_NO_SEED) == 0;
     switch (g.block) {
         case 32: return launch_qb<32>(ma, mb, p, grid, partials, seed, st);
-        case 64: return launch_qb<64>(ma, mb, p, grid, partials, seed, st, (g.flags >> 8) & 7);
+        case 64: return launch_qb<64>(ma, mb, p, grid, partials, seed, st);
         case 128: return launch_qb<128>(ma, mb, p, grid, partials, seed, st);
     }
     return fail(BI8_ERR_BLOCK, "tensor-core GEMM supports block 32, 64, 128 (got %d)", g.block);

@@ -59,11 +59,26 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity, uint32_t
     return ok != 0;
 }
 
-// Bounded wait on an mbarrier phase.  After every failed (suspended) poll the thread looks at the CTA's abort
-// flag (a word in shared memory, given by its shared address, raised by whichever thread gives up first) and at the SM cycle
-// counter; it gives up after `limit_cycles` (default 4e9, about two seconds) and returns false.
+// Non-blocking poll of an mbarrier phase.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait on an mbarrier phase.  Fast path: one non-blocking poll.  Otherwise suspended polls; after
+// every failed one the thread looks at the CTA's abort flag (a word in shared memory, given by its shared
+// address, raised by whichever thread gives up first) and at the SM cycle counter; it gives up after
+// `limit_cycles` (default 4e9, about two seconds) and returns false.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t abort_flag_smem,
                                           long long limit_cycles = 4000000000ll) {
+    if (mbar_test(bar, parity)) return true;
     if (mbar_try(bar, parity)) return true;
     const long long t0 = clock64();
     while (true) {
@@ -71,6 +86,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
         if (lds_volatile_u32(abort_flag_smem) != 0u) return false;
         if (clock64() - t0 > limit_cycles) return false;
     }
+}
+
+// The same for a whole converged warp: every lane polls; the result is made uniform with one vote, so that
+// a warp-aligned instruction after the wait is never reached by only some of the lanes.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, uint32_t abort_flag_smem) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag_smem));
 }
 
 // Asynchronous 16-byte / 4-byte copies global -> shared (no registers, no waiting in the issuing thread).

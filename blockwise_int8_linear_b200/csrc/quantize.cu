@@ -7,9 +7,10 @@
 //   colwise     block_linear.py:93-94,100-103 transpose copy followed by the row-wise quantizer
 //
 // Data movement: every warp instruction of the vector kernels reads or writes one contiguous run of a
-// row (32-byte or 16-byte per lane), the block absmax is an xor-shuffle reduction inside the lanes that
-// share a block, and the transposed scale tensor [K/block, rows] is staged through shared memory so that
-// its stores (and, for dequantize, its loads) are contiguous along the row index.
+// row (32-byte or 16-byte per lane) and the block absmax is an xor-shuffle reduction inside the lanes that
+// share a block.  The transposed scale tensor [K/block, rows] is written in 16-byte pieces (four rows of one
+// block) by the streaming quantizer, and staged through shared memory by the tile kernels so that its
+// stores (and, for dequantize, its loads) are contiguous along the row index.
 #include "bi8_common.cuh"
 
 #include <cstdlib>
@@ -164,6 +165,155 @@ __global__ void __launch_bounds__(kThreads) quantize_rowwise_vec_kernel(
         const int j = t / kTileRows, r = t % kTileRows;
         const int jb = ct * BPT + j, row = rt * kTileRows + r;
         if (jb < nb && row < M) s[(int64_t)jb * M + row] = s_scale[j][r];
+    }
+}
+
+// Packed fp32 pairs (add/mul/fma.rn.f32x2): one instruction for two lanes of data, each lane rounded exactly
+// like the scalar instruction.
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void f2_unpack_bits(uint64_t v, uint32_t& lo, uint32_t& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
+// Row-wise quantize, streaming path (16-bit inputs, K % 16 == 0, 32-byte aligned rows).
+// Persistent warps: a warp owns units of 4 rows x 512 columns (lane = 16 consecutive elements of a row, one
+// 32-byte load and one 16-byte store per row) and keeps the loads of its NEXT unit in flight while it quantizes
+// the current one, so the memory system always has 128 bytes per lane outstanding.  No shared memory and no CTA
+// barrier: the lane that leads a block keeps the four row scales of its block and writes them as one 16-byte
+// piece of the transposed scale tensor (s[j, m0..m0+3]).  The arithmetic is done on packed fp32 pairs.
+template <typename T, int B>
+__global__ void __launch_bounds__(kThreads, 2) quantize_rowwise_stream_kernel(
+    const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ q, float* __restrict__ s, int M, int K, int nb,
+    int col_units, int64_t total_units) {
+    constexpr int LPB = B / 16;             // lanes sharing one block
+    const int lane = threadIdx.x & 31;
+    const int64_t gw = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+    const int64_t nw = (int64_t)gridDim.x * (kThreads / 32);
+    // fl(127*y) and the round-to-integer step must stay two separately rounded operations.  A packed multiply
+    // followed by a packed ADD was observed to come out as one fused operation (ties then round differently from
+    // the reference's two-step evaluation), so the second step is written as fma(z, 1, magic): the product z*1 is
+    // exact, the result is the single rounding of z + magic, and there is no multiply left to contract into it.
+    const uint64_t c127 = f2_pack(127.0f, 127.0f), cmagic = f2_pack(kMagic, kMagic), cone = f2_pack(1.0f, 1.0f);
+    auto round_pair = [&](uint64_t y2, uint32_t& b0, uint32_t& b1) {
+        const uint64_t z = f2_mul(c127, y2);
+        f2_unpack_bits(f2_fma(z, cone, cmagic), b0, b1);
+    };
+
+    auto load_unit = [&](int64_t u, uint32_t (&buf)[4][8]) {
+        const int rg = (int)(u / col_units), ct = (int)(u % col_units);
+        const int col = ct * 512 + lane * 16;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int row = rg * 4 + i;
+            if (col < K && row < M) {
+                ld_nc_v8(x + (int64_t)row * ldx + col, buf[i]);
+            } else {
+#pragma unroll
+                for (int w = 0; w < 8; ++w) buf[i][w] = 0u;
+            }
+        }
+    };
+    auto process_unit = [&](int64_t u, const uint32_t (&buf)[4][8]) {
+        const int rg = (int)(u / col_units), ct = (int)(u % col_units);
+        const int col = ct * 512 + lane * 16;
+        float sc[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int row = rg * 4 + i;
+            uint64_t v2[8];
+            float amax = 0.0f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) {
+                float lo, hi;
+                unpack2<T>(buf[i][w], lo, hi);
+                amax = fmaxf(amax, fmaxf(fabsf(lo), fabsf(hi)));
+                v2[w] = f2_pack(lo, hi);
+            }
+#pragma unroll
+            for (int off = 1; off < LPB; off <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+            sc[i] = amax;
+            BlockQ bq;
+            bq.set(amax, true);
+            uint32_t out[4];
+            if (bq.fast) {
+                const uint64_t r2 = f2_pack(bq.rcp, bq.rcp), ns2 = f2_pack(-amax, -amax);
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    uint32_t b0, b1, b2, b3;
+                    {
+                        const uint64_t q0 = f2_mul(v2[2 * w], r2);
+                        const uint64_t e = f2_fma(ns2, q0, v2[2 * w]);
+                        const uint64_t y = f2_fma(e, r2, q0);
+                        round_pair(y, b0, b1);
+                    }
+                    {
+                        const uint64_t q0 = f2_mul(v2[2 * w + 1], r2);
+                        const uint64_t e = f2_fma(ns2, q0, v2[2 * w + 1]);
+                        const uint64_t y = f2_fma(e, r2, q0);
+                        round_pair(y, b2, b3);
+                    }
+                    out[w] = pack4(b0, b1, b2, b3);
+                }
+            } else {
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    uint32_t a0, a1, a2, a3;
+                    f2_unpack_bits(v2[2 * w], a0, a1);
+                    f2_unpack_bits(v2[2 * w + 1], a2, a3);
+                    out[w] = pack4(bq.q(__uint_as_float(a0)), bq.q(__uint_as_float(a1)), bq.q(__uint_as_float(a2)),
+                                   bq.q(__uint_as_float(a3)));
+                }
+            }
+            if (col < K && row < M)
+                *reinterpret_cast<uint4*>(q + (int64_t)row * K + col) = make_uint4(out[0], out[1], out[2], out[3]);
+        }
+        if ((lane % LPB) == 0) {
+            const int jb = (col / B);
+            const int m0 = rg * 4;
+            if (jb < nb && m0 < M) {
+                float* dst = s + (int64_t)jb * M + m0;
+                if (((M & 3) == 0)) {
+                    *reinterpret_cast<float4*>(dst) = make_float4(sc[0], sc[1], sc[2], sc[3]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (m0 + i < M) dst[i] = sc[i];
+                }
+            }
+        }
+    };
+
+    uint32_t bufa[4][8], bufb[4][8];
+    int64_t u = gw;
+    if (u < total_units) load_unit(u, bufa);
+    while (u < total_units) {
+        const int64_t u1 = u + nw;
+        if (u1 < total_units) load_unit(u1, bufb);
+        process_unit(u, bufa);
+        if (u1 >= total_units) break;
+        const int64_t u2 = u1 + nw;
+        if (u2 < total_units) load_unit(u2, bufa);
+        process_unit(u1, bufb);
+        u = u2;
     }
 }
 
@@ -379,6 +529,25 @@ int quantize_rowwise_t(const T* x, int64_t ldx, int8_t* q, float* s, int64_t M, 
         return BI8_OK;                                                                                     \
     } while (0)
     if constexpr (sizeof(T) == 2) {
+        if (v16 && aligned(s, 16) && (block == 32 || block == 64 || block == 128 || block == 256)) {
+            int dev = 0, sms = 0;
+            BI8_CUDA_TRY(cudaGetDevice(&dev));
+            BI8_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+            const int col_units = (int)((K + 511) / 512);
+            const int64_t total = ((M + 3) / 4) * col_units;
+            const int64_t warps_wanted = total;                      // one unit per warp at least
+            int64_t ctas = (warps_wanted + kThreads / 32 - 1) / (kThreads / 32);
+            if (ctas > 2ll * sms) ctas = 2ll * sms;                  // two resident CTAs per SM, persistent beyond that
+#define BI8_QSTREAM(BB)                                                                                          \
+    if (block == BB) {                                                                                           \
+        quantize_rowwise_stream_kernel<T, BB><<<(unsigned)ctas, kThreads, 0, st>>>(x, ldx, q, s, (int)M, (int)K,  \
+                                                                                   (int)nb, col_units, total);   \
+        BI8_CUDA_TRY(cudaGetLastError());                                                                        \
+        return BI8_OK;                                                                                           \
+    }
+            BI8_QSTREAM(32) BI8_QSTREAM(64) BI8_QSTREAM(128) BI8_QSTREAM(256)
+#undef BI8_QSTREAM
+        }
         if (v16) {
             if (block == 32) BI8_QROW(32, 16);
             if (block == 64) BI8_QROW(64, 16);

@@ -138,14 +138,20 @@ int bi8_dequantize_rowwise(const int8_t* q, const float* s, void* out, int out_d
     return launch_dequantize_rowwise(q, s, out, out_dtype, M, K, block, static_cast<cudaStream_t>(stream));
 }
 
-size_t bi8_gemm_workspace_bytes(int64_t, int64_t, int64_t, int) { return 0; }
+size_t bi8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int block) {
+    if (M <= 0 || N <= 0 || K <= 0 || (block != 32 && block != 64 && block != 128)) return 0;
+    GemmArgs g{};
+    g.M = M;
+    g.N = N;
+    g.K = K;
+    g.block = block;
+    return gemm_tc_workspace_bytes(g);
+}
 
 int bi8_gemm_dequant(const int8_t* A, int64_t lda, const int8_t* Bt, int64_t ldb, const float* sA, const float* sB,
                      const void* bias, int bias_dtype, void* C, int64_t ldc, int out_dtype, int64_t M, int64_t N, int64_t K,
                      int block, void* workspace, size_t workspace_bytes, int flags, void* stream) {
-    (void)workspace;
-    (void)workspace_bytes;
-    GemmArgs g{A, lda, Bt, ldb, sA, sB, bias, bias_dtype, C, ldc, out_dtype, nullptr, M, N, K, block, flags};
+    GemmArgs g{A, lda, Bt, ldb, sA, sB, bias, bias_dtype, C, ldc, out_dtype, nullptr, M, N, K, block, flags, workspace, workspace_bytes};
     int rc = check_gemm(g, false);
     if (rc != BI8_OK || M == 0 || N == 0) return rc;
     return dispatch_gemm(g, static_cast<cudaStream_t>(stream));
@@ -153,7 +159,7 @@ int bi8_gemm_dequant(const int8_t* A, int64_t lda, const int8_t* Bt, int64_t ldb
 
 int bi8_gemm_block_partials(const int8_t* A, int64_t lda, const int8_t* Bt, int64_t ldb, int32_t* P, int64_t M, int64_t N,
                             int64_t K, int block, int flags, void* stream) {
-    GemmArgs g{A, lda, Bt, ldb, nullptr, nullptr, nullptr, 0, nullptr, N, BI8_F32, P, M, N, K, block, flags};
+    GemmArgs g{A, lda, Bt, ldb, nullptr, nullptr, nullptr, 0, nullptr, N, BI8_F32, P, M, N, K, block, flags, nullptr, 0};
     int rc = check_gemm(g, true);
     if (rc != BI8_OK || M == 0 || N == 0 || K == 0) return rc;
     return dispatch_gemm(g, static_cast<cudaStream_t>(stream));

@@ -48,8 +48,11 @@ struct GemmArgs {
     int64_t M, N, K;
     int block;
     int flags;
+    void* workspace;          // optional scratch of gemm_tc_workspace_bytes() bytes (split-K partial results)
+    size_t workspace_bytes;
 };
 bool gemm_tc_applicable(const GemmArgs& g, const char** why);
+size_t gemm_tc_workspace_bytes(const GemmArgs& g);
 int launch_gemm_tc(const GemmArgs& g, cudaStream_t st);
 int launch_gemm_generic(const GemmArgs& g, cudaStream_t st);
 int run_mma_peak_probe(int iters, float* ms, int* sm_count);

@@ -70,6 +70,9 @@ struct TcParams {
     int out_dtype, bias_dtype;
     int vec_store;      // C base and row pitch allow 16-byte stores
     int vec_scales;     // sA, sB and their row lengths allow 16-byte loads
+    int ksplit;         // > 1: the K stages are divided over ksplit work items per tile (split-K)
+    int stages_per_split;
+    float* ws;          // split-K: fp32 partial results [ksplit, M, N]
 };
 
 struct Smem {
@@ -98,6 +101,17 @@ __device__ __forceinline__ void report_timeout(int* status, uint32_t abort_flag,
     if (atomicCAS(status, 0, BI8_ERR_TIMEOUT) == 0) status[1] = code;
 }
 
+// Work item -> tile and K-stage range.  Items of one split are consecutive, so CTAs that run together work on
+// different tiles of the same K range.
+__device__ __forceinline__ void item_range(int item, int num_tiles, int nks, int stages_per_split, int& tile, int& split,
+                                           int& ks0, int& ks1) {
+    tile = item % num_tiles;
+    split = item / num_tiles;
+    ks0 = split * stages_per_split;
+    ks1 = ks0 + stages_per_split;
+    if (ks1 > nks) ks1 = nks;
+}
+
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int& m0, int& n0) {
     // consecutive tiles (CTAs that run together) share a column panel of Bt and sweep the rows of A
     m0 = (tile % tiles_m) * kBM;
@@ -123,6 +137,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_tiles = p.tiles_m * p.tiles_n;
     const int nks = (p.K + kBK - 1) / kBK;
+    const int num_items = num_tiles * p.ksplit;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -166,10 +181,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
             for (int s = 0; s < kStages; ++s) last_parity[s] = -1;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                int m0, n0;
+            for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+                int tile, split, ks0, ks1, m0, n0;
+                item_range(item, num_tiles, nks, p.stages_per_split, tile, split, ks0, ks1);
                 tile_coords(tile, p.tiles_m, m0, n0);
-                for (int ks = 0; ks < nks; ++ks) {
+                for (int ks = ks0; ks < ks1; ++ks) {
                     ok = __all_sync(0xffffffffu, mbar_wait(bar(G::EMPTY_AB + stage), phase ^ 1u, abort_flag));
                     if (!ok) {
                         if (lane == 0) report_timeout(p.status, abort_flag, W_EMPTY_AB);
@@ -202,8 +218,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             int stage = 0, accbuf = 0;
             uint32_t phase = 0, accphase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                for (int ks = 0; ks < nks && ok; ++ks) {
+            for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+                int tile, split, ks0, ks1;
+                item_range(item, num_tiles, nks, p.stages_per_split, tile, split, ks0, ks1);
+                for (int ks = ks0; ks < ks1 && ok; ++ks) {
                     ok = __all_sync(0xffffffffu, mbar_wait(bar(G::FULL_AB + stage), phase, abort_flag));
                     if (!ok) {
                         if (lane == 0) report_timeout(p.status, abort_flag, W_FULL_AB);
@@ -249,11 +267,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             int sstage = 0;
             uint32_t sphase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                int m0, n0;
+            for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+                int tile, split, ks0, ks1, m0, n0;
+                item_range(item, num_tiles, nks, p.stages_per_split, tile, split, ks0, ks1);
                 tile_coords(tile, p.tiles_m, m0, n0);
                 const int x0 = is_a ? m0 : n0;
-                for (int ks = 0; ks < nks; ++ks) {
+                for (int ks = ks0; ks < ks1; ++ks) {
                     ok = __all_sync(0xffffffffu, mbar_wait(bar(G::SC_EMPTY + sstage), sphase ^ 1u, abort_flag));
                     if (!ok) {
                         if (lane == 0) report_timeout(p.status, abort_flag, W_SC_EMPTY);
@@ -316,17 +335,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         int accbuf = 0, sstage = 0;
         uint32_t accphase = 0, sphase = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-            int m0, n0;
+        for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+            int tile, split, ks0, ks1, m0, n0;
+            item_range(item, num_tiles, nks, p.stages_per_split, tile, split, ks0, ks1);
             tile_coords(tile, p.tiles_m, m0, n0);
             const int m = m0 + row;
+            const bool warp_live = (m0 + quarter * 32) < p.M;      // small M: most warps own no valid row
             const int nbase = n0 + slice * kEpiCols;
             // kEpiCols fp32 accumulators per thread, kept as packed pairs for fma.rn.f32x2
             uint64_t acc2[kEpiCols / 2];
 #pragma unroll
             for (int i = 0; i < kEpiCols / 2; ++i) acc2[i] = 0ull;
 
-            for (int ks = 0; ks < nks && ok; ++ks) {
+            for (int ks = ks0; ks < ks1 && ok; ++ks) {
                 ok = __all_sync(0xffffffffu, mbar_wait(bar(G::SC_FULL + sstage), sphase, abort_flag));
                 if (!ok) {
                     if (lane == 0) report_timeout(p.status, abort_flag, W_SC_FULL);
@@ -345,7 +366,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     }
                     tc_fence_after();
                     const uint32_t t_acc = t_lane + (uint32_t)(accbuf * kAccStride);
-                    if (MODE == 1) {
+                    if (!warp_live) {
+                        // all 32 rows of this warp lie beyond M: nothing to fold, and what the MMAs leave in these
+                        // tensor-memory lanes is never read
+                    } else if (MODE == 1) {
 #pragma unroll
                         for (int c = 0; c < kEpiCols / 8; ++c) {
                             uint32_t pv[8];
@@ -414,6 +438,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 float acc[kEpiCols];
 #pragma unroll
                 for (int i = 0; i < kEpiCols / 2; ++i) unpack_f32x2(acc2[i], acc[2 * i], acc[2 * i + 1]);
+                if (p.ksplit > 1) {
+                    // split-K: raw fp32 partial result of this K range; cast and bias happen in the reduction
+                    float* wrow = p.ws + ((int64_t)split * p.M + m) * p.N;
+#pragma unroll
+                    for (int g = 0; g < kEpiCols / 4; ++g) {
+                        const int n = nbase + g * 4;
+                        if ((p.N & 3) == 0 && n + 4 <= p.N) {
+                            *reinterpret_cast<float4*>(wrow + n) = make_float4(acc[g * 4], acc[g * 4 + 1], acc[g * 4 + 2], acc[g * 4 + 3]);
+                        } else {
+#pragma unroll
+                            for (int u = 0; u < 4; ++u)
+                                if (n + u < p.N) wrow[n + u] = acc[g * 4 + u];
+                        }
+                    }
+                    continue;
+                }
                 const bool has_bias = p.bias != nullptr;
                 auto bias_at = [&](int n) -> float {
                     if (p.bias_dtype == BI8_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n]);
@@ -485,6 +525,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (warp == 2) {
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// Split-K reduction: C[m,n] = cast(sum_s ws[s,m,n]) (+ cast(bias[n]) in the output type).  The splits are added in
+// ascending order, so the result does not depend on scheduling.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ ws, int ksplit, const void* __restrict__ bias,
+                                                            int bias_dtype, void* __restrict__ C, int64_t ldc, int out_dtype,
+                                                            int M, int N) {
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= (int64_t)M * N) return;
+    const int m = (int)(i / N), n = (int)(i % N);
+    float acc = 0.0f;
+    for (int s = 0; s < ksplit; ++s) acc = __fadd_rn(acc, ws[((int64_t)s * M + m) * N + n]);
+    float bv = 0.0f;
+    const bool hb = bias != nullptr;
+    if (hb) {
+        if (bias_dtype == BI8_BF16) bv = __bfloat162float(static_cast<const __nv_bfloat16*>(bias)[n]);
+        else if (bias_dtype == BI8_F16) bv = __half2float(static_cast<const __half*>(bias)[n]);
+        else bv = static_cast<const float*>(bias)[n];
+    }
+    if (out_dtype == BI8_F32) {
+        static_cast<float*>(C)[(int64_t)m * ldc + n] = hb ? __fadd_rn(acc, bv) : acc;
+    } else if (out_dtype == BI8_BF16) {
+        __nv_bfloat16 c = __float2bfloat16_rn(acc);
+        if (hb) c = __float2bfloat16_rn(__fadd_rn(__bfloat162float(c), __bfloat162float(__float2bfloat16_rn(bv))));
+        static_cast<__nv_bfloat16*>(C)[(int64_t)m * ldc + n] = c;
+    } else {
+        __half c = __float2half_rn(acc);
+        if (hb) c = __float2half_rn(__fadd_rn(__half2float(c), __half2float(__float2half_rn(bv))));
+        static_cast<__half*>(C)[(int64_t)m * ldc + n] = c;
     }
 }
 
@@ -601,6 +671,40 @@ int launch_qb(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, i
 
 }  // namespace
 
+// Split-K plan: when the output has fewer tiles than the device has SMs (small M), the K stages of every tile are
+// divided over `ksplit` work items so that all SMs stream weights; partial results go to an fp32 workspace
+// [ksplit, M, N] and a second kernel adds them in a fixed order.
+namespace {
+struct SplitPlan {
+    int ksplit = 1;
+    int stages_per_split = 0;
+    size_t bytes = 0;
+};
+SplitPlan plan_split(int64_t M, int64_t N, int64_t K, int sms) {
+    SplitPlan pl;
+    const int64_t tiles = ((M + kBM - 1) / kBM) * ((N + kBN - 1) / kBN);
+    const int nks = (int)((K + kBK - 1) / kBK);
+    pl.stages_per_split = nks;
+    if (tiles <= 0 || nks <= 1 || tiles * 2 > sms) return pl;
+    int s = (int)(sms / tiles);
+    if (s > nks) s = nks;
+    if (s > 32) s = 32;
+    while (s > 1 && (size_t)s * (size_t)M * (size_t)N * 4 > (size_t)256 << 20) --s;
+    if (s <= 1) return pl;
+    const int spp = (nks + s - 1) / s;
+    pl.ksplit = (nks + spp - 1) / spp;
+    pl.stages_per_split = spp;
+    pl.bytes = pl.ksplit > 1 ? (size_t)pl.ksplit * (size_t)M * (size_t)N * 4 : 0;
+    return pl;
+}
+}  // namespace
+
+size_t gemm_tc_workspace_bytes(const GemmArgs& g) {
+    const DeviceInfo di = device_info();
+    if (!di.ok || g.partials != nullptr) return 0;
+    return plan_split(g.M, g.N, g.K, di.sms).bytes;
+}
+
 bool gemm_tc_applicable(const GemmArgs& g, const char** why) {
     auto no = [&](const char* w) {
         if (why) *why = w;
@@ -644,16 +748,33 @@ int launch_gemm_tc(const GemmArgs& g, cudaStream_t st) {
     p.vec_store = (g.C != nullptr && aligned(g.C, 16) && (g.ldc * esz) % 16 == 0) ? 1 : 0;
     p.vec_scales = (g.partials == nullptr && aligned(g.sA, 16) && aligned(g.sB, 16) && g.M % 4 == 0 && g.N % 4 == 0) ? 1 : 0;
     const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
-    if (tiles >= (1ll << 31)) return fail(BI8_ERR_SHAPE, "too many output tiles");
-    const int grid = (int)(tiles < di.sms ? tiles : di.sms);
+    if (tiles >= (1ll << 31) / 32) return fail(BI8_ERR_SHAPE, "too many output tiles");
     const bool partials = g.partials != nullptr;
+    SplitPlan pl;
+    pl.stages_per_split = (int)((g.K + kBK - 1) / kBK);
+    if (!partials) {
+        const SplitPlan want = plan_split(g.M, g.N, g.K, di.sms);
+        // without a large enough, 16-byte aligned workspace the GEMM simply runs unsplit
+        if (want.ksplit > 1 && g.workspace != nullptr && g.workspace_bytes >= want.bytes && aligned(g.workspace, 16)) pl = want;
+    }
+    p.ksplit = pl.ksplit;
+    p.stages_per_split = pl.stages_per_split;
+    p.ws = static_cast<float*>(g.workspace);
+    const int64_t items = tiles * pl.ksplit;
+    const int grid = (int)(items < di.sms ? items : di.sms);
     const bool seed = (g.flags & BI8_GEMM_NO_SEED) == 0;
     switch (g.block) {
-        case 32: return launch_qb<32>(ma, mb, p, grid, partials, seed, st);
-        case 64: return launch_qb<64>(ma, mb, p, grid, partials, seed, st);
-        case 128: return launch_qb<128>(ma, mb, p, grid, partials, seed, st);
+        case 32: rc = launch_qb<32>(ma, mb, p, grid, partials, seed, st); break;
+        case 64: rc = launch_qb<64>(ma, mb, p, grid, partials, seed, st); break;
+        case 128: rc = launch_qb<128>(ma, mb, p, grid, partials, seed, st); break;
+        default: return fail(BI8_ERR_BLOCK, "tensor-core GEMM supports block 32, 64, 128 (got %d)", g.block);
     }
-    return fail(BI8_ERR_BLOCK, "tensor-core GEMM supports block 32, 64, 128 (got %d)", g.block);
+    if (rc != BI8_OK || pl.ksplit == 1) return rc;
+    const int64_t total = g.M * g.N;
+    splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(p.ws, pl.ksplit, g.bias, g.bias_dtype, g.C, g.ldc,
+                                                                          g.out_dtype, (int)g.M, (int)g.N);
+    BI8_CUDA_TRY(cudaGetLastError());
+    return BI8_OK;
 }
 
 int run_mma_peak_probe(int iters, float* ms, int* sm_count) {

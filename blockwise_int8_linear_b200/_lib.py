@@ -22,7 +22,7 @@ _DTYPE_CODE = {torch.bfloat16: BI8_BF16, torch.float32: BI8_F32, torch.float16: 
 EXPORTS = [
     "bi8_version", "bi8_last_error_string", "bi8_device_status", "bi8_quantize_rowwise", "bi8_quantize_colwise",
     "bi8_dequantize_rowwise", "bi8_gemm_dequant", "bi8_gemm_workspace_bytes", "bi8_gemm_block_partials",
-    "bi8_linear_forward", "bi8_mma_peak_probe",
+    "bi8_linear_forward", "bi8_mma_peak_probe", "bi8_gemm_dequant_static", "bi8_gemm_static_scratch_bytes",
 ]
 
 _lib = None
@@ -57,7 +57,7 @@ def lib() -> ctypes.CDLL:
         L.bi8_mma_peak_probe.argtypes = [i32, c.POINTER(c.c_float), c.POINTER(i32)]
         for name in EXPORTS:
             fn = getattr(L, name)
-            if name not in ("bi8_last_error_string", "bi8_gemm_workspace_bytes"):
+            if name not in ("bi8_last_error_string", "bi8_gemm_workspace_bytes", "bi8_gemm_static_scratch_bytes"):
                 fn.restype = i32
         _lib = L
     return _lib

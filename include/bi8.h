@@ -102,6 +102,21 @@ BI8_API int bi8_gemm_dequant(const int8_t* A, int64_t lda, const int8_t* Bt, int
 
 BI8_API size_t bi8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int block);
 
+/* bi8_gemm_dequant for callers that cannot provide a workspace because they cannot allocate device memory when
+ * they call: a serving loop that must not touch cudaMalloc after start-up, a plugin whose host runtime owns the
+ * allocator, a caller with a fixed memory footprint.  (No counterpart in the reference, whose wrappers allocate
+ * with torch on every call.)  The split-K scratch comes from a fixed 8 MiB array inside the library (reported by
+ * bi8_gemm_static_scratch_bytes; every GPU that loads the library holds it until exit); a shape whose plan needs
+ * more returns BI8_ERR_LIMIT.  No cudaMalloc/cudaFree or allocating library call is made.  The first call on a
+ * device looks up the array's device address: make it outside any stream capture.  All calls share the array
+ * (nothing needs clearing between calls); calls that can overlap on one GPU race on it and must be serialised by
+ * the caller.  Arguments and results are those of bi8_gemm_dequant. */
+BI8_API int bi8_gemm_dequant_static(const int8_t* A, int64_t lda, const int8_t* Bt, int64_t ldb,
+                            const float* sA, const float* sB, const void* bias, int bias_dtype,
+                            void* C, int64_t ldc, int out_dtype, int64_t M, int64_t N, int64_t K, int block,
+                            int flags, void* stream);
+BI8_API size_t bi8_gemm_static_scratch_bytes(void);
+
 /* Diagnostic twin of bi8_gemm_dequant (same loads and tensor-core instructions): writes the exact
  * int32 partial sums P [ceil(K/block), M, N] instead of the scaled result (triton_functions.py:115). */
 BI8_API int bi8_gemm_block_partials(const int8_t* A, int64_t lda, const int8_t* Bt, int64_t ldb, int32_t* P,

@@ -108,7 +108,7 @@ __device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-// 2-D tiled TMA load (no multicast): box at coordinates (x = innermost, y) -> shared memory, completion
+// 2-D tiled TMA load into this CTA only: box at coordinates (x = innermost, y) -> shared memory, completion
 // counted in bytes on `bar`.  x * element size must be a multiple of 16 bytes.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void* tensor_map, uint32_t bar, int x, int y) {
     asm volatile(

@@ -144,7 +144,23 @@ def _gemm_operands(a: torch.Tensor, b: torch.Tensor):
         raise ValueError(f"operands must be int8, got {a.dtype} and {b.dtype}")
     a = _rows_contiguous(a)
     bt = _rows_contiguous(b.t())
+    # The tensor-core kernel needs 16-byte aligned operand rows.  For a large contraction length that is not a multiple
+    # of 16 (GPT-2's 50257-wide dX contraction) re-pitch both operands once: the values are untouched, the row pitch becomes
+    # the next multiple of 16 and the bytes between K and the pitch are never read.
+    k = a.shape[1]
+    if k % 16 != 0 and k >= 256 and a.shape[0] * bt.shape[0] >= 128 * 128:
+        a, bt = _repitch(a), _repitch(bt)
     return a, bt
+
+
+def _repitch(t: torch.Tensor) -> torch.Tensor:
+    rows, k = t.shape
+    if _pitch(t) % 16 == 0 and t.data_ptr() % 16 == 0:
+        return t
+    buf = torch.empty((rows, (k + 15) // 16 * 16), device=t.device, dtype=t.dtype)
+    view = buf[:, :k]
+    view.copy_(t)
+    return view
 
 
 def int8_matmul_block64_rowwise_dequantize(a, b, state_x, state_w, bias=None, *, flags: int = 0):

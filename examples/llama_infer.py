@@ -1,0 +1,211 @@
+"""Llama-2-7B-architecture inference with every linear layer replaced by BlockInt8Linear.
+
+The reference's example only quantizes one weight matrix of a downloaded checkpoint
+(``examples/quantised_infer_llama.py/infer_llama.ipynb``); checkpoints are not available offline, so this driver
+builds the architecture (32 layers, d = 4096, 32 heads, FFN 11008, vocab 32000) with seeded random weights
+N(0, 0.02), runs a 512-token prompt for a batch of 8 and decodes 128 tokens greedily with a KV cache.
+
+Single GPU:            python examples/llama_infer.py
+Tensor parallel (N):   python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 examples/llama_infer.py
+
+Tensor parallelism follows ``blockwise_int8_linear_b200.parallel``: q/k/v, gate/up and the LM head are split over output
+features (bit-identical columns), o_proj and down_proj over input features on block boundaries (11008 = 172 blocks of 64 is
+split 22/21 blocks for 8 ranks) with fp32 partial results summed by one all-reduce per layer half.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+import time
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+import torch.nn.functional as F
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import block_linear_config as cfg  # noqa: E402
+from block_linear import BlockInt8Linear  # noqa: E402
+from blockwise_int8_linear_b200.parallel import block_aligned_bounds  # noqa: E402
+
+
+def seeded_weight(out_f, in_f, seed, dev, rows=None, cols=None):
+    """N(0, 0.02) bf16 [out_f, in_f], generated from `seed` so that every rank sees the same full matrix, then sliced."""
+    g = torch.Generator(device=dev).manual_seed(seed)
+    w = (torch.randn((out_f, in_f), device=dev, generator=g) * 0.02).to(torch.bfloat16)
+    if rows is not None:
+        w = w[rows[0]:rows[1]]
+    if cols is not None:
+        w = w[:, cols[0]:cols[1]]
+    return w.contiguous()
+
+
+class Int8Linear(nn.Module):
+    """A BlockInt8Linear holding this rank's shard.  mode 'col': rows [lo,hi) of the weight, local output.
+    mode 'row': columns [lo,hi), fp32 partial output summed over the group."""
+
+    def __init__(self, in_f, out_f, seed, dev, mode, rank, world, block):
+        super().__init__()
+        self.mode, self.world = mode, world
+        if mode == "col":
+            lo, hi = block_aligned_bounds(out_f, world, block)[rank]
+            w = seeded_weight(out_f, in_f, seed, dev, rows=(lo, hi))
+        else:
+            lo, hi = block_aligned_bounds(in_f, world, block)[rank]
+            w = seeded_weight(out_f, in_f, seed, dev, cols=(lo, hi))
+        self.bounds = (lo, hi)
+        self.lin = BlockInt8Linear(w.shape[1], w.shape[0], bias=False, device=dev, dtype=torch.bfloat16)
+        self.lin.weight.data = w
+        self.lin.eval()
+        self.lin.prepare_for_eval()
+        self.lin.weight.data = torch.empty(0, device=dev, dtype=torch.bfloat16)      # keep only the int8 copy resident
+
+    def forward(self, x):
+        if self.mode == "col" or self.world == 1:
+            return self.lin.infer(x)
+        prev = cfg.INPUT_OUTPUT_TORCH_TYPE
+        cfg.INPUT_OUTPUT_TORCH_TYPE = torch.float32
+        try:
+            part = self.lin.infer(x)
+        finally:
+            cfg.INPUT_OUTPUT_TORCH_TYPE = prev
+        dist.all_reduce(part)
+        return part.to(prev)
+
+
+def rms_norm(x, eps=1e-5):
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)
+
+
+def rope(x, pos, theta=10000.0):
+    # x [B, H, T, D]; pos [T]
+    d = x.shape[-1]
+    inv = 1.0 / (theta ** (torch.arange(0, d, 2, device=x.device, dtype=torch.float32) / d))
+    ang = pos.float()[:, None] * inv[None, :]
+    cos, sin = ang.cos()[None, None], ang.sin()[None, None]
+    x1, x2 = x.float()[..., 0::2], x.float()[..., 1::2]
+    out = torch.stack((x1 * cos - x2 * sin, x1 * sin + x2 * cos), dim=-1).flatten(-2)
+    return out.to(x.dtype)
+
+
+class Layer(nn.Module):
+    def __init__(self, i, a, dev, rank, world):
+        super().__init__()
+        d, f, blk = a.hidden, a.ffn, a.block
+        mk = lambda in_f, out_f, s, mode: Int8Linear(in_f, out_f, 1000 * i + s, dev, mode, rank, world, blk)
+        self.q, self.k, self.v = mk(d, d, 1, "col"), mk(d, d, 2, "col"), mk(d, d, 3, "col")
+        self.o = mk(d, d, 4, "row")
+        self.gate, self.up = mk(d, f, 5, "col"), mk(d, f, 6, "col")
+        self.down = mk(f, d, 7, "row")
+        self.heads_local = (self.q.bounds[1] - self.q.bounds[0]) // a.head_dim
+        self.head_dim = a.head_dim
+        self.kcache = self.vcache = None
+
+    def forward(self, x, pos0, max_len):
+        B, T, _ = x.shape
+        h = rms_norm(x)
+        q = self.q(h).view(B, T, self.heads_local, self.head_dim).transpose(1, 2)
+        k = self.k(h).view(B, T, self.heads_local, self.head_dim).transpose(1, 2)
+        v = self.v(h).view(B, T, self.heads_local, self.head_dim).transpose(1, 2)
+        pos = torch.arange(pos0, pos0 + T, device=x.device)
+        q, k = rope(q, pos), rope(k, pos)
+        if self.kcache is None:
+            self.kcache = torch.empty((B, self.heads_local, max_len, self.head_dim), device=x.device, dtype=x.dtype)
+            self.vcache = torch.empty_like(self.kcache)
+        self.kcache[:, :, pos0:pos0 + T] = k
+        self.vcache[:, :, pos0:pos0 + T] = v
+        kk, vv = self.kcache[:, :, :pos0 + T], self.vcache[:, :, :pos0 + T]
+        att = F.scaled_dot_product_attention(q, kk, vv, is_causal=(T > 1))
+        att = att.transpose(1, 2).reshape(B, T, self.heads_local * self.head_dim)
+        x = x + self.o(att)
+        h = rms_norm(x)
+        x = x + self.down(F.silu(self.gate(h)) * self.up(h))
+        return x
+
+
+class Llama(nn.Module):
+    def __init__(self, a, dev, rank, world):
+        super().__init__()
+        g = torch.Generator(device=dev).manual_seed(7)
+        self.emb = (torch.randn((a.vocab, a.hidden), device=dev, generator=g) * 0.02).to(torch.bfloat16)
+        self.layers = nn.ModuleList(Layer(i, a, dev, rank, world) for i in range(a.layers))
+        self.head = Int8Linear(a.hidden, a.vocab, 99, dev, "col", rank, world, a.block)
+        self.world, self.vocab, self.block = world, a.vocab, a.block
+
+    @torch.no_grad()
+    def forward(self, ids, pos0, max_len):
+        x = self.emb[ids]
+        for layer in self.layers:
+            x = layer(x, pos0, max_len)
+        logits = self.head(rms_norm(x[:, -1:]))                    # [B, 1, V_local]
+        if self.world > 1:
+            sizes = [hi - lo for lo, hi in block_aligned_bounds(self.vocab, self.world, self.block)]
+            width = max(sizes)
+            pad = torch.full((logits.shape[0], 1, width), float("-inf"), device=logits.device, dtype=logits.dtype)
+            pad[..., : logits.shape[-1]] = logits
+            bufs = [torch.empty_like(pad) for _ in range(self.world)]
+            dist.all_gather(bufs, pad)
+            logits = torch.cat([b[..., :n] for b, n in zip(bufs, sizes)], dim=-1)
+        return logits
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--ffn", type=int, default=11008)
+    ap.add_argument("--vocab", type=int, default=32000)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--prompt", type=int, default=512)
+    ap.add_argument("--decode", type=int, default=128)
+    ap.add_argument("--block", type=int, default=64)
+    a = ap.parse_args()
+    a.head_dim = a.hidden // a.heads
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    assert a.heads % world == 0, "heads must divide over the ranks"
+    cfg.GROUP_SIZE, cfg.INPUT_OUTPUT_TORCH_TYPE = a.block, torch.bfloat16
+    model = Llama(a, dev, rank, world)
+    ids = torch.randint(0, a.vocab, (a.batch, a.prompt), generator=torch.Generator().manual_seed(4000)).to(dev)
+    max_len = a.prompt + a.decode
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    logits = model(ids, 0, max_len)
+    torch.cuda.synchronize()
+    t_prefill = time.perf_counter() - t0
+    nxt = logits.argmax(-1)
+    out = [nxt]
+    t0 = time.perf_counter()
+    for step in range(a.decode - 1):
+        logits = model(nxt, a.prompt + step, max_len)
+        nxt = logits.argmax(-1)
+        out.append(nxt)
+    torch.cuda.synchronize()
+    t_decode = time.perf_counter() - t0
+    if rank == 0:
+        toks = torch.cat(out, dim=1)
+        print(json.dumps({
+            "model": f"llama-arch {a.layers}x{a.hidden} ffn {a.ffn} vocab {a.vocab}, random init N(0,0.02), BlockInt8Linear block {a.block}",
+            "n_gpus": world, "batch": a.batch, "prompt": a.prompt, "decode": a.decode,
+            "prefill_tokens_per_s": a.batch * a.prompt / t_prefill, "prefill_s": t_prefill,
+            "decode_tokens_per_s": a.batch * (a.decode - 1) / t_decode, "decode_ms_per_step": 1e3 * t_decode / (a.decode - 1),
+            "first_tokens": toks[0, :8].tolist(),
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -226,6 +226,20 @@ def test_largest_projection_shape_properties():
     assert_clean_device()
 
 
+def test_unaligned_long_contraction_is_repitched_onto_the_tensor_cores():
+    """K = 1000 + 17: not a multiple of 16.  The shim re-pitches the operands; results equal the CUDA-core kernel's
+    within the tensor-core tolerance and the int32 partial sums stay exact."""
+    from triton_functions import int8_matmul_block_partials
+    set_config(64, torch.float32)
+    m, k, n = 160, 1017, 200
+    xq, xs, wq, ws = quantized_pair(m, k, n, 64, seed=77)
+    c = _gemm(xq, wq, xs, ws)
+    _check_fp32(c, xq, wq, xs, ws, 64)
+    p = int8_matmul_block_partials(xq.to(DEV), wq.to(DEV).t(), 64)
+    assert torch.equal(p.cpu(), O.gemm_block_partials(xq, wq.t(), 64))
+    set_config(64)
+
+
 def test_zero_sized():
     from triton_functions import int8_matmul_block64_rowwise_dequantize as mm
     set_config(64)

@@ -70,6 +70,12 @@ int check_gemm(const GemmArgs& g, bool partials) {
 int dispatch_gemm(const GemmArgs& g, cudaStream_t st) {
     const char* why = "";
     const bool tc_ok = g.K > 0 && gemm_tc_applicable(g, &why);
+    if (g.flags & BI8_GEMM_FORCE_SMALLM) {
+        if (!gemm_smallm_applicable(g)) return fail(BI8_ERR_ALIGN, "small-M GEMM not applicable (needs M <= 16, block 32/64/128, K %% 16 == 0, 32-byte aligned weight rows)");
+        return launch_gemm_smallm(g, st);
+    }
+    if (!(g.flags & (BI8_GEMM_FORCE_TC | BI8_GEMM_FORCE_GENERIC)) && g.K > 0 && gemm_smallm_applicable(g))
+        return launch_gemm_smallm(g, st);
     if (g.flags & BI8_GEMM_FORCE_TC) {
         if (!tc_ok) return fail(BI8_ERR_ALIGN, "tensor-core GEMM not applicable: %s", why);
         return launch_gemm_tc(g, st);

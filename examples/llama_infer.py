@@ -85,7 +85,7 @@ def rms_norm(x, eps=1e-5):
 
 
 def rope(x, pos, theta=10000.0):
-    # x [B, H, T, D]; pos [T]
+    # x [B, H, T, D]; pos [T] (a device tensor, so that a captured decode step can advance it in place)
     d = x.shape[-1]
     inv = 1.0 / (theta ** (torch.arange(0, d, 2, device=x.device, dtype=torch.float32) / d))
     ang = pos.float()[:, None] * inv[None, :]
@@ -108,21 +108,31 @@ class Layer(nn.Module):
         self.head_dim = a.head_dim
         self.kcache = self.vcache = None
 
-    def forward(self, x, pos0, max_len):
+    def forward(self, x, pos0, max_len, pos_dev=None):
+        """Prefill: pos0 is a Python int and the cache is sliced.  Decode (pos_dev given, T == 1): the position is a device
+        tensor, the cache is written with index_copy_ and attended in full under a mask, so that every shape is static and
+        the step can be captured in a CUDA graph."""
         B, T, _ = x.shape
         h = rms_norm(x)
         q = self.q(h).view(B, T, self.heads_local, self.head_dim).transpose(1, 2)
         k = self.k(h).view(B, T, self.heads_local, self.head_dim).transpose(1, 2)
         v = self.v(h).view(B, T, self.heads_local, self.head_dim).transpose(1, 2)
-        pos = torch.arange(pos0, pos0 + T, device=x.device)
-        q, k = rope(q, pos), rope(k, pos)
         if self.kcache is None:
-            self.kcache = torch.empty((B, self.heads_local, max_len, self.head_dim), device=x.device, dtype=x.dtype)
-            self.vcache = torch.empty_like(self.kcache)
-        self.kcache[:, :, pos0:pos0 + T] = k
-        self.vcache[:, :, pos0:pos0 + T] = v
-        kk, vv = self.kcache[:, :, :pos0 + T], self.vcache[:, :, :pos0 + T]
-        att = F.scaled_dot_product_attention(q, kk, vv, is_causal=(T > 1))
+            self.kcache = torch.zeros((B, self.heads_local, max_len, self.head_dim), device=x.device, dtype=x.dtype)
+            self.vcache = torch.zeros_like(self.kcache)
+        if pos_dev is None:
+            pos = torch.arange(pos0, pos0 + T, device=x.device)
+            q, k = rope(q, pos), rope(k, pos)
+            self.kcache[:, :, pos0:pos0 + T] = k
+            self.vcache[:, :, pos0:pos0 + T] = v
+            kk, vv = self.kcache[:, :, :pos0 + T], self.vcache[:, :, :pos0 + T]
+            att = F.scaled_dot_product_attention(q, kk, vv, is_causal=(T > 1))
+        else:
+            q, k = rope(q, pos_dev), rope(k, pos_dev)
+            self.kcache.index_copy_(2, pos_dev, k)
+            self.vcache.index_copy_(2, pos_dev, v)
+            mask = (torch.arange(max_len, device=x.device) <= pos_dev).view(1, 1, 1, max_len)
+            att = F.scaled_dot_product_attention(q, self.kcache, self.vcache, attn_mask=mask)
         att = att.transpose(1, 2).reshape(B, T, self.heads_local * self.head_dim)
         x = x + self.o(att)
         h = rms_norm(x)
@@ -140,10 +150,10 @@ class Llama(nn.Module):
         self.world, self.vocab, self.block = world, a.vocab, a.block
 
     @torch.no_grad()
-    def forward(self, ids, pos0, max_len):
+    def forward(self, ids, pos0, max_len, pos_dev=None):
         x = self.emb[ids]
         for layer in self.layers:
-            x = layer(x, pos0, max_len)
+            x = layer(x, pos0, max_len, pos_dev)
         logits = self.head(rms_norm(x[:, -1:]))                    # [B, 1, V_local]
         if self.world > 1:
             sizes = [hi - lo for lo, hi in block_aligned_bounds(self.vocab, self.world, self.block)]
@@ -167,6 +177,7 @@ def main():
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--decode", type=int, default=128)
     ap.add_argument("--block", type=int, default=64)
+    ap.add_argument("--eager", action="store_true", help="do not capture the decode step in a CUDA graph")
     a = ap.parse_args()
     a.head_dim = a.hidden // a.heads
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
@@ -187,11 +198,43 @@ def main():
     t_prefill = time.perf_counter() - t0
     nxt = logits.argmax(-1)
     out = [nxt]
+    # Decode: one step = ~450 small launches (quantize + GEMM per linear, attention, norms); eager launch latency would
+    # dominate, so the step is captured once in a CUDA graph (static token / position buffers) and replayed.
+    tok = nxt.clone()
+    pos_dev = torch.full((1,), a.prompt, device=dev, dtype=torch.long)
+
+    def decode_step():
+        lg = model(tok, 0, max_len, pos_dev)
+        tok.copy_(lg.argmax(-1))
+        pos_dev.add_(1)
+
+    graph = None
+    if not a.eager:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):                                    # warm-up on a side stream (allocator, NCCL, lazy init)
+                decode_step()
+        torch.cuda.current_stream().wait_stream(side)
+        tok.copy_(nxt)
+        pos_dev.fill_(a.prompt)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            decode_step()
+        tok.copy_(nxt)                                            # the capture itself does not execute the step
+        pos_dev.fill_(a.prompt)
+    else:
+        decode_step()                                             # warm-up
+        tok.copy_(nxt)
+        pos_dev.fill_(a.prompt)
+    torch.cuda.synchronize()
     t0 = time.perf_counter()
     for step in range(a.decode - 1):
-        logits = model(nxt, a.prompt + step, max_len)
-        nxt = logits.argmax(-1)
-        out.append(nxt)
+        if graph is not None:
+            graph.replay()
+        else:
+            decode_step()
+        out.append(tok.clone())
     torch.cuda.synchronize()
     t_decode = time.perf_counter() - t0
     if rank == 0:
@@ -200,7 +243,7 @@ def main():
             "model": f"llama-arch {a.layers}x{a.hidden} ffn {a.ffn} vocab {a.vocab}, random init N(0,0.02), BlockInt8Linear block {a.block}",
             "n_gpus": world, "batch": a.batch, "prompt": a.prompt, "decode": a.decode,
             "prefill_tokens_per_s": a.batch * a.prompt / t_prefill, "prefill_s": t_prefill,
-            "decode_tokens_per_s": a.batch * (a.decode - 1) / t_decode, "decode_ms_per_step": 1e3 * t_decode / (a.decode - 1),
+            "decode_tokens_per_s": a.batch * (a.decode - 1) / t_decode, "decode_ms_per_step": 1e3 * t_decode / (a.decode - 1), "decode_mode": "eager" if a.eager else "cuda graph",
             "first_tokens": toks[0, :8].tolist(),
         }))
     if world > 1:

@@ -240,6 +240,35 @@ def test_unaligned_long_contraction_is_repitched_onto_the_tensor_cores():
     set_config(64)
 
 
+SMALLM = 8
+SMALL_SHAPES = [
+    # (M, K, N, block)
+    (1, 64, 4, 64), (1, 4096, 512, 64), (5, 1056, 75, 64), (8, 2048, 1000, 64), (9, 256, 260, 64), (16, 4096, 1024, 64),
+    (3, 192, 33, 32), (8, 1056, 130, 32), (16, 2048, 256, 128), (7, 416, 50, 128), (2, 11008, 64, 64),
+]
+
+
+@pytest.mark.parametrize("shape", SMALL_SHAPES)
+def test_small_m_weight_streaming_kernel(shape):
+    """M <= 16 (decode): the CUDA-core weight-streaming kernel.  Every term is evaluated in the reference's order; only the
+    order of the fp32 additions differs, so the tensor-core tolerance applies; bf16 results as for the tensor-core kernel."""
+    m, k, n, block = shape
+    xq, xs, wq, ws = quantized_pair(m, k, n, block, seed=11 * m + k + n)
+    bias = torch.randn(n, generator=torch.Generator().manual_seed(n)).to(torch.bfloat16)
+    set_config(block, torch.float32)
+    _check_fp32(_gemm(xq, wq, xs, ws, flags=SMALLM), xq, wq, xs, ws, block)
+    _check_fp32(_gemm(xq, wq, xs, ws, bias, flags=SMALLM), xq, wq, xs, ws, block, bias)
+    assert torch.equal(_gemm(xq, wq, xs, ws), _gemm(xq, wq, xs, ws, flags=SMALLM)), "default dispatch for M <= 16"
+    set_config(block, torch.bfloat16)
+    _check_bf16(_gemm(xq, wq, xs, ws, bias, flags=SMALLM), xq, wq, xs, ws, block, bias)
+    from blockwise_int8_linear_b200._lib import Bi8Error
+    with pytest.raises(Bi8Error):
+        big = quantized_pair(17, 128, 32, block, seed=1)
+        _gemm(big[0], big[2], big[1], big[3], flags=SMALLM)
+    assert_clean_device()
+    set_config(64)
+
+
 def test_zero_sized():
     from triton_functions import int8_matmul_block64_rowwise_dequantize as mm
     set_config(64)

@@ -74,7 +74,8 @@ int dispatch_gemm(const GemmArgs& g, cudaStream_t st) {
         if (!gemm_smallm_applicable(g)) return fail(BI8_ERR_ALIGN, "small-M GEMM not applicable (needs M <= 16, block 32/64/128, K %% 16 == 0, 32-byte aligned weight rows)");
         return launch_gemm_smallm(g, st);
     }
-    if (!(g.flags & (BI8_GEMM_FORCE_TC | BI8_GEMM_FORCE_GENERIC)) && g.K > 0 && gemm_smallm_applicable(g))
+    // default for M <= 8 (one pass over the weights); 9..16 would stream them twice and is faster on the tensor cores
+    if (!(g.flags & (BI8_GEMM_FORCE_TC | BI8_GEMM_FORCE_GENERIC)) && g.K > 0 && g.M <= 8 && gemm_smallm_applicable(g))
         return launch_gemm_smallm(g, st);
     if (g.flags & BI8_GEMM_FORCE_TC) {
         if (!tc_ok) return fail(BI8_ERR_ALIGN, "tensor-core GEMM not applicable: %s", why);

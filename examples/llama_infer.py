@@ -179,6 +179,10 @@ def main():
     ap.add_argument("--block", type=int, default=64)
     ap.add_argument("--eager", action="store_true", help="do not capture the decode step in a CUDA graph")
     a = ap.parse_args()
+    if int(os.environ.get("WORLD_SIZE", 1)) > 1:
+        # the captured decode step has only been validated on one GPU; with tensor parallelism (NCCL collectives inside the
+        # step) the driver decodes eagerly
+        a.eager = True
     a.head_dim = a.hidden // a.heads
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))

@@ -57,7 +57,7 @@ extern "C" {
 #define BI8_GEMM_FORCE_GENERIC 1   /* CUDA-core kernel even where the tensor-core kernel applies */
 #define BI8_GEMM_FORCE_TC 2        /* fail with BI8_ERR_ALIGN instead of falling back */
 #define BI8_GEMM_NO_SEED 4         /* tensor-core kernel: convert partial sums with cvt instead of seeded TMEM */
-#define BI8_GEMM_FORCE_SMALLM 8    /* weight-streaming CUDA-core kernel for M <= 16 (the default choice there) */
+#define BI8_GEMM_FORCE_SMALLM 8    /* weight-streaming CUDA-core kernel, M <= 16 (the default choice for M <= 8) */
 
 BI8_API int bi8_version(void);
 

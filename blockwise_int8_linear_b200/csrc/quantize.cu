@@ -341,8 +341,10 @@ __global__ void __launch_bounds__(kThreads) quantize_rowwise_generic_kernel(
 // ------------------------------------------------------------------------------------------------
 // Column-wise quantize (fused transpose): x [R,C] -> q [C,R], s [ceil(R/B), C].  A CTA stages a tile of
 // NBLK*B rows x 128 columns in shared memory with 16-byte row-contiguous loads; then one thread owns one
-// (block, column): B values read down the column (bank-conflict free: lanes are consecutive columns),
-// absmax, quantize, and B bytes written as 16-byte pieces of output row c.
+// (block, column): it reads the B values down the column once (bank-conflict free: lanes are consecutive columns),
+// keeps them packed in registers, takes the absmax and quantizes.  The int8 results go back to shared memory
+// transposed ([column][row], reusing the staging area), and the CTA writes them out as whole 128-byte (or longer)
+// runs of the output rows.
 template <typename T, int B>
 __global__ void __launch_bounds__(kThreads) quantize_colwise_vec_kernel(
     const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ q, float* __restrict__ s, int R, int C, int col_tiles) {
@@ -350,56 +352,81 @@ __global__ void __launch_bounds__(kThreads) quantize_colwise_vec_kernel(
     constexpr int NBLK = kThreads / TC;     // blocks (along rows of x) per tile
     constexpr int TR = NBLK * B;
     constexpr int PITCH = TC + 2;           // 16-bit elements; +2 keeps column reads conflict free
+    constexpr int OPITCH = TR + 16;         // bytes per output row in the transposed tile
+    static_assert(TC * OPITCH <= TR * PITCH * 2, "the transposed tile reuses the staging area");
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint16_t* tile = reinterpret_cast<uint16_t*>(smem_raw);
 
     const int ct = blockIdx.x % col_tiles, rt = blockIdx.x / col_tiles;
     const int c0 = ct * TC, r0 = rt * TR;
-    // load: each row of the tile is 16 lanes x 16 bytes
+    // load: each row of the tile is 16 lanes x 16 bytes; all loads of a thread are issued before its first store
     constexpr int VPR = TC / 8;
-    for (int v = threadIdx.x; v < TR * VPR; v += kThreads) {
-        const int r = v / VPR, cv = (v % VPR) * 8;
-        uint4 d = make_uint4(0u, 0u, 0u, 0u);
-        if (r0 + r < R && c0 + cv < C) d = ld_nc_v4(x + (int64_t)(r0 + r) * ldx + c0 + cv);
-        uint32_t* dst = reinterpret_cast<uint32_t*>(tile + r * PITCH + cv);   // 4-byte aligned (PITCH even)
-        dst[0] = d.x; dst[1] = d.y; dst[2] = d.z; dst[3] = d.w;
+    constexpr int PER_THREAD = TR * VPR / kThreads;
+    {
+        uint4 d[PER_THREAD];
+#pragma unroll
+        for (int u = 0; u < PER_THREAD; ++u) {
+            const int v = threadIdx.x + u * kThreads;
+            const int r = v / VPR, cv = (v % VPR) * 8;
+            d[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (r0 + r < R && c0 + cv < C) d[u] = ld_nc_v4(x + (int64_t)(r0 + r) * ldx + c0 + cv);
+        }
+#pragma unroll
+        for (int u = 0; u < PER_THREAD; ++u) {
+            const int v = threadIdx.x + u * kThreads;
+            const int r = v / VPR, cv = (v % VPR) * 8;
+            uint32_t* dst = reinterpret_cast<uint32_t*>(tile + r * PITCH + cv);   // 4-byte aligned (PITCH even)
+            dst[0] = d[u].x; dst[1] = d[u].y; dst[2] = d[u].z; dst[3] = d[u].w;
+        }
     }
     __syncthreads();
     const int c = threadIdx.x % TC, blk = threadIdx.x / TC;
     const uint16_t* colp = tile + (blk * B) * PITCH + c;
+    uint32_t packed[B / 2];                 // the column's B values, two per register
     float amax = 0.0f;
-#pragma unroll 16
-    for (int r = 0; r < B; ++r) {
-        T e = *reinterpret_cast<const T*>(colp + r * PITCH);
-        amax = fmaxf(amax, fabsf(to_f32<T>(e)));
+#pragma unroll
+    for (int r = 0; r < B; r += 2) {
+        const uint32_t lo = colp[r * PITCH], hi = colp[(r + 1) * PITCH];
+        packed[r / 2] = lo | (hi << 16);
+        float flo, fhi;
+        unpack2<T>(packed[r / 2], flo, fhi);
+        amax = fmaxf(amax, fmaxf(fabsf(flo), fabsf(fhi)));
     }
     BlockQ bq;
     bq.set(amax, true);
+    uint32_t out[B / 4];
+#pragma unroll
+    for (int g = 0; g < B / 4; ++g) {
+        float f0, f1, f2, f3;
+        unpack2<T>(packed[2 * g], f0, f1);
+        unpack2<T>(packed[2 * g + 1], f2, f3);
+        out[g] = pack4(bq.q(f0), bq.q(f1), bq.q(f2), bq.q(f3));
+    }
     const int rb = r0 + blk * B;            // first row of this block
-    const bool live = (c0 + c < C) && (rb < R);
-    if (live) {
-        int8_t* o = q + (int64_t)(c0 + c) * R + rb;
-        const bool full = (rb + B <= R) && ((R & 15) == 0);
+    if (c0 + c < C && rb < R) s[(int64_t)(rb / B) * C + c0 + c] = amax;
+    __syncthreads();                        // every thread has read its column: the staging area can be reused
+    unsigned char* otile = smem_raw;        // [TC][OPITCH] int8, row = output row (column of x)
 #pragma unroll
-        for (int g = 0; g < B / 16; ++g) {
-            uint32_t w[4];
+    for (int g = 0; g < B / 16; ++g)
+        *reinterpret_cast<uint4*>(otile + c * OPITCH + blk * B + g * 16) = make_uint4(out[4 * g], out[4 * g + 1], out[4 * g + 2], out[4 * g + 3]);
+    __syncthreads();
+    // store: output row (c0 + cc) receives TR contiguous bytes starting at r0
+    constexpr int PIECES = TR / 16;         // 16-byte pieces per output row
+    const bool vec_ok = ((R & 15) == 0);
+    for (int v = threadIdx.x; v < TC * PIECES; v += kThreads) {
+        const int cc = v / PIECES, piece = v % PIECES;
+        const int rr = r0 + piece * 16;
+        if (c0 + cc >= C || rr >= R) continue;
+        const uint4 d = *reinterpret_cast<const uint4*>(otile + cc * OPITCH + piece * 16);
+        int8_t* o = q + (int64_t)(c0 + cc) * R + rr;
+        if (vec_ok && rr + 16 <= R) {
+            *reinterpret_cast<uint4*>(o) = d;
+        } else {
+            const uint32_t w[4] = {d.x, d.y, d.z, d.w};
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const uint16_t* p = colp + (g * 16 + u * 4) * PITCH;
-                w[u] = pack4(bq.q(to_f32<T>(*reinterpret_cast<const T*>(p))),
-                             bq.q(to_f32<T>(*reinterpret_cast<const T*>(p + PITCH))),
-                             bq.q(to_f32<T>(*reinterpret_cast<const T*>(p + 2 * PITCH))),
-                             bq.q(to_f32<T>(*reinterpret_cast<const T*>(p + 3 * PITCH))));
-            }
-            if (full) {
-                *reinterpret_cast<uint4*>(o + g * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-            } else {
-#pragma unroll
-                for (int u = 0; u < 16; ++u)
-                    if (rb + g * 16 + u < R) o[g * 16 + u] = (int8_t)((w[u / 4] >> (8 * (u % 4))) & 0xffu);
-            }
+            for (int u = 0; u < 16; ++u)
+                if (rr + u < R) o[u] = (int8_t)((w[u / 4] >> (8 * (u % 4))) & 0xffu);
         }
-        s[(int64_t)(rb / B) * C + c0 + c] = amax;
     }
 }
 

@@ -324,24 +324,53 @@ def run_ours(args):
     _lib.device_status()
 
     # ---- end to end through the public API with host buffers ----
+    # Every step copies its activations from pinned host memory, runs BlockInt8Linear.forward and copies the result back
+    # to pinned host memory.  The three legs run on three streams with double buffers, so that the copy engines work on
+    # the neighbouring steps while the kernels of one step run (the way a serving loop drives the layer); every byte of
+    # every step still crosses PCIe inside the timed region.
     lin = BlockInt8Linear(K, N, bias=False, device=dev, dtype=torch.bfloat16).eval()
     lin.weight.data = w
     x_host = [xs_dev[i].cpu().pin_memory() for i in range(2)]
-    y_host = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    y_host = [torch.empty((M, N), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    x_dev2 = [torch.empty((M, K), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    y_dev2 = [torch.empty((M, N), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    s_in, s_run, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_run = [torch.cuda.Event() for _ in range(2)]
+    ev_out = [torch.cuda.Event() for _ in range(2)]
+    ev_free = [torch.cuda.Event() for _ in range(2)]
 
     def e2e_step(i):
-        xd = x_host[i % 2].to(dev, non_blocking=True)
-        with torch.no_grad():
-            y = lin(xd)
-        y_host.copy_(y, non_blocking=True)
+        b = i % 2
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(ev_free[b])                 # x_dev2[b] was consumed by the step that used it last
+            x_dev2[b].copy_(x_host[b], non_blocking=True)
+            ev_in[b].record(s_in)
+        with torch.cuda.stream(s_run):
+            s_run.wait_event(ev_in[b])
+            s_run.wait_event(ev_out[b])                 # y_dev2[b] has been copied out
+            with torch.no_grad():
+                y_dev2[b].copy_(lin(x_dev2[b]))
+            ev_free[b].record(s_run)
+            ev_run[b].record(s_run)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_run[b])
+            y_host[b].copy_(y_dev2[b], non_blocking=True)
+            ev_out[b].record(s_out)
 
+    for ev in ev_free + ev_out:
+        ev.record()
     for i in range(max(3, args.warmup)):
         e2e_step(i)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
+    for s_ in (s_in, s_run, s_out):
+        s_.wait_event(e0)
     for i in range(args.steps):
         e2e_step(i)
+    for s_ in (s_in, s_run, s_out):
+        torch.cuda.current_stream().wait_stream(s_)
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1) / args.steps
@@ -350,7 +379,7 @@ def run_ours(args):
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         e2e_ms = t.item()
     e2e_value = world * ops_step / (e2e_ms * 1e-3) / 1e12
-    del lin, x_host
+    del lin, x_host, y_host, x_dev2, y_dev2
 
     if rank != 0:
         if world > 1:
@@ -398,8 +427,8 @@ def run_ours(args):
                    "parallelism": f"dp{world} over tokens, no collective"},
         "roofline": roofline,
         "e2e": {"value": e2e_value, "unit": "TOP/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": M * K * 2,
-                "d2h_bytes_per_step": M * N * 2, "api": "BlockInt8Linear.forward (eval) on pinned host buffers"},
-        "gpu_launches": world * args.steps * 2,
+                "d2h_bytes_per_step": M * N * 2, "api": "BlockInt8Linear.forward (eval) on pinned host buffers; H2D, kernels and D2H of neighbouring steps overlap on three streams"},
+        "gpu_launches": world * args.steps * 2,          # quantize + GEMM per step in the device-timed region (the e2e leg launches the same two per step)
         "clocks": clocks,
     }
     if cpu is not None:

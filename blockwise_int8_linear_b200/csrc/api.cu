@@ -74,9 +74,18 @@ int dispatch_gemm(const GemmArgs& g, cudaStream_t st) {
         if (!gemm_smallm_applicable(g)) return fail(BI8_ERR_ALIGN, "small-M GEMM not applicable (needs M <= 16, block 32/64/128, K %% 16 == 0, 32-byte aligned weight rows)");
         return launch_gemm_smallm(g, st);
     }
-    // default for M <= 8 (one pass over the weights); 9..16 would stream them twice and is faster on the tensor cores
-    if (!(g.flags & (BI8_GEMM_FORCE_TC | BI8_GEMM_FORCE_GENERIC)) && g.K > 0 && g.M <= 8 && gemm_smallm_applicable(g))
-        return launch_gemm_smallm(g, st);
+    if (g.flags & BI8_GEMM_FORCE_SKINNY) {
+        if (!gemm_skinny_applicable(g))
+            return fail(BI8_ERR_ALIGN, "skinny tensor-core GEMM not applicable (needs M <= 32, block 32/64/128, N %% 4 == 0, 16-byte aligned "
+                                       "operand rows and weight scales, and the workspace bi8_gemm_workspace_bytes() asks for)");
+        return launch_gemm_skinny(g, st);
+    }
+    const bool free_choice = !(g.flags & (BI8_GEMM_FORCE_TC | BI8_GEMM_FORCE_GENERIC)) && g.K > 0;
+    // M <= 32: one pass over the weights on the tensor cores with exchanged operand roles (needs the workspace)
+    if (free_choice && gemm_skinny_applicable(g)) return launch_gemm_skinny(g, st);
+    // otherwise M <= 8 streams the weights on the CUDA cores; 9..16 would stream them twice and is faster on the
+    // general tensor-core kernel
+    if (free_choice && g.M <= 8 && gemm_smallm_applicable(g)) return launch_gemm_smallm(g, st);
     if (g.flags & BI8_GEMM_FORCE_TC) {
         if (!tc_ok) return fail(BI8_ERR_ALIGN, "tensor-core GEMM not applicable: %s", why);
         return launch_gemm_tc(g, st);
@@ -152,7 +161,8 @@ size_t bi8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int block) {
     g.N = N;
     g.K = K;
     g.block = block;
-    return gemm_tc_workspace_bytes(g);
+    const size_t a = gemm_tc_workspace_bytes(g), b = gemm_skinny_workspace_bytes(g);
+    return a > b ? a : b;
 }
 
 int bi8_gemm_dequant(const int8_t* A, int64_t lda, const int8_t* Bt, int64_t ldb, const float* sA, const float* sB,

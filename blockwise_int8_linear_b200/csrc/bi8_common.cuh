@@ -55,6 +55,9 @@ bool gemm_tc_applicable(const GemmArgs& g, const char** why);
 size_t gemm_tc_workspace_bytes(const GemmArgs& g);
 int launch_gemm_tc(const GemmArgs& g, cudaStream_t st);
 int launch_gemm_generic(const GemmArgs& g, cudaStream_t st);
+bool gemm_skinny_applicable(const GemmArgs& g);
+size_t gemm_skinny_workspace_bytes(const GemmArgs& g);
+int launch_gemm_skinny(const GemmArgs& g, cudaStream_t st);
 bool gemm_smallm_applicable(const GemmArgs& g);
 int launch_gemm_smallm(const GemmArgs& g, cudaStream_t st);
 int run_mma_peak_probe(int iters, float* ms, int* sm_count);

@@ -25,13 +25,10 @@
 //   t = fma(word, s, -1.5*2^23 * s) = fl(P * s)
 // needs no int->float conversion.  s = sA[j,m]/127^2 rounded to 22 significant bits makes 1.5*2^23*s exact.
 #include "bi8_common.cuh"
-#include "sm100_ptx.cuh"
-
-#include <cuda.h>
+#include "tc_common.cuh"
 
 #include <cstdlib>
 #include <cstring>
-#include <mutex>
 
 namespace bi8 {
 namespace {
@@ -43,7 +40,6 @@ constexpr int kBN = 160;                 // tile columns (40 per promotion warp:
 constexpr int kAccBufs = 3;              // s32 accumulators in tensor memory (3 x 160 of the 512 columns)
 constexpr int kAccStride = kBN;          // tensor-memory columns between consecutive accumulators
 constexpr int kProbeN = 256;             // N of the issue-rate probe's MMAs
-constexpr int kBK = 128;                 // K bytes per stage (one 128-byte swizzle row)
 constexpr int kStages = 5;
 constexpr int kScaleStages = 4;
 constexpr int kEpiWarps = 16;             // 4 lane quarters x 4 column slices of 64
@@ -53,9 +49,6 @@ constexpr uint32_t kABytes = kBM * kBK;  // 16 KiB
 constexpr uint32_t kBBytes = kBN * kBK;  // 20 KiB
 constexpr uint32_t kSeedBits = 0x4B400000u;   // float 1.5 * 2^23
 constexpr float kSeedF = 12582912.0f;
-
-// codes stored in the status word's detail when a bounded wait gives up
-enum WaitCode { W_EMPTY_AB = 1, W_FULL_AB = 2, W_ACC_EMPTY = 3, W_ACC_FULL = 4, W_SC_EMPTY = 5, W_SC_FULL = 6, W_PROBE = 7 };
 
 struct TcParams {
     const float* sA;
@@ -95,11 +88,6 @@ struct Geo {
     static constexpr uint32_t misc_off = bar_off + NBARS * 8;   // tmem holder (4 B) + abort flag (4 B)
     static constexpr uint32_t total = misc_off + 16;
 };
-
-__device__ __forceinline__ void report_timeout(int* status, uint32_t abort_flag, int code) {
-    sts_u32(abort_flag, 1u);
-    if (atomicCAS(status, 0, BI8_ERR_TIMEOUT) == 0) status[1] = code;
-}
 
 // Work item -> tile and K-stage range.  Items of one split are consecutive, so CTAs that run together work on
 // different tiles of the same K range.
@@ -600,57 +588,6 @@ __global__ void __launch_bounds__(128, 1) mma_peak_probe_kernel(int iters, int* 
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
     }
-}
-
-// ---- host side --------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* sym = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(sym);
-    });
-    return fn;
-}
-
-// int8 [rows, K] row-major with row pitch ld bytes -> boxes of 128 K-bytes x box_rows rows, 128-byte swizzle
-int make_operand_map(CUtensorMap* map, const int8_t* ptr, int64_t rows, int64_t K, int64_t ld, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return fail(BI8_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-    cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t gstride[1] = {(cuuint64_t)ld};
-    cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(ptr), gdim, gstride, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(BI8_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
-    return BI8_OK;
-}
-
-struct DeviceInfo {
-    int sms = 0;
-    bool ok = false;
-};
-DeviceInfo device_info() {
-    static DeviceInfo cache[64];
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return DeviceInfo{};
-    if (!cache[dev].ok) {
-        int sms = 0, major = 0;
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return DeviceInfo{};
-        if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return DeviceInfo{};
-        cache[dev].sms = sms;
-        cache[dev].ok = (major == 10);
-    }
-    return cache[dev];
 }
 
 template <int QB, int MODE, bool SEED>

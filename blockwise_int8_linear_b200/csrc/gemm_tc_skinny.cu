@@ -1,0 +1,461 @@
+// Int8 block GEMM with fused dequantize for a handful of activation rows (decode: M <= 32), on the sm_100a tensor
+// cores with the operand roles exchanged.
+//
+// Same contract as the reference kernel at triton_functions.py:69-139 (path inside the reference project).  With so few
+// rows of A the work is one pass over the weights Bt[N, K]: the kernel is bound by streaming them from HBM, and is
+// organised around that stream.
+//   * The weights are the M operand of the MMA: a tile is 128 weight rows, the activations (padded to 16 or 32 rows by
+//     the TMA's zero fill) are the N operand, so one tcgen05.mma kind::i8 (M128 N16|32 K32) covers 128 weight rows
+//     and every activation row, and the s32 accumulator of a quantisation block is only 16|32 tensor-memory columns.
+//   * All (tile, K stage) pairs form one sequence that is cut into equal contiguous ranges, one per CTA and one CTA
+//     per SM, so every SM streams the same number of bytes whatever N and K are.  A range may begin or end inside a
+//     tile: such a part of a tile goes to an fp32 workspace slot (at most two per CTA) and a second kernel adds the
+//     slots of a tile in ascending K order; tiles that lie completely inside one range are written directly.
+//   * warp P (producer) issues, per stage, three TMA copies that complete on one barrier: 128 weight rows x 128
+//     K-bytes, the activation rows of the same K range, and the stage's weight scales (a [blocks, 128] fp32 box of
+//     sB); warp P+1 issues the MMAs of the stage, one accumulator range per quantisation block, and commits;
+//     the promotion warps (four per 16 activation rows, one per tensor-memory lane quarter) convert and scale.
+//   * Promotion follows the reference's order term by term, sB*(sA*(float(P)*fl32(1/127^2))), added in ascending block
+//     order within a range, so a tile that is not divided is bit-identical to the CUDA-core kernel.
+#include "tc_common.cuh"
+
+#include <cstring>
+
+namespace bi8 {
+namespace {
+
+using namespace ptx;
+
+constexpr int kTileRows = 128;    // weight rows per tile (the MMA's M)
+constexpr int kSkStages = 6;      // 6 x 16 KiB of weights in flight per SM
+constexpr int kSkMaxM = 32;
+constexpr size_t kSxMaxBytes = 64 * 1024;   // activation scales staged per CTA
+
+constexpr int pow2_at_least(int x) {
+    int p = 32;
+    while (p < x) p *= 2;
+    return p;
+}
+
+template <int QB, int BNS>
+struct SkGeo {
+    static constexpr int BPS = kBK / QB;                  // quantisation blocks per stage
+    static constexpr int MMAS = QB / 32;                  // MMAs (K = 32) per block
+    static constexpr int CHUNKS = BNS / 16;               // groups of 16 activation rows
+    static constexpr int PROMO_WARPS = 4 * CHUNKS;
+    static constexpr int THREADS = (PROMO_WARPS + 2) * 32;
+    static constexpr int ACC_STRIDE = BPS * BNS;          // tensor-memory columns of one stage's accumulators
+    static constexpr int NBUF = (512 / ACC_STRIDE) < 4 ? (512 / ACC_STRIDE) : 4;
+    static constexpr int TMEM_COLS = pow2_at_least(NBUF * ACC_STRIDE);
+    static constexpr uint32_t W_BYTES = kTileRows * kBK;
+    static constexpr uint32_t X_BYTES = BNS * kBK;
+    static constexpr uint32_t S_TX = BPS * kTileRows * 4;                 // bytes the scale copy delivers
+    static constexpr uint32_t S_BYTES = S_TX < 1024 ? 1024 : S_TX;        // keeps every stage 1024-byte aligned
+    static constexpr uint32_t STAGE_BYTES = W_BYTES + X_BYTES + S_BYTES;
+    static constexpr uint32_t bar_off = kSkStages * STAGE_BYTES;
+    static constexpr int FULL_AB = 0, EMPTY_AB = kSkStages, ACC_FULL = 2 * kSkStages, ACC_EMPTY = 2 * kSkStages + NBUF,
+                         NBARS = 2 * kSkStages + 2 * NBUF;
+    static constexpr uint32_t misc_off = bar_off + NBARS * 8;             // tmem holder, abort flag, never-raised flag
+    static constexpr uint32_t sx_off = (misc_off + 16 + 15) & ~15u;       // activation scales [nb][BNS]
+};
+
+struct SkParams {
+    const float* sA;
+    const void* bias;
+    void* C;
+    float* ws;
+    int* status;
+    int64_t ldc;
+    long long total_stages;
+    int M, N, K, nb, nks;
+    int out_dtype, bias_dtype;
+    int live_chunks;    // groups of 16 activation rows that hold a valid row
+};
+
+// first (tile, stage) pair of CTA c when `total` pairs are divided over `ctas` CTAs
+__host__ __device__ __forceinline__ long long range_start(long long c, long long total, long long ctas) { return c * total / ctas; }
+
+// C[m, n] = cast(acc) (+ cast(bias[n]) in the output type: reference lines 125-131)
+__device__ __forceinline__ void finish_store(float acc, int m, int n, const void* bias, int bias_dtype, void* C, int64_t ldc,
+                                             int out_dtype) {
+    float bv = 0.0f;
+    const bool hb = bias != nullptr;
+    if (hb) {
+        if (bias_dtype == BI8_BF16) bv = __bfloat162float(static_cast<const __nv_bfloat16*>(bias)[n]);
+        else if (bias_dtype == BI8_F16) bv = __half2float(static_cast<const __half*>(bias)[n]);
+        else bv = static_cast<const float*>(bias)[n];
+    }
+    const int64_t o = (int64_t)m * ldc + n;
+    if (out_dtype == BI8_F32) {
+        static_cast<float*>(C)[o] = hb ? __fadd_rn(acc, bv) : acc;
+    } else if (out_dtype == BI8_BF16) {
+        __nv_bfloat16 c = __float2bfloat16_rn(acc);
+        if (hb) c = __float2bfloat16_rn(__fadd_rn(__bfloat162float(c), __bfloat162float(__float2bfloat16_rn(bv))));
+        static_cast<__nv_bfloat16*>(C)[o] = c;
+    } else {
+        __half c = __float2half_rn(acc);
+        if (hb) c = __float2half_rn(__fadd_rn(__half2float(c), __half2float(__float2half_rn(bv))));
+        static_cast<__half*>(C)[o] = c;
+    }
+}
+
+template <int QB, int BNS>
+__global__ void __launch_bounds__(SkGeo<QB, BNS>::THREADS, 1)
+gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                      const __grid_constant__ CUtensorMap tmS, const SkParams p) {
+    using G = SkGeo<QB, BNS>;
+    extern __shared__ __align__(1024) unsigned char smem_dyn[];
+    const uint32_t raw = smem_u32(smem_dyn);
+    const uint32_t base = (raw + 1023u) & ~1023u;      // the swizzle atom needs 1024-byte alignment
+    unsigned char* base_ptr = smem_dyn + (base - raw);
+    const uint32_t bars = base + G::bar_off;
+    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(base_ptr + G::misc_off);
+    const uint32_t abort_flag = base + G::misc_off + 4;
+    const uint32_t never_flag = base + G::misc_off + 8;
+    float* sx = reinterpret_cast<float*>(base_ptr + G::sx_off);
+    const uint32_t sx_u32 = base + G::sx_off;
+    auto bar = [&](int slot) -> uint32_t { return bars + 8u * (uint32_t)slot; };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int live_warps = 4 * p.live_chunks;
+    constexpr int PW = G::PROMO_WARPS, MW = G::PROMO_WARPS + 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kSkStages; ++s) {
+            mbar_init(bar(G::FULL_AB + s), 1);
+            // a stage is free again when its MMAs have completed and every promotion warp has read its scales
+            mbar_init(bar(G::EMPTY_AB + s), 1 + live_warps);
+        }
+        for (int b = 0; b < G::NBUF; ++b) {
+            mbar_init(bar(G::ACC_FULL + b), 1);
+            mbar_init(bar(G::ACC_EMPTY + b), live_warps);
+        }
+        sts_u32(abort_flag, 0u);
+        sts_u32(never_flag, 0u);
+        mbar_fence_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == MW) {
+        tmem_alloc(smem_u32((const void*)tmem_holder), G::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    const long long s_begin = range_start(blockIdx.x, p.total_stages, gridDim.x);
+    const long long s_end = range_start((long long)blockIdx.x + 1, p.total_stages, gridDim.x);
+
+    if (warp == PW) {
+        // ---------------- TMA producer ----------------
+        int stage = 0;
+        uint32_t phase = 0;
+        int last_parity[kSkStages];
+#pragma unroll
+        for (int s = 0; s < kSkStages; ++s) last_parity[s] = -1;
+        bool ok = true;
+        for (long long s = s_begin; s < s_end; ++s) {
+            const int tile = (int)(s / p.nks), ks = (int)(s - (long long)tile * p.nks);
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(G::EMPTY_AB + stage), phase ^ 1u, abort_flag));
+            if (!ok) {
+                if (lane == 0) report_timeout(p.status, abort_flag, W_EMPTY_AB);
+                break;
+            }
+            if (lane == 0) {
+                const uint32_t dst = base + (uint32_t)stage * G::STAGE_BYTES;
+                mbar_expect_tx(bar(G::FULL_AB + stage), G::W_BYTES + G::X_BYTES + G::S_TX);
+                tma_load_2d(dst, &tmW, bar(G::FULL_AB + stage), ks * kBK, tile * kTileRows);
+                tma_load_2d(dst + G::W_BYTES, &tmX, bar(G::FULL_AB + stage), ks * kBK, 0);
+                tma_load_2d(dst + G::W_BYTES + G::X_BYTES, &tmS, bar(G::FULL_AB + stage), tile * kTileRows, ks * G::BPS);
+            }
+            __syncwarp();
+#pragma unroll
+            for (int q = 0; q < kSkStages; ++q)
+                if (q == stage) last_parity[q] = (int)phase;
+            if (++stage == kSkStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) {
+            // do not leave while our own copies may still land in this CTA's shared memory
+#pragma unroll
+            for (int q = 0; q < kSkStages; ++q)
+                if (last_parity[q] >= 0) (void)mbar_wait(bar(G::FULL_AB + q), (uint32_t)last_parity[q], never_flag, 200000000ll);
+        }
+    } else if (warp == MW) {
+        // ---------------- MMA issuer ----------------
+        constexpr uint32_t idesc = umma_idesc_i8(kTileRows, BNS);
+        int stage = 0, buf = 0;
+        uint32_t phase = 0, accphase = 0;
+        for (long long s = s_begin; s < s_end; ++s) {
+            const int tile = (int)(s / p.nks), ks = (int)(s - (long long)tile * p.nks);
+            bool ok = __all_sync(0xffffffffu, mbar_wait(bar(G::FULL_AB + stage), phase, abort_flag));
+            if (!ok) {
+                if (lane == 0) report_timeout(p.status, abort_flag, W_FULL_AB);
+                break;
+            }
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(G::ACC_EMPTY + buf), accphase ^ 1u, abort_flag));
+            if (!ok) {
+                if (lane == 0) report_timeout(p.status, abort_flag, W_ACC_EMPTY);
+                break;
+            }
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t st_base = base + (uint32_t)stage * G::STAGE_BYTES;
+                const uint64_t wdesc = umma_desc_k_sw128(st_base);
+                const uint64_t xdesc = umma_desc_k_sw128(st_base + G::W_BYTES);
+#pragma unroll
+                for (int blk = 0; blk < G::BPS; ++blk) {
+                    if (ks * G::BPS + blk < p.nb) {
+#pragma unroll
+                        for (int i = 0; i < G::MMAS; ++i) {
+                            const uint64_t koff = (uint64_t)((blk * G::MMAS + i) * 32 / 16);
+                            mma_i8(tmem_base + (uint32_t)(buf * G::ACC_STRIDE + blk * BNS), wdesc + koff, xdesc + koff, idesc,
+                                   i > 0 ? 1u : 0u);
+                        }
+                    }
+                }
+                tc_commit(bar(G::ACC_FULL + buf));
+                tc_commit(bar(G::EMPTY_AB + stage));
+            }
+            __syncwarp();
+            if (++stage == kSkStages) { stage = 0; phase ^= 1u; }
+            if (++buf == G::NBUF) { buf = 0; accphase ^= 1u; }
+        }
+    } else if ((warp >> 2) < p.live_chunks) {
+        // ---------------- promotion + epilogue: warp = 4 * chunk + lane quarter ----------------
+        const int quarter = warp & 3, chunk = warp >> 2;
+        const int row = quarter * 32 + lane;                       // weight row inside the tile
+        const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(chunk * 16);
+        const float div = 1.0f / (127.0f * 127.0f);
+
+        // activation scales of all blocks, zero beyond the valid rows: [nb][BNS]
+        {
+            const int nthreads = live_warps * 32;
+            const int total = p.nb * BNS;
+            for (int i = threadIdx.x; i < total; i += nthreads) {
+                const int j = i / BNS, m = i % BNS;
+                sx[i] = (m < p.M) ? __ldg(p.sA + (int64_t)j * p.M + m) : 0.0f;
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+        }
+
+        int stage = 0, buf = 0;
+        uint32_t phase = 0, accphase = 0;
+        bool ok = true;
+        for (long long s = s_begin; s < s_end && ok;) {
+            const int tile = (int)(s / p.nks), ks0 = (int)(s - (long long)tile * p.nks);
+            const long long left = s_end - s;
+            const int len = (long long)(p.nks - ks0) < left ? (p.nks - ks0) : (int)left;
+            const int ks1 = ks0 + len;
+            float acc[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[i] = 0.0f;
+
+            for (int ks = ks0; ks < ks1; ++ks) {
+                // the stage's barrier is waited on here as well: this warp reads the scales the TMA wrote
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(G::FULL_AB + stage), phase, abort_flag));
+                if (!ok) {
+                    if (lane == 0) report_timeout(p.status, abort_flag, W_FULL_AB);
+                    break;
+                }
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(G::ACC_FULL + buf), accphase, abort_flag));
+                if (!ok) {
+                    if (lane == 0) report_timeout(p.status, abort_flag, W_ACC_FULL);
+                    break;
+                }
+                tc_fence_after();
+                uint32_t v[G::BPS][16];
+                float sw[G::BPS];
+                const uint32_t sc_u32 = base + (uint32_t)stage * G::STAGE_BYTES + G::W_BYTES + G::X_BYTES + (uint32_t)(row * 4);
+#pragma unroll
+                for (int blk = 0; blk < G::BPS; ++blk) {
+                    tmem_ld16(t_lane + (uint32_t)(buf * G::ACC_STRIDE + blk * BNS), v[blk]);
+                    sw[blk] = lds_f32(sc_u32 + (uint32_t)(blk * kTileRows * 4));
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(G::EMPTY_AB + stage));       // scales are in registers
+                tmem_wait_ld();
+#pragma unroll
+                for (int blk = 0; blk < G::BPS; ++blk) {
+                    const int j = ks * G::BPS + blk;
+                    if (j < p.nb) {
+                        const uint32_t sxa = sx_u32 + (uint32_t)((j * BNS + chunk * 16) * 4);
+#pragma unroll
+                        for (int q = 0; q < 2; ++q) {
+                            uint64_t a0, a1, a2, a3;
+                            lds_2xb64(sxa + (uint32_t)(q * 32), a0, a1);
+                            lds_2xb64(sxa + (uint32_t)(q * 32 + 16), a2, a3);
+                            float sv[8];
+                            unpack_f32x2(a0, sv[0], sv[1]);
+                            unpack_f32x2(a1, sv[2], sv[3]);
+                            unpack_f32x2(a2, sv[4], sv[5]);
+                            unpack_f32x2(a3, sv[6], sv[7]);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                // the reference's order for one term: sB * (sA * (float(P) * 1/127^2))
+                                const float pf = __fmul_rn((float)(int32_t)v[blk][q * 8 + i], div);
+                                acc[q * 8 + i] = __fadd_rn(acc[q * 8 + i], __fmul_rn(sw[blk], __fmul_rn(sv[i], pf)));
+                            }
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(G::ACC_EMPTY + buf));
+                if (++stage == kSkStages) { stage = 0; phase ^= 1u; }
+                if (++buf == G::NBUF) { buf = 0; accphase ^= 1u; }
+            }
+            if (!ok) break;
+
+            const int n = tile * kTileRows + row;
+            if (ks0 == 0 && ks1 == p.nks) {
+                if (n < p.N) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int m = chunk * 16 + i;
+                        if (m < p.M) finish_store(acc[i], m, n, p.bias, p.bias_dtype, p.C, p.ldc, p.out_dtype);
+                    }
+                }
+            } else {
+                // part of a tile: slot 0 of this CTA if the part begins where the CTA's range begins, else slot 1
+                const long long slot = 2ll * blockIdx.x + (s == s_begin ? 0 : 1);
+                float* w = p.ws + (slot * BNS + chunk * 16) * kTileRows + row;
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                    if (chunk * 16 + i < p.M) w[i * kTileRows] = acc[i];
+            }
+            s += len;
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == MW) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, G::TMEM_COLS);
+    }
+}
+
+// Adds the parts of divided tiles in ascending K order and writes C; tiles that one CTA covered completely were
+// already written by it.  One thread per output element (a thread per tile row with a loop over the activation rows
+// serialises the loads and is several times slower); `ctas` and `total_stages` are those of the GEMM launch, bns its BNS.
+__global__ void __launch_bounds__(256) skinny_reduce_kernel(const float* __restrict__ ws, long long total_stages, int ctas,
+                                                            int nks, int bns, const void* __restrict__ bias, int bias_dtype,
+                                                            void* __restrict__ C, int64_t ldc, int out_dtype, int M, int N) {
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= (int64_t)M * N) return;
+    const int m = (int)(i / N), n = (int)(i % N);
+    const int tile = n / kTileRows, row = n % kTileRows;
+    const long long t0 = (long long)tile * nks, t1 = t0 + nks;
+    long long c0 = t0 * ctas / total_stages;
+    while (c0 + 1 < ctas && range_start(c0 + 1, total_stages, ctas) <= t0) ++c0;
+    while (c0 > 0 && range_start(c0, total_stages, ctas) > t0) --c0;
+    // the tile's parts belong to CTAs c0, c0 + 1, ...; a part that begins where its CTA's range begins is that CTA's
+    // slot 0, and only the first part of a tile can begin elsewhere (at the tile's first stage, inside the range of c0)
+    const long long cs0 = range_start(c0, total_stages, ctas);
+    long long ce = range_start(c0 + 1, total_stages, ctas);
+    if (cs0 <= t0 && ce >= t1) return;                       // whole tile inside one range: written by the GEMM
+    float acc = ws[((2 * c0 + (cs0 < t0 ? 1 : 0)) * bns + m) * kTileRows + row];
+    for (long long c = c0 + 1; ce < t1; ++c) {
+        acc = __fadd_rn(acc, ws[(2 * c * bns + m) * kTileRows + row]);
+        ce = range_start(c + 1, total_stages, ctas);
+    }
+    finish_store(acc, m, n, bias, bias_dtype, C, ldc, out_dtype);
+}
+
+template <int QB, int BNS>
+size_t skinny_smem_bytes(int nb) {
+    return (size_t)SkGeo<QB, BNS>::sx_off + (size_t)nb * BNS * 4 + 1024;
+}
+
+template <int QB, int BNS>
+int launch_skinny(const GemmArgs& g, const SkParams& p, int grid, cudaStream_t st) {
+    using G = SkGeo<QB, BNS>;
+    CUtensorMap mw, mx, ms;
+    int rc = make_operand_map(&mw, g.Bt, g.N, g.K, g.ldb, kTileRows);
+    if (rc != BI8_OK) return rc;
+    rc = make_operand_map(&mx, g.A, g.M, g.K, g.lda, BNS);
+    if (rc != BI8_OK) return rc;
+    rc = make_scale_map(&ms, g.sB, p.nb, g.N, kTileRows, G::BPS);
+    if (rc != BI8_OK) return rc;
+    const size_t smem = skinny_smem_bytes<QB, BNS>(p.nb);
+    BI8_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_skinny_kernel<QB, BNS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    gemm_tc_skinny_kernel<QB, BNS><<<grid, G::THREADS, smem, st>>>(mw, mx, ms, p);
+    BI8_CUDA_TRY(cudaGetLastError());
+    return BI8_OK;
+}
+
+int bns_for(int64_t M) { return M <= 16 ? 16 : 32; }
+
+// conditions that depend on the shape only (the workspace query knows nothing else)
+bool skinny_shape_ok(int64_t M, int64_t N, int64_t K, int block) {
+    if (M < 1 || M > kSkMaxM || N < 1 || K < 1) return false;
+    if (block != 32 && block != 64 && block != 128) return false;
+    if (N % 4 != 0 || N >= (1ll << 30) || K >= (1ll << 30)) return false;
+    const int64_t nb = (K + block - 1) / block;
+    return (size_t)nb * bns_for(M) * 4 <= kSxMaxBytes;
+}
+
+}  // namespace
+
+size_t gemm_skinny_workspace_bytes(const GemmArgs& g) {
+    const DeviceInfo di = device_info();
+    if (!di.ok || g.partials != nullptr || !skinny_shape_ok(g.M, g.N, g.K, g.block)) return 0;
+    return (size_t)2 * di.sms * bns_for(g.M) * kTileRows * 4;
+}
+
+bool gemm_skinny_applicable(const GemmArgs& g) {
+    if (g.partials != nullptr || !skinny_shape_ok(g.M, g.N, g.K, g.block)) return false;
+    if (!device_info().ok) return false;
+    if (!aligned(g.A, 16) || !aligned(g.Bt, 16) || g.lda % 16 != 0 || g.ldb % 16 != 0) return false;
+    if (!aligned(g.sB, 16)) return false;
+    const size_t need = gemm_skinny_workspace_bytes(g);
+    return g.workspace != nullptr && g.workspace_bytes >= need && aligned(g.workspace, 16);
+}
+
+int launch_gemm_skinny(const GemmArgs& g, cudaStream_t st) {
+    const DeviceInfo di = device_info();
+    if (!di.ok) return fail(BI8_ERR_CUDA, "tensor-core GEMM needs a compute capability 10.x device");
+    SkParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.sA = g.sA;
+    p.bias = g.bias;
+    p.C = g.C;
+    p.ws = static_cast<float*>(g.workspace);
+    p.status = device_status_ptr();
+    if (!p.status) return BI8_ERR_CUDA;
+    p.ldc = g.ldc;
+    p.M = (int)g.M;
+    p.N = (int)g.N;
+    p.K = (int)g.K;
+    p.nb = (int)((g.K + g.block - 1) / g.block);
+    p.nks = (int)((g.K + kBK - 1) / kBK);
+    p.out_dtype = g.out_dtype;
+    p.bias_dtype = g.bias_dtype;
+    p.live_chunks = (int)((g.M + 15) / 16);
+    const long long tiles = (g.N + kTileRows - 1) / kTileRows;
+    p.total_stages = tiles * p.nks;
+    const int grid = (int)(p.total_stages < di.sms ? p.total_stages : di.sms);
+    const int bns = bns_for(g.M);
+    int rc;
+#define BI8_SK(QB)                                                                       \
+    rc = bns == 16 ? launch_skinny<QB, 16>(g, p, grid, st) : launch_skinny<QB, 32>(g, p, grid, st)
+    switch (g.block) {
+        case 32: BI8_SK(32); break;
+        case 64: BI8_SK(64); break;
+        case 128: BI8_SK(128); break;
+        default: return fail(BI8_ERR_BLOCK, "tensor-core GEMM supports block 32, 64, 128 (got %d)", g.block);
+    }
+#undef BI8_SK
+    if (rc != BI8_OK) return rc;
+    if (p.total_stages % grid == 0 && (p.total_stages / grid) % p.nks == 0) return BI8_OK;   // no tile is divided
+    const int64_t total = g.M * g.N;
+    skinny_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(p.ws, p.total_stages, grid, p.nks, bns, g.bias,
+                                                                          g.bias_dtype, g.C, g.ldc, g.out_dtype, (int)g.M,
+                                                                          (int)g.N);
+    BI8_CUDA_TRY(cudaGetLastError());
+    return BI8_OK;
+}
+
+}  // namespace bi8

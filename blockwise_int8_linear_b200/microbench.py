@@ -29,6 +29,7 @@ def main():
     ap.add_argument("--reps", type=int, default=7)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--flags", type=int, default=0, help="GEMM kernel selection flags (BI8_GEMM_* in include/bi8.h)")
     a = ap.parse_args()
     from blockwise_int8_linear_b200 import block_linear_config as cfg
     from blockwise_int8_linear_b200 import triton_functions as F
@@ -43,7 +44,7 @@ def main():
         wq = torch.randint(-127, 128, (n, k), dtype=torch.int8, device=dev, generator=g)
         xs = torch.rand((nb, m), device=dev, generator=g) + 0.5
         ws = torch.rand((nb, n), device=dev, generator=g) + 0.5
-        fn = lambda: F.int8_matmul_block64_rowwise_dequantize(xq, wq.t(), xs, ws)
+        fn = lambda: F.int8_matmul_block64_rowwise_dequantize(xq, wq.t(), xs, ws, flags=a.flags)
         work = 2.0 * m * n * k
         nbytes = m * k + n * k + 4 * (m + n) * nb + 2 * m * n
     else:

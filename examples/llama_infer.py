@@ -32,6 +32,7 @@ if ROOT not in sys.path:
 
 import block_linear_config as cfg  # noqa: E402
 from block_linear import BlockInt8Linear  # noqa: E402
+from triton_functions import int8_matmul_block64_rowwise_dequantize, quantize_block_rowwise  # noqa: E402
 from blockwise_int8_linear_b200.parallel import block_aligned_bounds  # noqa: E402
 
 
@@ -78,21 +79,29 @@ class Int8Linear(nn.Module):
         dist.all_reduce(part)
         return part.to(prev)
 
+    def forward_quantized(self, xq, xs, lead):
+        """Column-parallel layers that share one input (q/k/v, gate/up) share its quantization: the same two calls
+        BlockInt8Linear.infer makes (reference block_linear.py:141-143), with the first one hoisted by the caller."""
+        assert self.mode == "col" or self.world == 1
+        y = int8_matmul_block64_rowwise_dequantize(xq, self.lin.W_int8.t(), xs, self.lin.state_W, self.lin.bias)
+        return y.view(*lead, -1)
+
 
 def rms_norm(x, eps=1e-5):
-    xf = x.float()
-    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)
+    return F.rms_norm(x, (x.shape[-1],), eps=eps)
 
 
-def rope(x, pos, theta=10000.0):
-    # x [B, H, T, D]; pos [T] (a device tensor, so that a captured decode step can advance it in place)
-    d = x.shape[-1]
-    inv = 1.0 / (theta ** (torch.arange(0, d, 2, device=x.device, dtype=torch.float32) / d))
-    ang = pos.float()[:, None] * inv[None, :]
-    cos, sin = ang.cos()[None, None], ang.sin()[None, None]
-    x1, x2 = x.float()[..., 0::2], x.float()[..., 1::2]
-    out = torch.stack((x1 * cos - x2 * sin, x1 * sin + x2 * cos), dim=-1).flatten(-2)
-    return out.to(x.dtype)
+def rope_table(max_len, d, dev, theta=10000.0):
+    """cos/sin of every position as one complex table [max_len, d/2], built once."""
+    inv = 1.0 / (theta ** (torch.arange(0, d, 2, device=dev, dtype=torch.float32) / d))
+    ang = torch.arange(max_len, device=dev, dtype=torch.float32)[:, None] * inv[None, :]
+    return torch.polar(torch.ones_like(ang), ang)
+
+
+def rope(x, cis):
+    # x [B, H, T, D] with (even, odd) feature pairs rotated by the position's angle; cis [T, D/2] complex
+    xc = torch.view_as_complex(x.float().reshape(*x.shape[:-1], -1, 2))
+    return torch.view_as_real(xc * cis[None, None]).flatten(-2).to(x.dtype)
 
 
 class Layer(nn.Module):
@@ -108,35 +117,33 @@ class Layer(nn.Module):
         self.head_dim = a.head_dim
         self.kcache = self.vcache = None
 
-    def forward(self, x, pos0, max_len, pos_dev=None):
+    def forward(self, x, pos0, max_len, cis, mask=None, pos_dev=None):
         """Prefill: pos0 is a Python int and the cache is sliced.  Decode (pos_dev given, T == 1): the position is a device
         tensor, the cache is written with index_copy_ and attended in full under a mask, so that every shape is static and
-        the step can be captured in a CUDA graph."""
+        the step can be captured in a CUDA graph.  `cis` holds the rotary factors of this call's positions."""
         B, T, _ = x.shape
-        h = rms_norm(x)
-        q = self.q(h).view(B, T, self.heads_local, self.head_dim).transpose(1, 2)
-        k = self.k(h).view(B, T, self.heads_local, self.head_dim).transpose(1, 2)
-        v = self.v(h).view(B, T, self.heads_local, self.head_dim).transpose(1, 2)
+        hq, hs = quantize_block_rowwise(rms_norm(x).view(B * T, -1))       # one quantization feeds q, k and v
+        heads = (B, T, self.heads_local, self.head_dim)
+        q = self.q.forward_quantized(hq, hs, (B, T)).view(heads).transpose(1, 2)
+        k = self.k.forward_quantized(hq, hs, (B, T)).view(heads).transpose(1, 2)
+        v = self.v.forward_quantized(hq, hs, (B, T)).view(heads).transpose(1, 2)
         if self.kcache is None:
             self.kcache = torch.zeros((B, self.heads_local, max_len, self.head_dim), device=x.device, dtype=x.dtype)
             self.vcache = torch.zeros_like(self.kcache)
+        q, k = rope(q, cis), rope(k, cis)
         if pos_dev is None:
-            pos = torch.arange(pos0, pos0 + T, device=x.device)
-            q, k = rope(q, pos), rope(k, pos)
             self.kcache[:, :, pos0:pos0 + T] = k
             self.vcache[:, :, pos0:pos0 + T] = v
             kk, vv = self.kcache[:, :, :pos0 + T], self.vcache[:, :, :pos0 + T]
             att = F.scaled_dot_product_attention(q, kk, vv, is_causal=(T > 1))
         else:
-            q, k = rope(q, pos_dev), rope(k, pos_dev)
             self.kcache.index_copy_(2, pos_dev, k)
             self.vcache.index_copy_(2, pos_dev, v)
-            mask = (torch.arange(max_len, device=x.device) <= pos_dev).view(1, 1, 1, max_len)
             att = F.scaled_dot_product_attention(q, self.kcache, self.vcache, attn_mask=mask)
         att = att.transpose(1, 2).reshape(B, T, self.heads_local * self.head_dim)
         x = x + self.o(att)
-        h = rms_norm(x)
-        x = x + self.down(F.silu(self.gate(h)) * self.up(h))
+        hq, hs = quantize_block_rowwise(rms_norm(x).view(B * T, -1))       # ... and one feeds gate and up
+        x = x + self.down(F.silu(self.gate.forward_quantized(hq, hs, (B, T))) * self.up.forward_quantized(hq, hs, (B, T)))
         return x
 
 
@@ -148,12 +155,19 @@ class Llama(nn.Module):
         self.layers = nn.ModuleList(Layer(i, a, dev, rank, world) for i in range(a.layers))
         self.head = Int8Linear(a.hidden, a.vocab, 99, dev, "col", rank, world, a.block)
         self.world, self.vocab, self.block = world, a.vocab, a.block
+        self.cis = rope_table(a.prompt + a.decode, a.head_dim, dev)
+        self.positions = torch.arange(a.prompt + a.decode, device=dev)
 
     @torch.no_grad()
     def forward(self, ids, pos0, max_len, pos_dev=None):
         x = self.emb[ids]
+        if pos_dev is None:
+            cis, mask = self.cis[pos0:pos0 + ids.shape[1]], None
+        else:
+            cis = self.cis.index_select(0, pos_dev)
+            mask = (self.positions[:max_len] <= pos_dev).view(1, 1, 1, max_len)
         for layer in self.layers:
-            x = layer(x, pos0, max_len, pos_dev)
+            x = layer(x, pos0, max_len, cis, mask, pos_dev)
         logits = self.head(rms_norm(x[:, -1:]))                    # [B, 1, V_local]
         if self.world > 1:
             sizes = [hi - lo for lo, hi in block_aligned_bounds(self.vocab, self.world, self.block)]
@@ -195,6 +209,7 @@ def main():
     model = Llama(a, dev, rank, world)
     ids = torch.randint(0, a.vocab, (a.batch, a.prompt), generator=torch.Generator().manual_seed(4000)).to(dev)
     max_len = a.prompt + a.decode
+    model(ids[:, :16], 0, max_len)                                # warm-up (lazy initialisation, allocator)
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     logits = model(ids, 0, max_len)

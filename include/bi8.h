@@ -58,6 +58,7 @@ extern "C" {
 #define BI8_GEMM_FORCE_TC 2        /* fail with BI8_ERR_ALIGN instead of falling back */
 #define BI8_GEMM_NO_SEED 4         /* tensor-core kernel: convert partial sums with cvt instead of seeded TMEM */
 #define BI8_GEMM_FORCE_SMALLM 8    /* weight-streaming CUDA-core kernel, M <= 16 (the default choice for M <= 8) */
+#define BI8_GEMM_FORCE_SKINNY 16   /* weight-streaming tensor-core kernel with exchanged operand roles, M <= 32 */
 
 BI8_API int bi8_version(void);
 

@@ -259,13 +259,48 @@ def test_small_m_weight_streaming_kernel(shape):
     _check_fp32(_gemm(xq, wq, xs, ws, flags=SMALLM), xq, wq, xs, ws, block)
     _check_fp32(_gemm(xq, wq, xs, ws, bias, flags=SMALLM), xq, wq, xs, ws, block, bias)
     if m <= 8:
-        assert torch.equal(_gemm(xq, wq, xs, ws), _gemm(xq, wq, xs, ws, flags=SMALLM)), "default dispatch for M <= 8"
+        # default dispatch: the skinny tensor-core kernel where it applies (N % 4 == 0), else this kernel
+        chosen = 16 if n % 4 == 0 else SMALLM
+        assert torch.equal(_gemm(xq, wq, xs, ws), _gemm(xq, wq, xs, ws, flags=chosen)), "default dispatch for M <= 8"
     set_config(block, torch.bfloat16)
     _check_bf16(_gemm(xq, wq, xs, ws, bias, flags=SMALLM), xq, wq, xs, ws, block, bias)
     from blockwise_int8_linear_b200._lib import Bi8Error
     with pytest.raises(Bi8Error):
         big = quantized_pair(17, 128, 32, block, seed=1)
         _gemm(big[0], big[2], big[1], big[3], flags=SMALLM)
+    assert_clean_device()
+    set_config(64)
+
+
+SKINNY = 16
+SKINNY_SHAPES = [
+    # (M, K, N, block): N % 4 == 0, K % 16 == 0; tiles both divided over CTAs and undivided, K and N tails
+    (1, 64, 4, 64), (1, 4096, 512, 64), (5, 1056, 76, 64), (8, 2048, 1000, 64), (9, 256, 260, 64), (16, 4096, 1024, 64),
+    (3, 192, 36, 32), (8, 1056, 132, 32), (16, 2048, 256, 128), (7, 416, 52, 128), (2, 11008, 64, 64),
+    (17, 512, 384, 64), (32, 4096, 640, 64), (25, 1056, 260, 32), (32, 2048, 128, 128), (8, 4096, 11008, 64),
+    (4, 128, 40000, 64), (12, 80, 24, 32),
+]
+
+
+@pytest.mark.parametrize("shape", SKINNY_SHAPES)
+def test_skinny_tensor_core_kernel(shape):
+    """M <= 32 (decode): tensor-core kernel with exchanged operand roles.  Terms are evaluated in the reference's order;
+    a tile whose K range is divided over CTAs adds its parts in a fixed order, so the tensor-core tolerance applies and
+    repeated calls are bit-identical."""
+    m, k, n, block = shape
+    xq, xs, wq, ws = quantized_pair(m, k, n, block, seed=13 * m + k + n)
+    bias = torch.randn(n, generator=torch.Generator().manual_seed(n)).to(torch.bfloat16)
+    set_config(block, torch.float32)
+    first = _gemm(xq, wq, xs, ws, flags=SKINNY)
+    _check_fp32(first, xq, wq, xs, ws, block)
+    assert torch.equal(first, _gemm(xq, wq, xs, ws, flags=SKINNY)), "deterministic"
+    _check_fp32(_gemm(xq, wq, xs, ws, bias, flags=SKINNY), xq, wq, xs, ws, block, bias)
+    set_config(block, torch.bfloat16)
+    _check_bf16(_gemm(xq, wq, xs, ws, bias, flags=SKINNY), xq, wq, xs, ws, block, bias)
+    from blockwise_int8_linear_b200._lib import Bi8Error
+    with pytest.raises(Bi8Error):
+        big = quantized_pair(33, 128, 32, block, seed=1)
+        _gemm(big[0], big[2], big[1], big[3], flags=SKINNY)
     assert_clean_device()
     set_config(64)
 

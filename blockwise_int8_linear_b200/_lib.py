@@ -15,14 +15,14 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libbi8.so")
 
 BI8_BF16, BI8_F32, BI8_F16 = 0, 1, 2
-GEMM_DEFAULT, GEMM_FORCE_GENERIC, GEMM_FORCE_TC, GEMM_NO_SEED, GEMM_FORCE_SMALLM = 0, 1, 2, 4, 8
+GEMM_DEFAULT, GEMM_FORCE_GENERIC, GEMM_FORCE_TC, GEMM_NO_SEED, GEMM_FORCE_SMALLM, GEMM_FORCE_SKINNY = 0, 1, 2, 4, 8, 16
 
 _DTYPE_CODE = {torch.bfloat16: BI8_BF16, torch.float32: BI8_F32, torch.float16: BI8_F16}
 
 EXPORTS = [
     "bi8_version", "bi8_last_error_string", "bi8_device_status", "bi8_quantize_rowwise", "bi8_quantize_colwise",
     "bi8_dequantize_rowwise", "bi8_gemm_dequant", "bi8_gemm_workspace_bytes", "bi8_gemm_block_partials",
-    "bi8_linear_forward", "bi8_mma_peak_probe", "bi8_gemm_dequant_static", "bi8_gemm_static_scratch_bytes",
+    "bi8_linear_forward", "bi8_gemm_dequant_fused_quant", "bi8_mma_peak_probe", "bi8_gemm_dequant_static", "bi8_gemm_static_scratch_bytes",
 ]
 
 _lib = None
@@ -54,6 +54,7 @@ def lib() -> ctypes.CDLL:
         L.bi8_gemm_block_partials.argtypes = [vp, i64, vp, i64, vp, i64, i64, i64, i32, i32, vp]
         L.bi8_linear_forward.argtypes = [vp, i32, i64, vp, vp, vp, i64, vp, vp, i32, vp, i64, i32, i64, i64, i64, i32, vp, sz,
                                          i32, vp]
+        L.bi8_gemm_dequant_fused_quant.argtypes = L.bi8_linear_forward.argtypes
         L.bi8_mma_peak_probe.argtypes = [i32, c.POINTER(c.c_float), c.POINTER(i32)]
         for name in EXPORTS:
             fn = getattr(L, name)
@@ -82,6 +83,25 @@ def ptr(t) -> ctypes.c_void_p:
 
 def stream_ptr() -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+_workspaces: dict = {}
+
+
+def workspace(device: torch.device, nbytes: int):
+    """GEMM workspace of at least ``nbytes`` for (device, current stream), or None for 0 bytes.
+
+    The workspace is scratch for split-K partial results; one buffer per stream is reused by all GEMMs queued on that
+    stream (they run one after the other), which saves an allocator round trip per call.  A larger request replaces
+    the buffer."""
+    if nbytes <= 0:
+        return None
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 2 * ws.numel() if ws is not None else 0), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
 
 
 def device_status() -> int:

@@ -15,6 +15,7 @@ from .triton_functions import (
     int8_matmul_block64_rowwise_dequantize,
     quantize_block_colwise,
     quantize_block_rowwise,
+    quantize_matmul_block_rowwise_dequantize,
 )
 
 __all__ = [
@@ -123,6 +124,9 @@ class BlockInt8Linear(nn.Linear):
         if not hasattr(self, "W_int8"):
             self.prepare_for_eval()
         X = x.reshape(-1, x.size(-1))
+        if X.size(0) <= 32:
+            # decode-sized batches: the same two steps in one kernel (the GEMM quantizes the activations as it loads them)
+            return quantize_matmul_block_rowwise_dequantize(X, self.W_int8.t(), self.state_W, self.bias).view(*x.size()[:-1], -1)
         X_int8, state_X = quantize_block_rowwise(X)
         return int8_matmul_block64_rowwise_dequantize(
             X_int8, self.W_int8.t(), state_X, self.state_W, self.bias

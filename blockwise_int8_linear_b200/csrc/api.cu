@@ -182,13 +182,40 @@ int bi8_gemm_block_partials(const int8_t* A, int64_t lda, const int8_t* Bt, int6
     return dispatch_gemm(g, static_cast<cudaStream_t>(stream));
 }
 
-int bi8_linear_forward(const void* x, int x_dtype, int64_t ldx, int8_t* xq, float* sx, const int8_t* Wq, int64_t ldw,
-                       const float* sW, const void* bias, int bias_dtype, void* C, int64_t ldc, int out_dtype, int64_t M,
-                       int64_t N, int64_t K, int block, void* workspace, size_t workspace_bytes, int flags, void* stream) {
+int bi8_gemm_dequant_fused_quant(const void* x, int x_dtype, int64_t ldx, int8_t* xq, float* sx, const int8_t* Wq, int64_t ldw,
+                                 const float* sW, const void* bias, int bias_dtype, void* C, int64_t ldc, int out_dtype,
+                                 int64_t M, int64_t N, int64_t K, int block, void* workspace, size_t workspace_bytes, int flags,
+                                 void* stream) {
+    // one kernel where the skinny tensor-core GEMM applies (it quantizes the activations as it loads them) ...
+    if (!dtype_ok(x_dtype)) return fail(BI8_ERR_DTYPE, "gemm_dequant_fused_quant: unknown dtype code %d", x_dtype);
+    const bool forced = (flags & (BI8_GEMM_FORCE_GENERIC | BI8_GEMM_FORCE_TC | BI8_GEMM_FORCE_SMALLM)) != 0;
+    if (!forced && x && M > 0 && N > 0 && K > 0 && ldx >= K && aligned(x, dtype_size(x_dtype))) {
+        GemmArgs g{nullptr, K, Wq, ldw, nullptr, sW, bias, bias_dtype, C, ldc, out_dtype, nullptr, M, N, K, block, flags, workspace, workspace_bytes};
+        g.X = x;
+        g.x_dtype = x_dtype;
+        g.ldx = ldx;
+        if (gemm_skinny_applicable(g)) {
+            if (!Wq || !sW || !C) return fail(BI8_ERR_NULL, "gemm_dequant_fused_quant: null pointer");
+            if (ldw < K || ldc < N) return fail(BI8_ERR_SHAPE, "gemm_dequant_fused_quant: row pitch smaller than the row");
+            if (!dtype_ok(out_dtype) || (bias && !dtype_ok(bias_dtype))) return fail(BI8_ERR_DTYPE, "gemm_dequant_fused_quant: unknown dtype code");
+            if (!aligned(C, dtype_size(out_dtype))) return fail(BI8_ERR_ALIGN, "gemm_dequant_fused_quant: output not element aligned");
+            return launch_gemm_skinny(g, static_cast<cudaStream_t>(stream));
+        }
+    }
+    // ... two kernels otherwise, through the caller's scratch
+    if (M > 0 && K > 0 && (!xq || !sx))
+        return fail(BI8_ERR_WORKSPACE, "gemm_dequant_fused_quant: this shape runs as quantize + GEMM and needs the xq / sx scratch");
     int rc = bi8_quantize_rowwise(x, x_dtype, ldx, xq, sx, M, K, block, stream);
     if (rc != BI8_OK) return rc;
     return bi8_gemm_dequant(xq, K, Wq, ldw, sx, sW, bias, bias_dtype, C, ldc, out_dtype, M, N, K, block, workspace,
-                            workspace_bytes, flags, stream);
+                            workspace_bytes, flags & ~BI8_GEMM_FORCE_SKINNY, stream);
+}
+
+int bi8_linear_forward(const void* x, int x_dtype, int64_t ldx, int8_t* xq, float* sx, const int8_t* Wq, int64_t ldw,
+                       const float* sW, const void* bias, int bias_dtype, void* C, int64_t ldc, int out_dtype, int64_t M,
+                       int64_t N, int64_t K, int block, void* workspace, size_t workspace_bytes, int flags, void* stream) {
+    return bi8_gemm_dequant_fused_quant(x, x_dtype, ldx, xq, sx, Wq, ldw, sW, bias, bias_dtype, C, ldc, out_dtype, M, N, K, block,
+                                        workspace, workspace_bytes, flags, stream);
 }
 
 int bi8_mma_peak_probe(int iters, float* ms, int* sm_count) {

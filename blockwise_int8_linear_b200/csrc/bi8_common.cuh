@@ -48,9 +48,13 @@ struct GemmArgs {
     int64_t M, N, K;
     int block;
     int flags;
-    void* workspace;          // optional scratch of gemm_tc_workspace_bytes() bytes (split-K partial results)
+    void* workspace;          // optional scratch for split-K partial results
     size_t workspace_bytes;
+    const void* X = nullptr;  // non-null: activations before quantization (A and sA unused), quantized on load
+    int x_dtype = 0;
+    int64_t ldx = 0;
 };
+
 bool gemm_tc_applicable(const GemmArgs& g, const char** why);
 size_t gemm_tc_workspace_bytes(const GemmArgs& g);
 int launch_gemm_tc(const GemmArgs& g, cudaStream_t st);

@@ -10,13 +10,19 @@
 //   * All (tile, K stage) pairs form one sequence that is cut into equal contiguous ranges, one per CTA and one CTA
 //     per SM, so every SM streams the same number of bytes whatever N and K are.  A range may begin or end inside a
 //     tile: such a part of a tile goes to an fp32 workspace slot (at most two per CTA) and a second kernel adds the
-//     slots of a tile in ascending K order; tiles that lie completely inside one range are written directly.
+//     slots of a tile in ascending K order; tiles that lie completely inside one range are written directly.  (Adding
+//     the parts inside the GEMM, by whichever CTA finishes a tile last, was measured slower than the second launch: the
+//     fence, the arrival count and the read-back are three dependent trips to L2 at the end of every CTA.)
 //   * warp P (producer) issues, per stage, three TMA copies that complete on one barrier: 128 weight rows x 128
 //     K-bytes, the activation rows of the same K range, and the stage's weight scales (a [blocks, 128] fp32 box of
 //     sB); warp P+1 issues the MMAs of the stage, one accumulator range per quantisation block, and commits;
 //     the promotion warps (four per 16 activation rows, one per tensor-memory lane quarter) convert and scale.
+//   * With FUSED the activations arrive as bf16/fp16/fp32 and four more warps quantize, per stage, the 128 K-columns of
+//     every activation row into the stage's operand tile (same arithmetic as the standalone quantizer, written in the
+//     128-byte swizzle the MMA expects) and their block scales into the scale table: quantize-on-load, no extra launch.
 //   * Promotion follows the reference's order term by term, sB*(sA*(float(P)*fl32(1/127^2))), added in ascending block
 //     order within a range, so a tile that is not divided is bit-identical to the CUDA-core kernel.
+#include "quant_math.cuh"
 #include "tc_common.cuh"
 
 #include <cstring>
@@ -27,7 +33,7 @@ namespace {
 using namespace ptx;
 
 constexpr int kTileRows = 128;    // weight rows per tile (the MMA's M)
-constexpr int kSkStages = 6;      // 6 x 16 KiB of weights in flight per SM
+constexpr int kSkStages = 4;      // 4 x 16 KiB of weights in flight per SM (3, 6 and 10 stages measure the same)
 constexpr int kSkMaxM = 32;
 constexpr size_t kSxMaxBytes = 64 * 1024;   // activation scales staged per CTA
 
@@ -37,13 +43,15 @@ constexpr int pow2_at_least(int x) {
     return p;
 }
 
-template <int QB, int BNS>
+constexpr int kQuantWarps = 4;    // FUSED: warps that quantize the activations of a stage
+
+template <int QB, int BNS, bool FUSED = false>
 struct SkGeo {
     static constexpr int BPS = kBK / QB;                  // quantisation blocks per stage
     static constexpr int MMAS = QB / 32;                  // MMAs (K = 32) per block
     static constexpr int CHUNKS = BNS / 16;               // groups of 16 activation rows
     static constexpr int PROMO_WARPS = 4 * CHUNKS;
-    static constexpr int THREADS = (PROMO_WARPS + 2) * 32;
+    static constexpr int THREADS = (PROMO_WARPS + 2 + (FUSED ? kQuantWarps : 0)) * 32;
     static constexpr int ACC_STRIDE = BPS * BNS;          // tensor-memory columns of one stage's accumulators
     static constexpr int NBUF = (512 / ACC_STRIDE) < 4 ? (512 / ACC_STRIDE) : 4;
     static constexpr int TMEM_COLS = pow2_at_least(NBUF * ACC_STRIDE);
@@ -56,11 +64,14 @@ struct SkGeo {
     static constexpr int FULL_AB = 0, EMPTY_AB = kSkStages, ACC_FULL = 2 * kSkStages, ACC_EMPTY = 2 * kSkStages + NBUF,
                          NBARS = 2 * kSkStages + 2 * NBUF;
     static constexpr uint32_t misc_off = bar_off + NBARS * 8;             // tmem holder, abort flag, never-raised flag
-    static constexpr uint32_t sx_off = (misc_off + 16 + 15) & ~15u;       // activation scales [nb][BNS]
+    static constexpr uint32_t sx_off = (misc_off + 32 + 15) & ~15u;       // activation scales [nb][BNS]
 };
 
 struct SkParams {
     const float* sA;
+    const void* X;          // FUSED: activations before quantization, row pitch ldx elements
+    int64_t ldx;
+    int x_dtype;
     const void* bias;
     void* C;
     float* ws;
@@ -99,11 +110,11 @@ __device__ __forceinline__ void finish_store(float acc, int m, int n, const void
     }
 }
 
-template <int QB, int BNS>
-__global__ void __launch_bounds__(SkGeo<QB, BNS>::THREADS, 1)
+template <int QB, int BNS, bool FUSED>
+__global__ void __launch_bounds__(SkGeo<QB, BNS, FUSED>::THREADS, 1)
 gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                       const __grid_constant__ CUtensorMap tmS, const SkParams p) {
-    using G = SkGeo<QB, BNS>;
+    using G = SkGeo<QB, BNS, FUSED>;
     extern __shared__ __align__(1024) unsigned char smem_dyn[];
     const uint32_t raw = smem_u32(smem_dyn);
     const uint32_t base = (raw + 1023u) & ~1023u;      // the swizzle atom needs 1024-byte alignment
@@ -118,22 +129,48 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int live_warps = 4 * p.live_chunks;
-    constexpr int PW = G::PROMO_WARPS, MW = G::PROMO_WARPS + 1;
+    constexpr int PW = G::PROMO_WARPS, MW = G::PROMO_WARPS + 1, QW0 = G::PROMO_WARPS + 2;
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kSkStages; ++s) {
-            mbar_init(bar(G::FULL_AB + s), 1);
-            // a stage is free again when its MMAs have completed and every promotion warp has read its scales
-            mbar_init(bar(G::EMPTY_AB + s), 1 + live_warps);
+    const long long s_begin = range_start(blockIdx.x, p.total_stages, gridDim.x);
+    const long long s_end = range_start((long long)blockIdx.x + 1, p.total_stages, gridDim.x);
+    // position of the CTA's first stage; every role then steps (tile, ks) by itself, without a division per stage
+    const int tile_begin = (int)(s_begin / p.nks), ks_begin = (int)(s_begin - (long long)tile_begin * p.nks);
+
+    auto issue_stage = [&](int stage, int tile, int ks) {            // one lane
+        const uint32_t dst = base + (uint32_t)stage * G::STAGE_BYTES;
+        mbar_expect_tx(bar(G::FULL_AB + stage), G::W_BYTES + (FUSED ? 0u : G::X_BYTES) + G::S_TX);
+        tma_load_2d(dst, &tmW, bar(G::FULL_AB + stage), ks * kBK, tile * kTileRows);
+        if (!FUSED) tma_load_2d(dst + G::W_BYTES, &tmX, bar(G::FULL_AB + stage), ks * kBK, 0);
+        tma_load_2d(dst + G::W_BYTES + G::X_BYTES, &tmS, bar(G::FULL_AB + stage), tile * kTileRows, ks * G::BPS);
+    };
+
+    // The producer warp sets the barriers up and starts the copies of the first stages right away (the ring is empty, so
+    // nothing has to be waited for); the tensor-memory allocation and the CTA-wide sync overlap their latency.
+    int pre_tile = tile_begin, pre_ks = ks_begin, pre_count = 0;
+    if (warp == PW) {
+        if (lane == 0) {
+            for (int s = 0; s < kSkStages; ++s) {
+                mbar_init(bar(G::FULL_AB + s), FUSED ? 1 + kQuantWarps : 1);   // the TMA's bytes (+ the quantizer warps)
+                // a stage is free again when every promotion warp has seen its accumulator complete (so the MMAs have
+                // read the operands) and has taken its scales
+                mbar_init(bar(G::EMPTY_AB + s), live_warps);
+            }
+            for (int b = 0; b < G::NBUF; ++b) {
+                mbar_init(bar(G::ACC_FULL + b), 1);
+                mbar_init(bar(G::ACC_EMPTY + b), live_warps);
+            }
+            sts_u32(abort_flag, 0u);
+            sts_u32(never_flag, 0u);
+            mbar_fence_init();
+            fence_proxy_async_smem();
         }
-        for (int b = 0; b < G::NBUF; ++b) {
-            mbar_init(bar(G::ACC_FULL + b), 1);
-            mbar_init(bar(G::ACC_EMPTY + b), live_warps);
+        __syncwarp();
+        while (pre_count < kSkStages && s_begin + pre_count < s_end) {
+            if (lane == 0) issue_stage(pre_count, pre_tile, pre_ks);
+            ++pre_count;
+            if (++pre_ks == p.nks) { pre_ks = 0; ++pre_tile; }
         }
-        sts_u32(abort_flag, 0u);
-        sts_u32(never_flag, 0u);
-        mbar_fence_init();
-        fence_proxy_async_smem();
+        __syncwarp();
     }
     if (warp == MW) {
         tmem_alloc(smem_u32((const void*)tmem_holder), G::TMEM_COLS);
@@ -144,36 +181,28 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
 
-    const long long s_begin = range_start(blockIdx.x, p.total_stages, gridDim.x);
-    const long long s_end = range_start((long long)blockIdx.x + 1, p.total_stages, gridDim.x);
-
     if (warp == PW) {
         // ---------------- TMA producer ----------------
-        int stage = 0;
-        uint32_t phase = 0;
+        int stage = pre_count == kSkStages ? 0 : pre_count;
+        uint32_t phase = pre_count == kSkStages ? 1u : 0u;
         int last_parity[kSkStages];
 #pragma unroll
-        for (int s = 0; s < kSkStages; ++s) last_parity[s] = -1;
+        for (int q = 0; q < kSkStages; ++q) last_parity[q] = q < pre_count ? 0 : -1;
+        int tile = pre_tile, ks = pre_ks;
         bool ok = true;
-        for (long long s = s_begin; s < s_end; ++s) {
-            const int tile = (int)(s / p.nks), ks = (int)(s - (long long)tile * p.nks);
+        for (long long s = s_begin + pre_count; s < s_end; ++s) {
             ok = __all_sync(0xffffffffu, mbar_wait(bar(G::EMPTY_AB + stage), phase ^ 1u, abort_flag));
             if (!ok) {
                 if (lane == 0) report_timeout(p.status, abort_flag, W_EMPTY_AB);
                 break;
             }
-            if (lane == 0) {
-                const uint32_t dst = base + (uint32_t)stage * G::STAGE_BYTES;
-                mbar_expect_tx(bar(G::FULL_AB + stage), G::W_BYTES + G::X_BYTES + G::S_TX);
-                tma_load_2d(dst, &tmW, bar(G::FULL_AB + stage), ks * kBK, tile * kTileRows);
-                tma_load_2d(dst + G::W_BYTES, &tmX, bar(G::FULL_AB + stage), ks * kBK, 0);
-                tma_load_2d(dst + G::W_BYTES + G::X_BYTES, &tmS, bar(G::FULL_AB + stage), tile * kTileRows, ks * G::BPS);
-            }
+            if (lane == 0) issue_stage(stage, tile, ks);
             __syncwarp();
 #pragma unroll
             for (int q = 0; q < kSkStages; ++q)
                 if (q == stage) last_parity[q] = (int)phase;
             if (++stage == kSkStages) { stage = 0; phase ^= 1u; }
+            if (++ks == p.nks) { ks = 0; ++tile; }
         }
         if (!ok) {
             // do not leave while our own copies may still land in this CTA's shared memory
@@ -184,18 +213,14 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     } else if (warp == MW) {
         // ---------------- MMA issuer ----------------
         constexpr uint32_t idesc = umma_idesc_i8(kTileRows, BNS);
-        int stage = 0, buf = 0;
+        int stage = 0, buf = 0, ks = ks_begin;
         uint32_t phase = 0, accphase = 0;
         for (long long s = s_begin; s < s_end; ++s) {
-            const int tile = (int)(s / p.nks), ks = (int)(s - (long long)tile * p.nks);
-            bool ok = __all_sync(0xffffffffu, mbar_wait(bar(G::FULL_AB + stage), phase, abort_flag));
-            if (!ok) {
-                if (lane == 0) report_timeout(p.status, abort_flag, W_FULL_AB);
-                break;
-            }
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(G::ACC_EMPTY + buf), accphase ^ 1u, abort_flag));
-            if (!ok) {
-                if (lane == 0) report_timeout(p.status, abort_flag, W_ACC_EMPTY);
+            // operands landed and an accumulator range is free: one vote for both
+            const bool got_ab = mbar_wait(bar(G::FULL_AB + stage), phase, abort_flag);
+            const bool got_acc = got_ab && mbar_wait(bar(G::ACC_EMPTY + buf), accphase ^ 1u, abort_flag);
+            if (!__all_sync(0xffffffffu, got_acc)) {
+                if (lane == 0) report_timeout(p.status, abort_flag, got_ab ? W_ACC_EMPTY : W_FULL_AB);
                 break;
             }
             tc_fence_after();
@@ -214,23 +239,114 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
                         }
                     }
                 }
+                // one commit per stage: the promotion warps release the stage's shared memory once they have seen it
                 tc_commit(bar(G::ACC_FULL + buf));
-                tc_commit(bar(G::EMPTY_AB + stage));
             }
             __syncwarp();
             if (++stage == kSkStages) { stage = 0; phase ^= 1u; }
             if (++buf == G::NBUF) { buf = 0; accphase ^= 1u; }
+            if (++ks == p.nks) ks = 0;
         }
-    } else if ((warp >> 2) < p.live_chunks) {
+    } else if (FUSED && warp >= QW0) {
+        // ---------------- quantize-on-load: the activations of a stage, straight into the MMA's operand tile -------------
+        // A unit is 8 consecutive K elements of one activation row; a stage holds 16 units per row.  Thread t of the 128
+        // takes units t, t + 128, ...: the units of one quantisation block sit in QB/8 neighbouring lanes, whose absmax is
+        // an xor-shuffle reduction.  The raw values of the next stage are loaded before the current one is converted.
+        constexpr int UNITS = BNS / 8;                     // units per thread and stage (BNS * 16 / 128)
+        constexpr int LPB = QB / 8;                        // lanes that share a block
+        const int qt = (int)threadIdx.x - QW0 * 32;
+        const bool wide = p.x_dtype == BI8_F32;
+        const int esz = wide ? 4 : 2;
+        const unsigned char* xb = static_cast<const unsigned char*>(p.X);
+        uint4 cur[UNITS][2], nxt[UNITS][2];
+        auto load_stage = [&](int ks, uint4 (&r)[UNITS][2]) {
+#pragma unroll
+            for (int u = 0; u < UNITS; ++u) {
+                const int unit = qt + u * 128, m = unit >> 4, k = ks * kBK + (unit & 15) * 8;
+                r[u][0] = make_uint4(0u, 0u, 0u, 0u);
+                r[u][1] = make_uint4(0u, 0u, 0u, 0u);
+                if (m < p.M && k < p.K) {
+                    const unsigned char* src = xb + ((int64_t)m * p.ldx + k) * esz;
+                    r[u][0] = ld_nc_v4(src);
+                    if (wide) r[u][1] = ld_nc_v4(src + 16);
+                }
+            }
+        };
+        int stage = 0;
+        uint32_t phase = 0;
+        int ks = ks_begin;
+        if (s_begin < s_end) load_stage(ks, nxt);
+        for (long long s = s_begin; s < s_end; ++s) {
+#pragma unroll
+            for (int u = 0; u < UNITS; ++u) {
+                cur[u][0] = nxt[u][0];
+                cur[u][1] = nxt[u][1];
+            }
+            const int ks_next = (ks + 1 == p.nks) ? 0 : ks + 1;
+            if (s + 1 < s_end) load_stage(ks_next, nxt);
+            const bool ok = __all_sync(0xffffffffu, mbar_wait(bar(G::EMPTY_AB + stage), phase ^ 1u, abort_flag));
+            if (!ok) {
+                if (lane == 0) report_timeout(p.status, abort_flag, W_EMPTY_AB);
+                break;
+            }
+            const uint32_t xt = base + (uint32_t)stage * G::STAGE_BYTES + G::W_BYTES;
+#pragma unroll
+            for (int u = 0; u < UNITS; ++u) {
+                const int unit = qt + u * 128, m = unit >> 4, piece = unit & 15, k = ks * kBK + piece * 8;
+                float f[8];
+                if (wide) {
+                    f[0] = __uint_as_float(cur[u][0].x); f[1] = __uint_as_float(cur[u][0].y);
+                    f[2] = __uint_as_float(cur[u][0].z); f[3] = __uint_as_float(cur[u][0].w);
+                    f[4] = __uint_as_float(cur[u][1].x); f[5] = __uint_as_float(cur[u][1].y);
+                    f[6] = __uint_as_float(cur[u][1].z); f[7] = __uint_as_float(cur[u][1].w);
+                } else {
+                    const uint32_t w4[4] = {cur[u][0].x, cur[u][0].y, cur[u][0].z, cur[u][0].w};
+#pragma unroll
+                    for (int h = 0; h < 4; ++h) {
+                        if (p.x_dtype == BI8_BF16) {
+                            f[2 * h] = bf16lo(w4[h]);
+                            f[2 * h + 1] = bf16hi(w4[h]);
+                        } else {
+                            const float2 t2 = __half22float2(*reinterpret_cast<const __half2*>(&w4[h]));
+                            f[2 * h] = t2.x;
+                            f[2 * h + 1] = t2.y;
+                        }
+                    }
+                }
+                float amax = 0.0f;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+#pragma unroll
+                for (int off = 1; off < LPB; off <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+                BlockQ bq;
+                bq.set(amax, !wide);
+                const uint32_t lo = pack4(bq.q(f[0]), bq.q(f[1]), bq.q(f[2]), bq.q(f[3]));
+                const uint32_t hi = pack4(bq.q(f[4]), bq.q(f[5]), bq.q(f[6]), bq.q(f[7]));
+                if (m < p.M) {
+                    // 128-byte swizzle of a K-major tile: the 16-byte chunk index is xor-ed with the row index mod 8
+                    const uint32_t dst = xt + (uint32_t)(m * 128 + ((((piece >> 1) ^ (m & 7)) << 4) | ((piece & 1) << 3)));
+                    asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(dst), "r"(lo), "r"(hi) : "memory");
+                    const int j = k / QB;
+                    if ((piece % LPB) == 0 && j < p.nb) sx[j * BNS + m] = amax;
+                }
+            }
+            fence_proxy_async_smem();            // the MMA reads the tile through the async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(G::FULL_AB + stage));
+            if (++stage == kSkStages) { stage = 0; phase ^= 1u; }
+            ks = ks_next;
+        }
+    } else if (warp < PW && (warp >> 2) < p.live_chunks) {
         // ---------------- promotion + epilogue: warp = 4 * chunk + lane quarter ----------------
         const int quarter = warp & 3, chunk = warp >> 2;
         const int row = quarter * 32 + lane;                       // weight row inside the tile
         const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(chunk * 16);
         const float div = 1.0f / (127.0f * 127.0f);
 
-        // activation scales of all blocks, zero beyond the valid rows: [nb][BNS]
-        {
-            const int nthreads = live_warps * 32;
+        // activation scales of all blocks, zero beyond the valid rows: [nb][BNS] (FUSED: the quantizer warps write the
+        // entries of a stage before they arrive on its barrier; columns beyond M are never stored)
+        const int nthreads = live_warps * 32;
+        if (!FUSED) {
             const int total = p.nb * BNS;
             for (int i = threadIdx.x; i < total; i += nthreads) {
                 const int j = i / BNS, m = i % BNS;
@@ -364,24 +480,23 @@ __global__ void __launch_bounds__(256) skinny_reduce_kernel(const float* __restr
     finish_store(acc, m, n, bias, bias_dtype, C, ldc, out_dtype);
 }
 
-template <int QB, int BNS>
-size_t skinny_smem_bytes(int nb) {
-    return (size_t)SkGeo<QB, BNS>::sx_off + (size_t)nb * BNS * 4 + 1024;
-}
-
-template <int QB, int BNS>
+template <int QB, int BNS, bool FUSED>
 int launch_skinny(const GemmArgs& g, const SkParams& p, int grid, cudaStream_t st) {
-    using G = SkGeo<QB, BNS>;
+    using G = SkGeo<QB, BNS, FUSED>;
     CUtensorMap mw, mx, ms;
     int rc = make_operand_map(&mw, g.Bt, g.N, g.K, g.ldb, kTileRows);
     if (rc != BI8_OK) return rc;
-    rc = make_operand_map(&mx, g.A, g.M, g.K, g.lda, BNS);
-    if (rc != BI8_OK) return rc;
+    if (FUSED) {
+        mx = mw;                    // not used: the quantizer warps write the activation tile
+    } else {
+        rc = make_operand_map(&mx, g.A, g.M, g.K, g.lda, BNS);
+        if (rc != BI8_OK) return rc;
+    }
     rc = make_scale_map(&ms, g.sB, p.nb, g.N, kTileRows, G::BPS);
     if (rc != BI8_OK) return rc;
-    const size_t smem = skinny_smem_bytes<QB, BNS>(p.nb);
-    BI8_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_skinny_kernel<QB, BNS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    gemm_tc_skinny_kernel<QB, BNS><<<grid, G::THREADS, smem, st>>>(mw, mx, ms, p);
+    const size_t smem = (size_t)G::sx_off + (size_t)p.nb * BNS * 4 + 1024;
+    BI8_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_skinny_kernel<QB, BNS, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    gemm_tc_skinny_kernel<QB, BNS, FUSED><<<grid, G::THREADS, smem, st>>>(mw, mx, ms, p);
     BI8_CUDA_TRY(cudaGetLastError());
     return BI8_OK;
 }
@@ -399,6 +514,7 @@ bool skinny_shape_ok(int64_t M, int64_t N, int64_t K, int block) {
 
 }  // namespace
 
+// two fp32 slots of 128 x BNS per CTA
 size_t gemm_skinny_workspace_bytes(const GemmArgs& g) {
     const DeviceInfo di = device_info();
     if (!di.ok || g.partials != nullptr || !skinny_shape_ok(g.M, g.N, g.K, g.block)) return 0;
@@ -408,8 +524,14 @@ size_t gemm_skinny_workspace_bytes(const GemmArgs& g) {
 bool gemm_skinny_applicable(const GemmArgs& g) {
     if (g.partials != nullptr || !skinny_shape_ok(g.M, g.N, g.K, g.block)) return false;
     if (!device_info().ok) return false;
-    if (!aligned(g.A, 16) || !aligned(g.Bt, 16) || g.lda % 16 != 0 || g.ldb % 16 != 0) return false;
-    if (!aligned(g.sB, 16)) return false;
+    if (!aligned(g.Bt, 16) || g.ldb % 16 != 0 || !aligned(g.sB, 16)) return false;
+    if (g.X != nullptr) {
+        // quantize-on-load reads 8 elements (16 or 32 bytes) at a time
+        const int esz = g.x_dtype == BI8_F32 ? 4 : 2;
+        if (!aligned(g.X, 16) || (g.ldx * esz) % 16 != 0 || g.K % 8 != 0) return false;
+    } else if (!aligned(g.A, 16) || g.lda % 16 != 0) {
+        return false;
+    }
     const size_t need = gemm_skinny_workspace_bytes(g);
     return g.workspace != nullptr && g.workspace_bytes >= need && aligned(g.workspace, 16);
 }
@@ -420,6 +542,9 @@ int launch_gemm_skinny(const GemmArgs& g, cudaStream_t st) {
     SkParams p;
     std::memset(&p, 0, sizeof(p));
     p.sA = g.sA;
+    p.X = g.X;
+    p.ldx = g.ldx;
+    p.x_dtype = g.x_dtype;
     p.bias = g.bias;
     p.C = g.C;
     p.ws = static_cast<float*>(g.workspace);
@@ -437,10 +562,11 @@ int launch_gemm_skinny(const GemmArgs& g, cudaStream_t st) {
     const long long tiles = (g.N + kTileRows - 1) / kTileRows;
     p.total_stages = tiles * p.nks;
     const int grid = (int)(p.total_stages < di.sms ? p.total_stages : di.sms);
-    const int bns = bns_for(g.M);
+    const bool wide = g.M > 16, fused = g.X != nullptr;
     int rc;
-#define BI8_SK(QB)                                                                       \
-    rc = bns == 16 ? launch_skinny<QB, 16>(g, p, grid, st) : launch_skinny<QB, 32>(g, p, grid, st)
+#define BI8_SK(QB)                                                                                                    \
+    rc = fused ? (wide ? launch_skinny<QB, 32, true>(g, p, grid, st) : launch_skinny<QB, 16, true>(g, p, grid, st))  \
+               : (wide ? launch_skinny<QB, 32, false>(g, p, grid, st) : launch_skinny<QB, 16, false>(g, p, grid, st))
     switch (g.block) {
         case 32: BI8_SK(32); break;
         case 64: BI8_SK(64); break;
@@ -451,7 +577,7 @@ int launch_gemm_skinny(const GemmArgs& g, cudaStream_t st) {
     if (rc != BI8_OK) return rc;
     if (p.total_stages % grid == 0 && (p.total_stages / grid) % p.nks == 0) return BI8_OK;   // no tile is divided
     const int64_t total = g.M * g.N;
-    skinny_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(p.ws, p.total_stages, grid, p.nks, bns, g.bias,
+    skinny_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(p.ws, p.total_stages, grid, p.nks, wide ? 32 : 16, g.bias,
                                                                           g.bias_dtype, g.C, g.ldc, g.out_dtype, (int)g.M,
                                                                           (int)g.N);
     BI8_CUDA_TRY(cudaGetLastError());

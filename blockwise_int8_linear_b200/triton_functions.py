@@ -20,7 +20,8 @@ from . import block_linear_config
 
 __all__ = [
     "ceil_div", "quantize_block_rowwise", "quantize_block_colwise", "dequantize_block_rowwise",
-    "int8_matmul_block64_rowwise_dequantize", "int8_matmul_block_partials", "fast_matmulT",
+    "int8_matmul_block64_rowwise_dequantize", "quantize_matmul_block_rowwise_dequantize", "int8_matmul_block_partials",
+    "fast_matmulT",
 ]
 
 
@@ -195,11 +196,59 @@ def int8_matmul_block64_rowwise_dequantize(a, b, state_x, state_w, bias=None, *,
     L = _lib.lib()
     with _on_device(a):
         ws_bytes = L.bi8_gemm_workspace_bytes(m, n, k, block)
-        ws = torch.empty(ws_bytes, device=a.device, dtype=torch.uint8) if ws_bytes else None
+        ws = _lib.workspace(a.device, ws_bytes)
         rc = L.bi8_gemm_dequant(_lib.ptr(a), _pitch(a), _lib.ptr(bt), _pitch(bt), _lib.ptr(state_x), _lib.ptr(state_w),
                                 _lib.ptr(bias), bias_code, _lib.ptr(c), n, _lib.dtype_code(out_dtype), m, n, k, block,
                                 _lib.ptr(ws), ws_bytes, flags, _lib.stream_ptr())
     _lib.check(rc, "bi8_gemm_dequant")
+    return c
+
+
+def quantize_matmul_block_rowwise_dequantize(x, b, state_w, bias=None, *, flags: int = 0):
+    """``int8_matmul_block64_rowwise_dequantize(*quantize_block_rowwise(x), ...)`` in one library call: the two steps
+    of the layer's forward (``block_linear.py:141-143``).  ``x [M, K]`` floating point, ``b [K, N]`` int8 (the ``.t()``
+    view of the ``[N, K]`` weights), ``state_w [ceil(K/block), N]``.  For ``M <= 32`` the activations are quantized
+    inside the GEMM kernel (quantize-on-load); the result is bit-identical to the two separate calls either way."""
+    block = _block()
+    assert x.is_cuda
+    if x.dim() != 2:
+        raise ValueError(f"expected a 2-D tensor, got {tuple(x.shape)}")
+    x = _rows_contiguous(x)
+    if b.stride(0) > 1 and b.stride(1) > 1:
+        b = b.contiguous()
+    assert x.shape[1] == b.shape[0], "incompatible dimensions"
+    if b.dtype != torch.int8:
+        raise ValueError(f"weights must be int8, got {b.dtype}")
+    bt = b.t()
+    if bt.shape[1] != 1 and bt.stride(1) != 1:
+        bt = bt.contiguous()
+    m, k = x.shape
+    n = bt.shape[0]
+    nb = ceil_div(k, block)
+    if tuple(state_w.shape) != (nb, n) or state_w.dtype != torch.float32:
+        raise ValueError(f"state_w must be float32 [{nb}, {n}] for block {block}, got {state_w.dtype} {tuple(state_w.shape)}")
+    state_w = state_w.contiguous()
+    out_dtype = block_linear_config.INPUT_OUTPUT_TORCH_TYPE
+    c = torch.empty((m, n), device=x.device, dtype=out_dtype)
+    bias_code = 0
+    if bias is not None:
+        if bias.numel() != n:
+            raise ValueError(f"bias must have {n} elements, got {bias.numel()}")
+        bias = bias.reshape(n).contiguous()
+        if bias.dtype not in (torch.bfloat16, torch.float16, torch.float32):
+            bias = bias.float()
+        bias_code = _lib.dtype_code(bias.dtype)
+    xq = torch.empty((m, k), device=x.device, dtype=torch.int8)
+    sx = torch.empty((nb, m), device=x.device, dtype=torch.float32)
+    L = _lib.lib()
+    with _on_device(x):
+        ws_bytes = L.bi8_gemm_workspace_bytes(m, n, k, block)
+        ws = _lib.workspace(x.device, ws_bytes)
+        rc = L.bi8_gemm_dequant_fused_quant(_lib.ptr(x), _lib.dtype_code(x.dtype), _pitch(x), _lib.ptr(xq), _lib.ptr(sx),
+                                            _lib.ptr(bt), _pitch(bt), _lib.ptr(state_w), _lib.ptr(bias), bias_code, _lib.ptr(c),
+                                            n, _lib.dtype_code(out_dtype), m, n, k, block, _lib.ptr(ws), ws_bytes, flags,
+                                            _lib.stream_ptr())
+    _lib.check(rc, "bi8_gemm_dequant_fused_quant")
     return c
 
 

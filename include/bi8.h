@@ -94,7 +94,9 @@ BI8_API int bi8_dequantize_rowwise(const int8_t* q, const float* s, void* out, i
  * A  [M,K] int8, row stride lda.  Bt [N,K] int8, row stride ldb — the reference's `b` operand is the
  * transposed view Bt^T with strides (1, ldb).  sA [ceil(K/block), M], sB [ceil(K/block), N] fp32.
  * bias [N] of bias_dtype or NULL.  C [M,N] of out_dtype, row stride ldc.
- * workspace: bi8_gemm_workspace_bytes(M,N,K,block) bytes of device memory (may be NULL when that is 0).
+ * workspace: bi8_gemm_workspace_bytes(M,N,K,block) bytes of 16-byte aligned device memory (may be NULL when that
+ * is 0; without it small-M shapes run on slower kernels).  It is plain scratch: nothing has to be cleared, every
+ * call overwrites what it later reads; calls that may run concurrently need separate workspaces.
  * The int32 partial sums are exact; the fp32 accumulation multiplies the three factors in a different
  * order than the reference (a few fp32 ulps per term). */
 BI8_API int bi8_gemm_dequant(const int8_t* A, int64_t lda, const int8_t* Bt, int64_t ldb,
@@ -124,9 +126,19 @@ BI8_API size_t bi8_gemm_static_scratch_bytes(void);
 BI8_API int bi8_gemm_block_partials(const int8_t* A, int64_t lda, const int8_t* Bt, int64_t ldb, int32_t* P,
                             int64_t M, int64_t N, int64_t K, int block, int flags, void* stream);
 
-/* Forward of the layer in one call (block_linear.py:78-80 / 141-143): quantizes x [M,K] (x_dtype, row
- * stride ldx) into the caller's scratch (xq [M,K] int8, sx [ceil(K/block),M] fp32) and runs the GEMM
- * against pre-quantized weights.  Same results as bi8_quantize_rowwise + bi8_gemm_dequant. */
+/* Forward of the layer in one call (block_linear.py:78-80 / 141-143): quantize-on-load GEMM.  x [M,K] of x_dtype, row
+ * stride ldx, is quantized per row and block exactly as bi8_quantize_rowwise does and multiplied with the
+ * pre-quantized weights Wq [N,K] / sW; the result equals bi8_quantize_rowwise followed by bi8_gemm_dequant.
+ * For M <= 32 (N a multiple of 4, K a multiple of 8, 16-byte aligned rows, workspace given) this is ONE kernel:
+ * the activations are quantized inside the GEMM as its stages are loaded and xq / sx are not touched.  Every
+ * other shape runs the two kernels through the caller's scratch xq [M,K] int8 and sx [ceil(K/block),M] fp32,
+ * which may be NULL only when the one-kernel conditions hold.  The scratch contents after the call are
+ * unspecified.  workspace as for bi8_gemm_dequant. */
+BI8_API int bi8_gemm_dequant_fused_quant(const void* x, int x_dtype, int64_t ldx, int8_t* xq, float* sx,
+                                 const int8_t* Wq, int64_t ldw, const float* sW, const void* bias, int bias_dtype,
+                                 void* C, int64_t ldc, int out_dtype, int64_t M, int64_t N, int64_t K, int block,
+                                 void* workspace, size_t workspace_bytes, int flags, void* stream);
+/* The same entry point under its earlier name. */
 BI8_API int bi8_linear_forward(const void* x, int x_dtype, int64_t ldx, int8_t* xq, float* sx,
                        const int8_t* Wq, int64_t ldw, const float* sW, const void* bias, int bias_dtype,
                        void* C, int64_t ldc, int out_dtype, int64_t M, int64_t N, int64_t K, int block,

@@ -17,7 +17,7 @@ import pytest
 import torch
 
 from oracle import blockwise_int8_oracle as O
-from tests.gpu_util import DEV, assert_clean_device, bf16_ulp_distance, quantized_pair, set_config
+from tests.gpu_util import DEV, assert_clean_device, bf16_ulp_distance, quantized_pair, randn_bf16, set_config
 from tests.helpers import golden_names, load_golden
 
 pytestmark = pytest.mark.gpu
@@ -301,6 +301,46 @@ def test_skinny_tensor_core_kernel(shape):
     with pytest.raises(Bi8Error):
         big = quantized_pair(33, 128, 32, block, seed=1)
         _gemm(big[0], big[2], big[1], big[3], flags=SKINNY)
+    assert_clean_device()
+    set_config(64)
+
+
+FUSED_SHAPES = [
+    # (M, K, N, block, dtype)
+    (1, 4096, 512, 64, torch.bfloat16), (8, 2048, 1000, 64, torch.bfloat16), (5, 1056, 76, 64, torch.bfloat16),
+    (16, 4096, 1024, 64, torch.float16), (7, 416, 52, 128, torch.float32), (3, 208, 36, 32, torch.bfloat16),
+    (17, 512, 384, 64, torch.bfloat16), (32, 1056, 260, 32, torch.float32), (32, 2048, 128, 128, torch.float16),
+    (8, 4096, 11008, 64, torch.bfloat16), (2, 11008, 4096, 64, torch.bfloat16),
+    (40, 512, 256, 64, torch.bfloat16), (4, 512, 50, 64, torch.bfloat16),      # not eligible: run as two kernels
+]
+
+
+@pytest.mark.parametrize("shape", FUSED_SHAPES)
+def test_quantize_on_load_gemm(shape):
+    """bi8_gemm_dequant_fused_quant: quantize + GEMM in one call, for M <= 32 inside one kernel.  The quantized
+    activations are bit-identical to the standalone quantizer's, so the result must equal the two-call sequence
+    exactly, which in turn is checked against the oracle."""
+    from triton_functions import (int8_matmul_block64_rowwise_dequantize as mm, quantize_block_rowwise,
+                                  quantize_matmul_block_rowwise_dequantize as qmm)
+    m, k, n, block, dtype = shape
+    x = randn_bf16((m, k), seed=3 * m + k).to(dtype)
+    if dtype == torch.float32:
+        x = x + torch.randn((m, k), generator=torch.Generator().manual_seed(k)) * 1e-3      # full fp32 mantissas
+    x[0, : min(k, block)] = 0                                                                # an all-zero block
+    w = randn_bf16((n, k), seed=k + n, std=0.02)
+    wq, ws = O.quantize(w, block)
+    bias = torch.randn(n, generator=torch.Generator().manual_seed(n)).to(torch.bfloat16)
+    for out_dtype in (torch.float32, torch.bfloat16):
+        set_config(block, out_dtype)
+        xd, wqd, wsd = x.to(DEV), wq.to(DEV), ws.to(DEV)
+        xq, xs = quantize_block_rowwise(xd)
+        two = mm(xq, wqd.t(), xs, wsd, bias.to(DEV))
+        one = qmm(xd, wqd.t(), wsd, bias.to(DEV))
+        assert torch.equal(one, two)
+        assert torch.equal(one, qmm(xd, wqd.t(), wsd, bias.to(DEV))), "deterministic"
+    set_config(block, torch.float32)
+    oq, os_ = O.quantize(x, block)
+    _check_fp32(qmm(x.to(DEV), wq.to(DEV).t(), ws.to(DEV)), oq, wq, os_, ws, block)
     assert_clean_device()
     set_config(64)
 

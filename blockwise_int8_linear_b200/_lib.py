@@ -16,6 +16,7 @@ LIB_PATH = os.path.join(_HERE, "libbi8.so")
 
 BI8_BF16, BI8_F32, BI8_F16 = 0, 1, 2
 GEMM_DEFAULT, GEMM_FORCE_GENERIC, GEMM_FORCE_TC, GEMM_NO_SEED, GEMM_FORCE_SMALLM, GEMM_FORCE_SKINNY = 0, 1, 2, 4, 8, 16
+GEMM_QUANT_IN_KERNEL = 32
 
 _DTYPE_CODE = {torch.bfloat16: BI8_BF16, torch.float32: BI8_F32, torch.float16: BI8_F16}
 

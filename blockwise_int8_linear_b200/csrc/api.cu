@@ -186,7 +186,9 @@ int bi8_gemm_dequant_fused_quant(const void* x, int x_dtype, int64_t ldx, int8_t
                                  const float* sW, const void* bias, int bias_dtype, void* C, int64_t ldc, int out_dtype,
                                  int64_t M, int64_t N, int64_t K, int block, void* workspace, size_t workspace_bytes, int flags,
                                  void* stream) {
-    // one kernel where the skinny tensor-core GEMM applies (it quantizes the activations as it loads them) ...
+    // Decode-sized M: the skinny tensor-core GEMM.  Default: a small quantizer kernel, then the GEMM launched so that its
+    // set-up and first weight copies overlap the quantizer (programmatic dependent launch).  With BI8_GEMM_QUANT_IN_KERNEL,
+    // or without scratch, the GEMM kernel quantizes the activations itself as it loads its stages (one kernel, slower).
     if (!dtype_ok(x_dtype)) return fail(BI8_ERR_DTYPE, "gemm_dequant_fused_quant: unknown dtype code %d", x_dtype);
     const bool forced = (flags & (BI8_GEMM_FORCE_GENERIC | BI8_GEMM_FORCE_TC | BI8_GEMM_FORCE_SMALLM)) != 0;
     if (!forced && x && M > 0 && N > 0 && K > 0 && ldx >= K && aligned(x, dtype_size(x_dtype))) {
@@ -199,6 +201,14 @@ int bi8_gemm_dequant_fused_quant(const void* x, int x_dtype, int64_t ldx, int8_t
             if (ldw < K || ldc < N) return fail(BI8_ERR_SHAPE, "gemm_dequant_fused_quant: row pitch smaller than the row");
             if (!dtype_ok(out_dtype) || (bias && !dtype_ok(bias_dtype))) return fail(BI8_ERR_DTYPE, "gemm_dequant_fused_quant: unknown dtype code");
             if (!aligned(C, dtype_size(out_dtype))) return fail(BI8_ERR_ALIGN, "gemm_dequant_fused_quant: output not element aligned");
+            const bool in_kernel = (flags & BI8_GEMM_QUANT_IN_KERNEL) || !xq || !sx || K % 16 != 0 || !aligned(xq, 16);
+            if (in_kernel) return launch_gemm_skinny(g, static_cast<cudaStream_t>(stream));
+            int rc = launch_skinny_quantize(x, x_dtype, ldx, xq, sx, M, K, block, static_cast<cudaStream_t>(stream));
+            if (rc != BI8_OK) return rc;
+            g.X = nullptr;
+            g.A = xq;
+            g.sA = sx;
+            g.after_own_quantizer = true;
             return launch_gemm_skinny(g, static_cast<cudaStream_t>(stream));
         }
     }

@@ -53,6 +53,7 @@ struct GemmArgs {
     const void* X = nullptr;  // non-null: activations before quantization (A and sA unused), quantized on load
     int x_dtype = 0;
     int64_t ldx = 0;
+    bool after_own_quantizer = false;   // the kernel launched just before is this library's decode quantizer
 };
 
 bool gemm_tc_applicable(const GemmArgs& g, const char** why);
@@ -62,6 +63,8 @@ int launch_gemm_generic(const GemmArgs& g, cudaStream_t st);
 bool gemm_skinny_applicable(const GemmArgs& g);
 size_t gemm_skinny_workspace_bytes(const GemmArgs& g);
 int launch_gemm_skinny(const GemmArgs& g, cudaStream_t st);
+int launch_skinny_quantize(const void* x, int x_dtype, int64_t ldx, int8_t* q, float* sx, int64_t M, int64_t K, int block,
+                           cudaStream_t st);
 bool gemm_smallm_applicable(const GemmArgs& g);
 int launch_gemm_smallm(const GemmArgs& g, cudaStream_t st);
 int run_mma_peak_probe(int iters, float* ms, int* sm_count);

@@ -33,9 +33,8 @@ namespace {
 using namespace ptx;
 
 constexpr int kTileRows = 128;    // weight rows per tile (the MMA's M)
-constexpr int kSkStages = 4;      // 4 x 16 KiB of weights in flight per SM (3, 6 and 10 stages measure the same)
 constexpr int kSkMaxM = 32;
-constexpr size_t kSxMaxBytes = 64 * 1024;   // activation scales staged per CTA
+constexpr size_t kSxMaxBytes = 48 * 1024;   // activation scales staged per CTA (with the stage ring: under 227 KiB)
 
 constexpr int pow2_at_least(int x) {
     int p = 32;
@@ -44,14 +43,18 @@ constexpr int pow2_at_least(int x) {
 }
 
 constexpr int kQuantWarps = 4;    // FUSED: warps that quantize the activations of a stage
+constexpr int kMmaWarps = 2;      // MMA issuers, taking the stages in turn
 
 template <int QB, int BNS, bool FUSED = false>
 struct SkGeo {
+    // ring depth: the loop producer -> HBM -> MMA -> promotion -> producer takes a few thousand cycles per slot, and a
+    // stage should be re-issued every ~700 to keep up with HBM
+    static constexpr int STAGES = BNS == 16 ? 8 : 6;
     static constexpr int BPS = kBK / QB;                  // quantisation blocks per stage
     static constexpr int MMAS = QB / 32;                  // MMAs (K = 32) per block
     static constexpr int CHUNKS = BNS / 16;               // groups of 16 activation rows
     static constexpr int PROMO_WARPS = 4 * CHUNKS;
-    static constexpr int THREADS = (PROMO_WARPS + 2 + (FUSED ? kQuantWarps : 0)) * 32;
+    static constexpr int THREADS = (PROMO_WARPS + 1 + kMmaWarps + (FUSED ? kQuantWarps : 0)) * 32;
     static constexpr int ACC_STRIDE = BPS * BNS;          // tensor-memory columns of one stage's accumulators
     static constexpr int NBUF = (512 / ACC_STRIDE) < 4 ? (512 / ACC_STRIDE) : 4;
     static constexpr int TMEM_COLS = pow2_at_least(NBUF * ACC_STRIDE);
@@ -60,9 +63,9 @@ struct SkGeo {
     static constexpr uint32_t S_TX = BPS * kTileRows * 4;                 // bytes the scale copy delivers
     static constexpr uint32_t S_BYTES = S_TX < 1024 ? 1024 : S_TX;        // keeps every stage 1024-byte aligned
     static constexpr uint32_t STAGE_BYTES = W_BYTES + X_BYTES + S_BYTES;
-    static constexpr uint32_t bar_off = kSkStages * STAGE_BYTES;
-    static constexpr int FULL_AB = 0, EMPTY_AB = kSkStages, ACC_FULL = 2 * kSkStages, ACC_EMPTY = 2 * kSkStages + NBUF,
-                         NBARS = 2 * kSkStages + 2 * NBUF;
+    static constexpr uint32_t bar_off = STAGES * STAGE_BYTES;
+    static constexpr int FULL_AB = 0, EMPTY_AB = STAGES, ACC_FULL = 2 * STAGES, ACC_EMPTY = 2 * STAGES + NBUF,
+                         NBARS = 2 * STAGES + 2 * NBUF;
     static constexpr uint32_t misc_off = bar_off + NBARS * 8;             // tmem holder, abort flag, never-raised flag
     static constexpr uint32_t sx_off = (misc_off + 32 + 15) & ~15u;       // activation scales [nb][BNS]
 };
@@ -129,27 +132,33 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int live_warps = 4 * p.live_chunks;
-    constexpr int PW = G::PROMO_WARPS, MW = G::PROMO_WARPS + 1, QW0 = G::PROMO_WARPS + 2;
+    constexpr int PW = G::PROMO_WARPS, MW = G::PROMO_WARPS + 1, QW0 = G::PROMO_WARPS + 1 + kMmaWarps;
+    static_assert(G::STAGES % kMmaWarps == 0 && G::NBUF % kMmaWarps == 0, "every issuer keeps its own stages and accumulators");
 
     const long long s_begin = range_start(blockIdx.x, p.total_stages, gridDim.x);
     const long long s_end = range_start((long long)blockIdx.x + 1, p.total_stages, gridDim.x);
     // position of the CTA's first stage; every role then steps (tile, ks) by itself, without a division per stage
     const int tile_begin = (int)(s_begin / p.nks), ks_begin = (int)(s_begin - (long long)tile_begin * p.nks);
 
-    auto issue_stage = [&](int stage, int tile, int ks) {            // one lane
+    // one lane; `with_x` false leaves out the activation tile, whose copy then has to follow (issue_x)
+    auto issue_stage = [&](int stage, int tile, int ks, bool with_x) {
         const uint32_t dst = base + (uint32_t)stage * G::STAGE_BYTES;
         mbar_expect_tx(bar(G::FULL_AB + stage), G::W_BYTES + (FUSED ? 0u : G::X_BYTES) + G::S_TX);
         tma_load_2d(dst, &tmW, bar(G::FULL_AB + stage), ks * kBK, tile * kTileRows);
-        if (!FUSED) tma_load_2d(dst + G::W_BYTES, &tmX, bar(G::FULL_AB + stage), ks * kBK, 0);
+        if (!FUSED && with_x) tma_load_2d(dst + G::W_BYTES, &tmX, bar(G::FULL_AB + stage), ks * kBK, 0);
         tma_load_2d(dst + G::W_BYTES + G::X_BYTES, &tmS, bar(G::FULL_AB + stage), tile * kTileRows, ks * G::BPS);
     };
+    auto issue_x = [&](int stage, int ks) {
+        tma_load_2d(base + (uint32_t)stage * G::STAGE_BYTES + G::W_BYTES, &tmX, bar(G::FULL_AB + stage), ks * kBK, 0);
+    };
 
-    // The producer warp sets the barriers up and starts the copies of the first stages right away (the ring is empty, so
-    // nothing has to be waited for); the tensor-memory allocation and the CTA-wide sync overlap their latency.
+    // The producer warp sets the barriers up, tells the others (named barrier 2: it arrives, they wait, so it never stands
+    // still) and starts the copies of the first stages right away: the ring is empty, nothing has to be waited for.  The
+    // tensor-memory allocation runs beside it.
     int pre_tile = tile_begin, pre_ks = ks_begin, pre_count = 0;
     if (warp == PW) {
         if (lane == 0) {
-            for (int s = 0; s < kSkStages; ++s) {
+            for (int s = 0; s < G::STAGES; ++s) {
                 mbar_init(bar(G::FULL_AB + s), FUSED ? 1 + kQuantWarps : 1);   // the TMA's bytes (+ the quantizer warps)
                 // a stage is free again when every promotion warp has seen its accumulator complete (so the MMAs have
                 // read the operands) and has taken its scales
@@ -165,10 +174,22 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
             fence_proxy_async_smem();
         }
         __syncwarp();
-        while (pre_count < kSkStages && s_begin + pre_count < s_end) {
-            if (lane == 0) issue_stage(pre_count, pre_tile, pre_ks);
+        asm volatile("bar.arrive 2, %0;" ::"n"(G::THREADS) : "memory");
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the reduction kernel may be made resident
+        while (pre_count < G::STAGES && s_begin + pre_count < s_end) {
+            if (lane == 0) issue_stage(pre_count, pre_tile, pre_ks, false);
             ++pre_count;
             if (++pre_ks == p.nks) { pre_ks = 0; ++pre_tile; }
+        }
+        // Everything above touched only the weights and their scales.  The activations may come from the kernel launched
+        // just before this one (a quantizer that lets its dependents start early): wait for it here.
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (!FUSED && lane == 0) {
+            int ks = ks_begin;
+            for (int q = 0; q < pre_count; ++q) {
+                issue_x(q, ks);
+                if (++ks == p.nks) ks = 0;
+            }
         }
         __syncwarp();
     }
@@ -176,18 +197,20 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         tmem_alloc(smem_u32((const void*)tmem_holder), G::TMEM_COLS);
         tmem_relinquish();
     }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_holder;
+    if (warp != PW) {
+        tc_fence_before();
+        asm volatile("bar.sync 2, %0;" ::"n"(G::THREADS) : "memory");
+        tc_fence_after();
+    }
+    const uint32_t tmem_base = (warp != PW) ? *tmem_holder : 0u;       // the producer never touches tensor memory
 
     if (warp == PW) {
         // ---------------- TMA producer ----------------
-        int stage = pre_count == kSkStages ? 0 : pre_count;
-        uint32_t phase = pre_count == kSkStages ? 1u : 0u;
-        int last_parity[kSkStages];
+        int stage = pre_count == G::STAGES ? 0 : pre_count;
+        uint32_t phase = pre_count == G::STAGES ? 1u : 0u;
+        int last_parity[G::STAGES];
 #pragma unroll
-        for (int q = 0; q < kSkStages; ++q) last_parity[q] = q < pre_count ? 0 : -1;
+        for (int q = 0; q < G::STAGES; ++q) last_parity[q] = q < pre_count ? 0 : -1;
         int tile = pre_tile, ks = pre_ks;
         bool ok = true;
         for (long long s = s_begin + pre_count; s < s_end; ++s) {
@@ -196,26 +219,31 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
                 if (lane == 0) report_timeout(p.status, abort_flag, W_EMPTY_AB);
                 break;
             }
-            if (lane == 0) issue_stage(stage, tile, ks);
+            if (lane == 0) issue_stage(stage, tile, ks, true);
             __syncwarp();
 #pragma unroll
-            for (int q = 0; q < kSkStages; ++q)
+            for (int q = 0; q < G::STAGES; ++q)
                 if (q == stage) last_parity[q] = (int)phase;
-            if (++stage == kSkStages) { stage = 0; phase ^= 1u; }
+            if (++stage == G::STAGES) { stage = 0; phase ^= 1u; }
             if (++ks == p.nks) { ks = 0; ++tile; }
         }
         if (!ok) {
             // do not leave while our own copies may still land in this CTA's shared memory
 #pragma unroll
-            for (int q = 0; q < kSkStages; ++q)
+            for (int q = 0; q < G::STAGES; ++q)
                 if (last_parity[q] >= 0) (void)mbar_wait(bar(G::FULL_AB + q), (uint32_t)last_parity[q], never_flag, 200000000ll);
         }
-    } else if (warp == MW) {
-        // ---------------- MMA issuer ----------------
+    } else if (warp >= MW && warp < MW + kMmaWarps) {
+        // ---------------- MMA issuers ----------------
+        // Issuing the four K = 32 MMAs of a stage and polling its two barriers costs one thread several hundred cycles, more
+        // than the stage's bytes take to arrive, so kMmaWarps warps take the stages in turn (stage ring slots and
+        // accumulator ranges of one residue class each).
         constexpr uint32_t idesc = umma_idesc_i8(kTileRows, BNS);
-        int stage = 0, buf = 0, ks = ks_begin;
+        const int me = warp - MW;
+        int stage = me, buf = me, ks = ks_begin + me;
+        while (ks >= p.nks) ks -= p.nks;
         uint32_t phase = 0, accphase = 0;
-        for (long long s = s_begin; s < s_end; ++s) {
+        for (long long s = s_begin + me; s < s_end; s += kMmaWarps) {
             // operands landed and an accumulator range is free: one vote for both
             const bool got_ab = mbar_wait(bar(G::FULL_AB + stage), phase, abort_flag);
             const bool got_acc = got_ab && mbar_wait(bar(G::ACC_EMPTY + buf), accphase ^ 1u, abort_flag);
@@ -243,9 +271,12 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
                 tc_commit(bar(G::ACC_FULL + buf));
             }
             __syncwarp();
-            if (++stage == kSkStages) { stage = 0; phase ^= 1u; }
-            if (++buf == G::NBUF) { buf = 0; accphase ^= 1u; }
-            if (++ks == p.nks) ks = 0;
+            stage += kMmaWarps;
+            if (stage >= G::STAGES) { stage -= G::STAGES; phase ^= 1u; }
+            buf += kMmaWarps;
+            if (buf >= G::NBUF) { buf -= G::NBUF; accphase ^= 1u; }
+            ks += kMmaWarps;
+            while (ks >= p.nks) ks -= p.nks;
         }
     } else if (FUSED && warp >= QW0) {
         // ---------------- quantize-on-load: the activations of a stage, straight into the MMA's operand tile -------------
@@ -259,6 +290,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         const int esz = wide ? 4 : 2;
         const unsigned char* xb = static_cast<const unsigned char*>(p.X);
         uint4 cur[UNITS][2], nxt[UNITS][2];
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         auto load_stage = [&](int ks, uint4 (&r)[UNITS][2]) {
 #pragma unroll
             for (int u = 0; u < UNITS; ++u) {
@@ -333,7 +365,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
             fence_proxy_async_smem();            // the MMA reads the tile through the async proxy
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(G::FULL_AB + stage));
-            if (++stage == kSkStages) { stage = 0; phase ^= 1u; }
+            if (++stage == G::STAGES) { stage = 0; phase ^= 1u; }
             ks = ks_next;
         }
     } else if (warp < PW && (warp >> 2) < p.live_chunks) {
@@ -342,15 +374,23 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         const int row = quarter * 32 + lane;                       // weight row inside the tile
         const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(chunk * 16);
         const float div = 1.0f / (127.0f * 127.0f);
+        asm volatile("griddepcontrol.wait;" ::: "memory");      // activation scales, and every store, after the previous kernel
 
         // activation scales of all blocks, zero beyond the valid rows: [nb][BNS] (FUSED: the quantizer warps write the
         // entries of a stage before they arrive on its barrier; columns beyond M are never stored)
         const int nthreads = live_warps * 32;
         if (!FUSED) {
             const int total = p.nb * BNS;
-            for (int i = threadIdx.x; i < total; i += nthreads) {
-                const int j = i / BNS, m = i % BNS;
-                sx[i] = (m < p.M) ? __ldg(p.sA + (int64_t)j * p.M + m) : 0.0f;
+            for (int i0 = threadIdx.x; i0 < total; i0 += nthreads * 8) {       // eight loads in flight per thread
+                float v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int i = i0 + u * nthreads, j = i / BNS, m = i % BNS;
+                    v[u] = (i < total && m < p.M) ? __ldg(p.sA + (int64_t)j * p.M + m) : 0.0f;
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (i0 + u * nthreads < total) sx[i0 + u * nthreads] = v[u];
             }
             asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
         }
@@ -418,7 +458,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(G::ACC_EMPTY + buf));
-                if (++stage == kSkStages) { stage = 0; phase ^= 1u; }
+                if (++stage == G::STAGES) { stage = 0; phase ^= 1u; }
                 if (++buf == G::NBUF) { buf = 0; accphase ^= 1u; }
             }
             if (!ok) break;
@@ -453,15 +493,71 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     }
 }
 
+// Row-wise block quantizer for the few activation rows of a decode step (same arithmetic as the standalone quantizer:
+// quant_math.cuh), used by the quantize-on-load entry point in front of the GEMM.  A thread takes 8 consecutive elements;
+// the QB/8 lanes of a block reduce the absmax with xor shuffles.  It lets the GEMM, launched with programmatic stream
+// serialisation, become resident at once: the GEMM's set-up and its first weight copies run beside this kernel and
+// only its activation loads wait for it.
+template <int QB>
+__global__ void __launch_bounds__(256) skinny_quantize_kernel(const void* __restrict__ x, int x_dtype, int64_t ldx,
+                                                              int8_t* __restrict__ q, float* __restrict__ sx, int M, int K, int nb) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    constexpr int LPB = QB / 8;
+    const int upr = nb * LPB;                                  // units per row, padded to whole blocks
+    const int64_t u = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    const int m = (int)(u / upr), piece = (int)(u % upr), k = piece * 8;
+    const bool wide = x_dtype == BI8_F32;
+    const bool valid = m < M && k < K;
+    float f[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = 0.0f;
+    if (valid) {
+        const unsigned char* src = static_cast<const unsigned char*>(x) + ((int64_t)m * ldx + k) * (wide ? 4 : 2);
+        const uint4 a = ld_nc_v4(src);
+        if (wide) {
+            const uint4 b = ld_nc_v4(src + 16);
+            f[0] = __uint_as_float(a.x); f[1] = __uint_as_float(a.y); f[2] = __uint_as_float(a.z); f[3] = __uint_as_float(a.w);
+            f[4] = __uint_as_float(b.x); f[5] = __uint_as_float(b.y); f[6] = __uint_as_float(b.z); f[7] = __uint_as_float(b.w);
+        } else {
+            const uint32_t w4[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+                if (x_dtype == BI8_BF16) {
+                    f[2 * h] = bf16lo(w4[h]);
+                    f[2 * h + 1] = bf16hi(w4[h]);
+                } else {
+                    const float2 t2 = __half22float2(*reinterpret_cast<const __half2*>(&w4[h]));
+                    f[2 * h] = t2.x;
+                    f[2 * h + 1] = t2.y;
+                }
+            }
+        }
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+#pragma unroll
+    for (int off = 1; off < LPB; off <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    if (!valid) return;
+    BlockQ bq;
+    bq.set(amax, !wide);
+    const uint32_t lo = pack4(bq.q(f[0]), bq.q(f[1]), bq.q(f[2]), bq.q(f[3]));
+    const uint32_t hi = pack4(bq.q(f[4]), bq.q(f[5]), bq.q(f[6]), bq.q(f[7]));
+    *reinterpret_cast<uint2*>(q + (int64_t)m * K + k) = make_uint2(lo, hi);
+    if ((piece % LPB) == 0) sx[(int64_t)(k / QB) * M + m] = amax;
+}
+
 // Adds the parts of divided tiles in ascending K order and writes C; tiles that one CTA covered completely were
 // already written by it.  One thread per output element (a thread per tile row with a loop over the activation rows
 // serialises the loads and is several times slower); `ctas` and `total_stages` are those of the GEMM launch, bns its BNS.
 __global__ void __launch_bounds__(256) skinny_reduce_kernel(const float* __restrict__ ws, long long total_stages, int ctas,
                                                             int nks, int bns, const void* __restrict__ bias, int bias_dtype,
                                                             void* __restrict__ C, int64_t ldc, int out_dtype, int M, int N) {
+    // Launched with programmatic stream serialisation: the blocks may become resident while the GEMM still runs and do
+    // their index arithmetic; griddepcontrol.wait returns when the GEMM grid has completed and its stores are visible.
     const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
-    if (i >= (int64_t)M * N) return;
-    const int m = (int)(i / N), n = (int)(i % N);
+    const bool live = i < (int64_t)M * N;
+    const int m = live ? (int)(i / N) : 0, n = live ? (int)(i % N) : 0;
     const int tile = n / kTileRows, row = n % kTileRows;
     const long long t0 = (long long)tile * nks, t1 = t0 + nks;
     long long c0 = t0 * ctas / total_stages;
@@ -470,12 +566,19 @@ __global__ void __launch_bounds__(256) skinny_reduce_kernel(const float* __restr
     // the tile's parts belong to CTAs c0, c0 + 1, ...; a part that begins where its CTA's range begins is that CTA's
     // slot 0, and only the first part of a tile can begin elsewhere (at the tile's first stage, inside the range of c0)
     const long long cs0 = range_start(c0, total_stages, ctas);
-    long long ce = range_start(c0 + 1, total_stages, ctas);
-    if (cs0 <= t0 && ce >= t1) return;                       // whole tile inside one range: written by the GEMM
-    float acc = ws[((2 * c0 + (cs0 < t0 ? 1 : 0)) * bns + m) * kTileRows + row];
-    for (long long c = c0 + 1; ce < t1; ++c) {
-        acc = __fadd_rn(acc, ws[(2 * c * bns + m) * kTileRows + row]);
-        ce = range_start(c + 1, total_stages, ctas);
+    const bool whole = cs0 <= t0 && range_start(c0 + 1, total_stages, ctas) >= t1;   // written by the GEMM itself
+    int parts = 1;
+    while (range_start(c0 + parts, total_stages, ctas) < t1) ++parts;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (!live || whole) return;
+    float acc = __ldcg(ws + ((2 * c0 + (cs0 < t0 ? 1 : 0)) * bns + m) * kTileRows + row);
+    for (int q = 1; q < parts; q += 4) {                     // four loads in flight, added in ascending order
+        float v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = (q + u < parts) ? __ldcg(ws + (2 * (c0 + q + u) * bns + m) * kTileRows + row) : 0.0f;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (q + u < parts) acc = __fadd_rn(acc, v[u]);
     }
     finish_store(acc, m, n, bias, bias_dtype, C, ldc, out_dtype);
 }
@@ -496,8 +599,20 @@ int launch_skinny(const GemmArgs& g, const SkParams& p, int grid, cudaStream_t s
     if (rc != BI8_OK) return rc;
     const size_t smem = (size_t)G::sx_off + (size_t)p.nb * BNS * 4 + 1024;
     BI8_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_skinny_kernel<QB, BNS, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    gemm_tc_skinny_kernel<QB, BNS, FUSED><<<grid, G::THREADS, smem, st>>>(mw, mx, ms, p);
-    BI8_CUDA_TRY(cudaGetLastError());
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(G::THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    // only behind this library's own activation quantizer: the kernel reads the weights before it waits for its
+    // predecessor, which is wrong behind a kernel that may still be writing them
+    cfg.numAttrs = g.after_own_quantizer ? 1 : 0;
+    BI8_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tc_skinny_kernel<QB, BNS, FUSED>, mw, mx, ms, p));
     return BI8_OK;
 }
 
@@ -519,6 +634,21 @@ size_t gemm_skinny_workspace_bytes(const GemmArgs& g) {
     const DeviceInfo di = device_info();
     if (!di.ok || g.partials != nullptr || !skinny_shape_ok(g.M, g.N, g.K, g.block)) return 0;
     return (size_t)2 * di.sms * bns_for(g.M) * kTileRows * 4;
+}
+
+int launch_skinny_quantize(const void* x, int x_dtype, int64_t ldx, int8_t* q, float* sx, int64_t M, int64_t K, int block,
+                           cudaStream_t st) {
+    const int nb = (int)((K + block - 1) / block);
+    const int64_t units = M * nb * (block / 8);
+    const unsigned blocks = (unsigned)((units + 255) / 256);
+    switch (block) {
+        case 32: skinny_quantize_kernel<32><<<blocks, 256, 0, st>>>(x, x_dtype, ldx, q, sx, (int)M, (int)K, nb); break;
+        case 64: skinny_quantize_kernel<64><<<blocks, 256, 0, st>>>(x, x_dtype, ldx, q, sx, (int)M, (int)K, nb); break;
+        case 128: skinny_quantize_kernel<128><<<blocks, 256, 0, st>>>(x, x_dtype, ldx, q, sx, (int)M, (int)K, nb); break;
+        default: return fail(BI8_ERR_BLOCK, "skinny quantizer supports block 32, 64, 128 (got %d)", block);
+    }
+    BI8_CUDA_TRY(cudaGetLastError());
+    return BI8_OK;
 }
 
 bool gemm_skinny_applicable(const GemmArgs& g) {
@@ -577,10 +707,18 @@ int launch_gemm_skinny(const GemmArgs& g, cudaStream_t st) {
     if (rc != BI8_OK) return rc;
     if (p.total_stages % grid == 0 && (p.total_stages / grid) % p.nks == 0) return BI8_OK;   // no tile is divided
     const int64_t total = g.M * g.N;
-    skinny_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(p.ws, p.total_stages, grid, p.nks, wide ? 32 : 16, g.bias,
-                                                                          g.bias_dtype, g.C, g.ldc, g.out_dtype, (int)g.M,
-                                                                          (int)g.N);
-    BI8_CUDA_TRY(cudaGetLastError());
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)((total + 255) / 256));
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;     // see skinny_reduce_kernel
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    BI8_CUDA_TRY(cudaLaunchKernelEx(&cfg, skinny_reduce_kernel, (const float*)p.ws, p.total_stages, grid, p.nks, wide ? 32 : 16,
+                                    g.bias, g.bias_dtype, g.C, g.ldc, g.out_dtype, (int)g.M, (int)g.N));
     return BI8_OK;
 }
 

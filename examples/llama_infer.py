@@ -122,11 +122,15 @@ class Layer(nn.Module):
         tensor, the cache is written with index_copy_ and attended in full under a mask, so that every shape is static and
         the step can be captured in a CUDA graph.  `cis` holds the rotary factors of this call's positions."""
         B, T, _ = x.shape
-        hq, hs = quantize_block_rowwise(rms_norm(x).view(B * T, -1))       # one quantization feeds q, k and v
         heads = (B, T, self.heads_local, self.head_dim)
-        q = self.q.forward_quantized(hq, hs, (B, T)).view(heads).transpose(1, 2)
-        k = self.k.forward_quantized(hq, hs, (B, T)).view(heads).transpose(1, 2)
-        v = self.v.forward_quantized(hq, hs, (B, T)).view(heads).transpose(1, 2)
+        fused = B * T <= 32          # decode: every layer quantizes its input inside its GEMM kernel, nothing to share
+        h = rms_norm(x)
+        if fused:
+            q, k, v = self.q(h).view(heads), self.k(h).view(heads), self.v(h).view(heads)
+        else:
+            hq, hs = quantize_block_rowwise(h.view(B * T, -1))               # one quantization feeds q, k and v
+            q, k, v = (lin.forward_quantized(hq, hs, (B, T)).view(heads) for lin in (self.q, self.k, self.v))
+        q, k, v = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
         if self.kcache is None:
             self.kcache = torch.zeros((B, self.heads_local, max_len, self.head_dim), device=x.device, dtype=x.dtype)
             self.vcache = torch.zeros_like(self.kcache)
@@ -142,8 +146,13 @@ class Layer(nn.Module):
             att = F.scaled_dot_product_attention(q, self.kcache, self.vcache, attn_mask=mask)
         att = att.transpose(1, 2).reshape(B, T, self.heads_local * self.head_dim)
         x = x + self.o(att)
-        hq, hs = quantize_block_rowwise(rms_norm(x).view(B * T, -1))       # ... and one feeds gate and up
-        x = x + self.down(F.silu(self.gate.forward_quantized(hq, hs, (B, T))) * self.up.forward_quantized(hq, hs, (B, T)))
+        h = rms_norm(x)
+        if fused:
+            gate, up = self.gate(h), self.up(h)
+        else:
+            hq, hs = quantize_block_rowwise(h.view(B * T, -1))               # ... and one feeds gate and up
+            gate, up = self.gate.forward_quantized(hq, hs, (B, T)), self.up.forward_quantized(hq, hs, (B, T))
+        x = x + self.down(F.silu(gate) * up)
         return x
 
 

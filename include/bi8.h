@@ -59,6 +59,7 @@ extern "C" {
 #define BI8_GEMM_NO_SEED 4         /* tensor-core kernel: convert partial sums with cvt instead of seeded TMEM */
 #define BI8_GEMM_FORCE_SMALLM 8    /* weight-streaming CUDA-core kernel, M <= 16 (the default choice for M <= 8) */
 #define BI8_GEMM_FORCE_SKINNY 16   /* weight-streaming tensor-core kernel with exchanged operand roles, M <= 32 */
+#define BI8_GEMM_QUANT_IN_KERNEL 32 /* bi8_gemm_dequant_fused_quant, M <= 32: quantize inside the GEMM kernel */
 
 BI8_API int bi8_version(void);
 
@@ -129,10 +130,12 @@ BI8_API int bi8_gemm_block_partials(const int8_t* A, int64_t lda, const int8_t* 
 /* Forward of the layer in one call (block_linear.py:78-80 / 141-143): quantize-on-load GEMM.  x [M,K] of x_dtype, row
  * stride ldx, is quantized per row and block exactly as bi8_quantize_rowwise does and multiplied with the
  * pre-quantized weights Wq [N,K] / sW; the result equals bi8_quantize_rowwise followed by bi8_gemm_dequant.
- * For M <= 32 (N a multiple of 4, K a multiple of 8, 16-byte aligned rows, workspace given) this is ONE kernel:
- * the activations are quantized inside the GEMM as its stages are loaded and xq / sx are not touched.  Every
- * other shape runs the two kernels through the caller's scratch xq [M,K] int8 and sx [ceil(K/block),M] fp32,
- * which may be NULL only when the one-kernel conditions hold.  The scratch contents after the call are
+ * For M <= 32 (N a multiple of 4, K a multiple of 8, 16-byte aligned rows, workspace given) the weight-streaming
+ * tensor-core GEMM runs behind a small quantizer kernel and is launched so that its set-up and first weight
+ * loads overlap that kernel; with BI8_GEMM_QUANT_IN_KERNEL (or without scratch) the GEMM kernel itself quantizes
+ * the activations as it loads its stages: one kernel, no scratch, but measured slower.  Every other shape runs the
+ * standalone quantizer and the GEMM back to back.  xq [M,K] int8 and sx [ceil(K/block),M] fp32 are scratch, which
+ * may be NULL only when the M <= 32 conditions hold.  The scratch contents after the call are
  * unspecified.  workspace as for bi8_gemm_dequant. */
 BI8_API int bi8_gemm_dequant_fused_quant(const void* x, int x_dtype, int64_t ldx, int8_t* xq, float* sx,
                                  const int8_t* Wq, int64_t ldw, const float* sW, const void* bias, int bias_dtype,

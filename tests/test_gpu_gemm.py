@@ -317,9 +317,10 @@ FUSED_SHAPES = [
 
 @pytest.mark.parametrize("shape", FUSED_SHAPES)
 def test_quantize_on_load_gemm(shape):
-    """bi8_gemm_dequant_fused_quant: quantize + GEMM in one call, for M <= 32 inside one kernel.  The quantized
-    activations are bit-identical to the standalone quantizer's, so the result must equal the two-call sequence
-    exactly, which in turn is checked against the oracle."""
+    """bi8_gemm_dequant_fused_quant: quantize + GEMM in one call.  For M <= 32 either a decode quantizer kernel overlapped
+    with the GEMM's start (default) or quantization inside the GEMM kernel (flag 32).  The quantized activations are
+    bit-identical to the standalone quantizer's, so the result must equal the two-call sequence exactly, which in turn
+    is checked against the oracle."""
     from triton_functions import (int8_matmul_block64_rowwise_dequantize as mm, quantize_block_rowwise,
                                   quantize_matmul_block_rowwise_dequantize as qmm)
     m, k, n, block, dtype = shape
@@ -337,6 +338,7 @@ def test_quantize_on_load_gemm(shape):
         two = mm(xq, wqd.t(), xs, wsd, bias.to(DEV))
         one = qmm(xd, wqd.t(), wsd, bias.to(DEV))
         assert torch.equal(one, two)
+        assert torch.equal(qmm(xd, wqd.t(), wsd, bias.to(DEV), flags=32), two), "quantized inside the GEMM kernel"
         assert torch.equal(one, qmm(xd, wqd.t(), wsd, bias.to(DEV))), "deterministic"
     set_config(block, torch.float32)
     oq, os_ = O.quantize(x, block)

@@ -10,16 +10,21 @@
 //   * All (tile, K stage) pairs form one sequence that is cut into equal contiguous ranges, one per CTA and one CTA
 //     per SM, so every SM streams the same number of bytes whatever N and K are.  A range may begin or end inside a
 //     tile: such a part of a tile goes to an fp32 workspace slot (at most two per CTA) and a second kernel adds the
-//     slots of a tile in ascending K order; tiles that lie completely inside one range are written directly.  (Adding
-//     the parts inside the GEMM, by whichever CTA finishes a tile last, was measured slower than the second launch: the
-//     fence, the arrival count and the read-back are three dependent trips to L2 at the end of every CTA.)
-//   * warp P (producer) issues, per stage, three TMA copies that complete on one barrier: 128 weight rows x 128
+//     slots of a tile in ascending K order; tiles that lie completely inside one range are written directly.  That
+//     kernel is launched with programmatic stream serialisation: it becomes resident while this one runs and
+//     griddepcontrol.wait releases it when this grid has completed.  (Adding the parts inside the GEMM, by whichever
+//     CTA finishes a tile last, was measured slower than the second launch: the fence, the arrival count and the
+//     read-back are three dependent trips to L2 at the end of every CTA.)
+//   * Warp roles: promotion warps (four per 16 activation rows, one per tensor-memory lane quarter) convert and scale;
+//     one producer warp issues, per stage, three TMA copies that complete on one barrier: 128 weight rows x 128
 //     K-bytes, the activation rows of the same K range, and the stage's weight scales (a [blocks, 128] fp32 box of
-//     sB); warp P+1 issues the MMAs of the stage, one accumulator range per quantisation block, and commits;
-//     the promotion warps (four per 16 activation rows, one per tensor-memory lane quarter) convert and scale.
+//     sB); two MMA issuer warps take the stages in turn (one accumulator range per quantisation block, one commit per
+//     stage).
 //   * With FUSED the activations arrive as bf16/fp16/fp32 and four more warps quantize, per stage, the 128 K-columns of
 //     every activation row into the stage's operand tile (same arithmetic as the standalone quantizer, written in the
-//     128-byte swizzle the MMA expects) and their block scales into the scale table: quantize-on-load, no extra launch.
+//     128-byte swizzle the MMA expects) and their block scales into the scale table: quantize-on-load in one kernel.
+//     It is the slower of the two quantize-on-load forms; the default one is skinny_quantize_kernel in front of this
+//     kernel, overlapped with its start (see the launch code at the end of the file).
 //   * Promotion follows the reference's order term by term, sB*(sA*(float(P)*fl32(1/127^2))), added in ascending block
 //     order within a range, so a tile that is not divided is bit-identical to the CUDA-core kernel.
 #include "quant_math.cuh"

@@ -32,7 +32,6 @@ if ROOT not in sys.path:
 
 import block_linear_config as cfg  # noqa: E402
 from block_linear import BlockInt8Linear  # noqa: E402
-from triton_functions import int8_matmul_block64_rowwise_dequantize, quantize_block_rowwise  # noqa: E402
 from blockwise_int8_linear_b200.parallel import block_aligned_bounds  # noqa: E402
 
 
@@ -48,19 +47,28 @@ def seeded_weight(out_f, in_f, seed, dev, rows=None, cols=None):
 
 
 class Int8Linear(nn.Module):
-    """A BlockInt8Linear holding this rank's shard.  mode 'col': rows [lo,hi) of the weight, local output.
+    """A BlockInt8Linear holding this rank's shard of one or several projections that share their input.
+
+    mode 'col': rows [lo,hi) of every weight in `out_fs` (q/k/v, or gate/up, are stored as one matrix, so the step runs one
+    GEMM for them; each part keeps its own seed, so the model is the same function as with separate layers), local output.
     mode 'row': columns [lo,hi), fp32 partial output summed over the group."""
 
-    def __init__(self, in_f, out_f, seed, dev, mode, rank, world, block):
+    def __init__(self, in_f, out_fs, seeds, dev, mode, rank, world, block):
         super().__init__()
         self.mode, self.world = mode, world
         if mode == "col":
-            lo, hi = block_aligned_bounds(out_f, world, block)[rank]
-            w = seeded_weight(out_f, in_f, seed, dev, rows=(lo, hi))
+            parts = []
+            for out_f, seed in zip(out_fs, seeds):
+                lo, hi = block_aligned_bounds(out_f, world, block)[rank]
+                parts.append(seeded_weight(out_f, in_f, seed, dev, rows=(lo, hi)))
+            self.bounds = (lo, hi)
+            self.widths = [p.shape[0] for p in parts]
+            w = torch.cat(parts, dim=0) if len(parts) > 1 else parts[0]
         else:
             lo, hi = block_aligned_bounds(in_f, world, block)[rank]
-            w = seeded_weight(out_f, in_f, seed, dev, cols=(lo, hi))
-        self.bounds = (lo, hi)
+            w = seeded_weight(out_fs[0], in_f, seeds[0], dev, cols=(lo, hi))
+            self.bounds = (lo, hi)
+            self.widths = [w.shape[0]]
         self.lin = BlockInt8Linear(w.shape[1], w.shape[0], bias=False, device=dev, dtype=torch.bfloat16)
         self.lin.weight.data = w
         self.lin.eval()
@@ -79,13 +87,6 @@ class Int8Linear(nn.Module):
         dist.all_reduce(part)
         return part.to(prev)
 
-    def forward_quantized(self, xq, xs, lead):
-        """Column-parallel layers that share one input (q/k/v, gate/up) share its quantization: the same two calls
-        BlockInt8Linear.infer makes (reference block_linear.py:141-143), with the first one hoisted by the caller."""
-        assert self.mode == "col" or self.world == 1
-        y = int8_matmul_block64_rowwise_dequantize(xq, self.lin.W_int8.t(), xs, self.lin.state_W, self.lin.bias)
-        return y.view(*lead, -1)
-
 
 def rms_norm(x, eps=1e-5):
     return F.rms_norm(x, (x.shape[-1],), eps=eps)
@@ -99,21 +100,21 @@ def rope_table(max_len, d, dev, theta=10000.0):
 
 
 def rope(x, cis):
-    # x [B, H, T, D] with (even, odd) feature pairs rotated by the position's angle; cis [T, D/2] complex
+    # x [B, T, G, H, D] (G = q and k) with (even, odd) feature pairs rotated by the position's angle; cis [T, D/2] complex
     xc = torch.view_as_complex(x.float().reshape(*x.shape[:-1], -1, 2))
-    return torch.view_as_real(xc * cis[None, None]).flatten(-2).to(x.dtype)
+    return torch.view_as_real(xc * cis[None, :, None, None]).flatten(-2).to(x.dtype)
 
 
 class Layer(nn.Module):
     def __init__(self, i, a, dev, rank, world):
         super().__init__()
         d, f, blk = a.hidden, a.ffn, a.block
-        mk = lambda in_f, out_f, s, mode: Int8Linear(in_f, out_f, 1000 * i + s, dev, mode, rank, world, blk)
-        self.q, self.k, self.v = mk(d, d, 1, "col"), mk(d, d, 2, "col"), mk(d, d, 3, "col")
-        self.o = mk(d, d, 4, "row")
-        self.gate, self.up = mk(d, f, 5, "col"), mk(d, f, 6, "col")
-        self.down = mk(f, d, 7, "row")
-        self.heads_local = (self.q.bounds[1] - self.q.bounds[0]) // a.head_dim
+        mk = lambda in_f, out_fs, seeds, mode: Int8Linear(in_f, out_fs, [1000 * i + s for s in seeds], dev, mode, rank, world, blk)
+        self.qkv = mk(d, (d, d, d), (1, 2, 3), "col")
+        self.o = mk(d, (d,), (4,), "row")
+        self.gate_up = mk(d, (f, f), (5, 6), "col")
+        self.down = mk(f, (d,), (7,), "row")
+        self.heads_local = self.qkv.widths[0] // a.head_dim
         self.head_dim = a.head_dim
         self.kcache = self.vcache = None
 
@@ -122,19 +123,13 @@ class Layer(nn.Module):
         tensor, the cache is written with index_copy_ and attended in full under a mask, so that every shape is static and
         the step can be captured in a CUDA graph.  `cis` holds the rotary factors of this call's positions."""
         B, T, _ = x.shape
-        heads = (B, T, self.heads_local, self.head_dim)
-        fused = B * T <= 32          # decode: every layer quantizes its input inside its GEMM kernel, nothing to share
-        h = rms_norm(x)
-        if fused:
-            q, k, v = self.q(h).view(heads), self.k(h).view(heads), self.v(h).view(heads)
-        else:
-            hq, hs = quantize_block_rowwise(h.view(B * T, -1))               # one quantization feeds q, k and v
-            q, k, v = (lin.forward_quantized(hq, hs, (B, T)).view(heads) for lin in (self.q, self.k, self.v))
-        q, k, v = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+        hl, hd = self.heads_local, self.head_dim
+        qkv = self.qkv(rms_norm(x)).view(B, T, 3, hl, hd)
+        qk = rope(qkv[:, :, :2], cis)                                   # q and k in one pass: [B, T, 2, H, D]
+        q, k, v = qk[:, :, 0].transpose(1, 2), qk[:, :, 1].transpose(1, 2), qkv[:, :, 2].transpose(1, 2)
         if self.kcache is None:
-            self.kcache = torch.zeros((B, self.heads_local, max_len, self.head_dim), device=x.device, dtype=x.dtype)
+            self.kcache = torch.zeros((B, hl, max_len, hd), device=x.device, dtype=x.dtype)
             self.vcache = torch.zeros_like(self.kcache)
-        q, k = rope(q, cis), rope(k, cis)
         if pos_dev is None:
             self.kcache[:, :, pos0:pos0 + T] = k
             self.vcache[:, :, pos0:pos0 + T] = v
@@ -144,14 +139,9 @@ class Layer(nn.Module):
             self.kcache.index_copy_(2, pos_dev, k)
             self.vcache.index_copy_(2, pos_dev, v)
             att = F.scaled_dot_product_attention(q, self.kcache, self.vcache, attn_mask=mask)
-        att = att.transpose(1, 2).reshape(B, T, self.heads_local * self.head_dim)
+        att = att.transpose(1, 2).reshape(B, T, hl * hd)
         x = x + self.o(att)
-        h = rms_norm(x)
-        if fused:
-            gate, up = self.gate(h), self.up(h)
-        else:
-            hq, hs = quantize_block_rowwise(h.view(B * T, -1))               # ... and one feeds gate and up
-            gate, up = self.gate.forward_quantized(hq, hs, (B, T)), self.up.forward_quantized(hq, hs, (B, T))
+        gate, up = self.gate_up(rms_norm(x)).split(self.gate_up.widths, dim=-1)
         x = x + self.down(F.silu(gate) * up)
         return x
 
@@ -162,7 +152,7 @@ class Llama(nn.Module):
         g = torch.Generator(device=dev).manual_seed(7)
         self.emb = (torch.randn((a.vocab, a.hidden), device=dev, generator=g) * 0.02).to(torch.bfloat16)
         self.layers = nn.ModuleList(Layer(i, a, dev, rank, world) for i in range(a.layers))
-        self.head = Int8Linear(a.hidden, a.vocab, 99, dev, "col", rank, world, a.block)
+        self.head = Int8Linear(a.hidden, (a.vocab,), (99,), dev, "col", rank, world, a.block)
         self.world, self.vocab, self.block = world, a.vocab, a.block
         self.cis = rope_table(a.prompt + a.decode, a.head_dim, dev)
         self.positions = torch.arange(a.prompt + a.decode, device=dev)

@@ -89,6 +89,7 @@ struct SkParams {
     int M, N, K, nb, nks;
     int out_dtype, bias_dtype;
     int live_chunks;    // groups of 16 activation rows that hold a valid row
+    int early_weights;  // the weight copies of the first stages may be issued before the preceding kernel has completed
 };
 
 // first (tile, stage) pair of CTA c when `total` pairs are divided over `ctas` CTAs
@@ -181,14 +182,18 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         __syncwarp();
         asm volatile("bar.arrive 2, %0;" ::"n"(G::THREADS) : "memory");
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the reduction kernel may be made resident
+        // The kernel is always launched so that it may start before its predecessor in the stream has completed.  Behind
+        // this library's own activation quantizer the weights are known to be at rest and their copies start at once;
+        // behind any other kernel (which may be the one writing the weights) nothing is read before the wait.
+        if (!p.early_weights) asm volatile("griddepcontrol.wait;" ::: "memory");
         while (pre_count < G::STAGES && s_begin + pre_count < s_end) {
             if (lane == 0) issue_stage(pre_count, pre_tile, pre_ks, false);
             ++pre_count;
             if (++pre_ks == p.nks) { pre_ks = 0; ++pre_tile; }
         }
-        // Everything above touched only the weights and their scales.  The activations may come from the kernel launched
-        // just before this one (a quantizer that lets its dependents start early): wait for it here.
-        asm volatile("griddepcontrol.wait;" ::: "memory");
+        // Everything above touched only the weights and their scales.  The activations come from the kernel launched just
+        // before this one (a quantizer that lets its dependents start early): wait for it here.
+        if (p.early_weights) asm volatile("griddepcontrol.wait;" ::: "memory");
         if (!FUSED && lane == 0) {
             int ks = ks_begin;
             for (int q = 0; q < pre_count; ++q) {
@@ -614,9 +619,7 @@ int launch_skinny(const GemmArgs& g, const SkParams& p, int grid, cudaStream_t s
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    // only behind this library's own activation quantizer: the kernel reads the weights before it waits for its
-    // predecessor, which is wrong behind a kernel that may still be writing them
-    cfg.numAttrs = g.after_own_quantizer ? 1 : 0;
+    cfg.numAttrs = 1;      // what may run before the predecessor has completed is decided in the kernel (early_weights)
     BI8_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tc_skinny_kernel<QB, BNS, FUSED>, mw, mx, ms, p));
     return BI8_OK;
 }
@@ -694,6 +697,7 @@ int launch_gemm_skinny(const GemmArgs& g, cudaStream_t st) {
     p.out_dtype = g.out_dtype;
     p.bias_dtype = g.bias_dtype;
     p.live_chunks = (int)((g.M + 15) / 16);
+    p.early_weights = g.after_own_quantizer ? 1 : 0;
     const long long tiles = (g.N + kTileRows - 1) / kTileRows;
     p.total_stages = tiles * p.nks;
     const int grid = (int)(p.total_stages < di.sms ? p.total_stages : di.sms);

@@ -209,33 +209,64 @@ def time_kernel(fn, reps: int, flush) -> float:
     return ts[len(ts) // 2]
 
 
+def time_graph(fn, reps: int) -> float:
+    """Median milliseconds per launch of fn(i), i = 0..reps-1, captured once in a CUDA graph and replayed 5 times.
+    The caller rotates its inputs over more bytes than L2 holds, so every launch starts cold; nothing but the launches is
+    on the stream, so neither the host nor a flush kernel's dirty lines sit inside the timed region."""
+    for i in range(3):
+        fn(i)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(reps):
+            fn(i)
+    ts = []
+    for _ in range(5):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        graph.replay()
+        b.record()
+        b.synchronize()
+        ts.append(a.elapsed_time(b) / reps)
+    ts.sort()
+    del graph
+    return ts[len(ts) // 2]
+
+
 def extras(dev, hbm_gbs, flush):
-    """Memory-bound kernels (quantize / dequantize sweep) and the other GEMM shapes; cold L2, median of 7."""
+    """Memory-bound kernels (quantize / dequantize sweep) and the other GEMM shapes, cold L2.
+
+    "us" comes from CUDA-graph replays over rotating inputs that together exceed L2 (time_graph); "us_flushed" from events
+    around single eager launches behind a 256 MB fill (time_kernel), which adds the launch latency and the write-back of
+    the fill's dirty lines to a kernel of a few tens of microseconds."""
     import block_linear_config as cfg
     from triton_functions import (dequantize_block_rowwise, int8_matmul_block64_rowwise_dequantize,
                                   quantize_block_colwise, quantize_block_rowwise, quantize_matmul_block_rowwise_dequantize)
     cfg.GROUP_SIZE, cfg.INPUT_OUTPUT_TORCH_TYPE = BLOCK, torch.bfloat16
     out = {"quantize": [], "dequantize": [], "quantize_colwise": [], "gemm": []}
     for n in (4096, 8192, 16384):
-        g = torch.Generator(device=dev).manual_seed(2000 + n)
-        x = torch.randn((n, n), device=dev, dtype=torch.float32, generator=g)
-        x = torch.where(torch.rand((n, n), device=dev, generator=g) < 0.001, x * 20, x).to(torch.bfloat16)
-        nbytes = n * n * (2 + 1 + 4 / BLOCK)
-        for _ in range(3):
+        copies = max(2, -(-(300 << 20) // (n * n * 2)) + 1)
+        xs, qs, ss = [], [], []
+        for c in range(copies):
+            g = torch.Generator(device=dev).manual_seed(2000 + n + c)
+            x = torch.randn((n, n), device=dev, dtype=torch.float32, generator=g)
+            x = torch.where(torch.rand((n, n), device=dev, generator=g) < 0.001, x * 20, x).to(torch.bfloat16)
             q, s = quantize_block_rowwise(x)
-        ms = time_kernel(lambda: quantize_block_rowwise(x), 7, flush)
-        out["quantize"].append({"shape": [n, n], "us": ms * 1e3, "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / hbm_gbs})
-        for _ in range(3):
-            dequantize_block_rowwise(q, s)
-        ms = time_kernel(lambda: dequantize_block_rowwise(q, s), 7, flush)
-        out["dequantize"].append({"shape": [n, n], "us": ms * 1e3, "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / hbm_gbs})
-        for _ in range(3):
-            quantize_block_colwise(x)
-        ms = time_kernel(lambda: quantize_block_colwise(x), 7, flush)
-        out["quantize_colwise"].append({"shape": [n, n], "us": ms * 1e3, "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / hbm_gbs})
-        del x, q, s
+            xs.append(x)
+            qs.append(q)
+            ss.append(s)
+        nbytes = n * n * (2 + 1 + 4 / BLOCK)
+        reps = 2 * copies
+        for key, fn in (("quantize", lambda i: quantize_block_rowwise(xs[i % copies])),
+                        ("dequantize", lambda i: dequantize_block_rowwise(qs[i % copies], ss[i % copies])),
+                        ("quantize_colwise", lambda i: quantize_block_colwise(xs[i % copies]))):
+            ms = time_graph(fn, reps)
+            ms_flushed = time_kernel(lambda: fn(0), 7, flush)
+            out[key].append({"shape": [n, n], "us": ms * 1e3, "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / hbm_gbs,
+                             "us_flushed": ms_flushed * 1e3, "frac_hbm_flushed": nbytes / ms_flushed / 1e6 / hbm_gbs})
+        del xs, qs, ss
     # Llama-7B projection shapes.  "us" times the GEMM on pre-quantized activations, "us_linear" the layer's forward from
-    # bf16 activations (quantize + GEMM: for M <= 32 one library call whose kernels overlap).  Launches of a few
+    # bf16 activations (quantize + GEMM: for M <= 64 one library call whose kernels overlap).  Launches of a few
     # microseconds are timed as CUDA-graph replays of 16 launches that rotate over enough weight copies to exceed L2
     # (an eager loop would time the host); the large ones with events around one launch after an L2 flush.
     for (k, n) in ((4096, 4096), (4096, 11008), (11008, 4096)):
@@ -255,34 +286,18 @@ def extras(dev, hbm_gbs, flush):
                 return int8_matmul_block64_rowwise_dequantize(xq, wqs[i % copies].t(), xs, wss[i % copies])
 
             def linear(i):
-                if m <= 32:
+                if m <= 64:
                     return quantize_matmul_block_rowwise_dequantize(x, wqs[i % copies].t(), wss[i % copies])
                 q, st = quantize_block_rowwise(x)
                 return int8_matmul_block64_rowwise_dequantize(q, wqs[i % copies].t(), st, wss[i % copies])
 
             times = {}
             for name, fn in (("us", gemm), ("us_linear", linear)):
-                for i in range(3):
-                    fn(i)
                 if m <= 128:
-                    reps = max(16, copies)
-                    torch.cuda.synchronize()
-                    graph = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(graph):
-                        for i in range(reps):
-                            fn(i)
-                    ts = []
-                    for _ in range(5):
-                        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                        a.record()
-                        graph.replay()
-                        b.record()
-                        b.synchronize()
-                        ts.append(a.elapsed_time(b) / reps)
-                    ts.sort()
-                    times[name] = ts[len(ts) // 2]
-                    del graph
+                    times[name] = time_graph(fn, max(16, copies))
                 else:
+                    for i in range(3):
+                        fn(i)
                     times[name] = time_kernel(lambda: fn(0), 7, flush)
             ms = times["us"]
             ops = 2.0 * m * n * k
@@ -455,7 +470,8 @@ def run_ours(args):
         extra = extras(dev, hbm_gbs, flush)
         extra["hbm_peak_gbs"] = hbm_gbs
         extra["hbm_peak_source"] = peak_src
-        extra["timing"] = "CUDA events, L2 flushed (256 MB fill) before every launch, median of 7"
+        extra["timing"] = ("us: CUDA-graph replays over rotating inputs larger than L2, median of 5 replays; us_flushed and the "
+                           "GEMM rows marked so: CUDA events around one launch behind a 256 MB fill, median of 7")
     cpu = None
     if world == 1 and not args.no_cpu:
         cpu, _ = cpu_baseline(args.workload)

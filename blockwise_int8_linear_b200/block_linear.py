@@ -124,8 +124,8 @@ class BlockInt8Linear(nn.Linear):
         if not hasattr(self, "W_int8"):
             self.prepare_for_eval()
         X = x.reshape(-1, x.size(-1))
-        if X.size(0) <= 32:
-            # decode-sized batches: the same two steps in one kernel (the GEMM quantizes the activations as it loads them)
+        if X.size(0) <= 64:
+            # decode-sized batches: the same two steps in one library call whose kernels overlap
             return quantize_matmul_block_rowwise_dequantize(X, self.W_int8.t(), self.state_W, self.bias).view(*x.size()[:-1], -1)
         X_int8, state_X = quantize_block_rowwise(X)
         return int8_matmul_block64_rowwise_dequantize(

@@ -76,12 +76,12 @@ int dispatch_gemm(const GemmArgs& g, cudaStream_t st) {
     }
     if (g.flags & BI8_GEMM_FORCE_SKINNY) {
         if (!gemm_skinny_applicable(g))
-            return fail(BI8_ERR_ALIGN, "skinny tensor-core GEMM not applicable (needs M <= 32, block 32/64/128, N %% 4 == 0, 16-byte aligned "
+            return fail(BI8_ERR_ALIGN, "skinny tensor-core GEMM not applicable (needs M <= 64, block 32/64/128, N %% 4 == 0, 16-byte aligned "
                                        "operand rows and weight scales, and the workspace bi8_gemm_workspace_bytes() asks for)");
         return launch_gemm_skinny(g, st);
     }
     const bool free_choice = !(g.flags & (BI8_GEMM_FORCE_TC | BI8_GEMM_FORCE_GENERIC)) && g.K > 0;
-    // M <= 32: one pass over the weights on the tensor cores with exchanged operand roles (needs the workspace)
+    // M <= 64: one pass over the weights on the tensor cores with exchanged operand roles (needs the workspace)
     if (free_choice && gemm_skinny_applicable(g)) return launch_gemm_skinny(g, st);
     // otherwise M <= 8 streams the weights on the CUDA cores; 9..16 would stream them twice and is faster on the
     // general tensor-core kernel
@@ -192,22 +192,27 @@ int bi8_gemm_dequant_fused_quant(const void* x, int x_dtype, int64_t ldx, int8_t
     if (!dtype_ok(x_dtype)) return fail(BI8_ERR_DTYPE, "gemm_dequant_fused_quant: unknown dtype code %d", x_dtype);
     const bool forced = (flags & (BI8_GEMM_FORCE_GENERIC | BI8_GEMM_FORCE_TC | BI8_GEMM_FORCE_SMALLM)) != 0;
     if (!forced && x && M > 0 && N > 0 && K > 0 && ldx >= K && aligned(x, dtype_size(x_dtype))) {
-        GemmArgs g{nullptr, K, Wq, ldw, nullptr, sW, bias, bias_dtype, C, ldc, out_dtype, nullptr, M, N, K, block, flags, workspace, workspace_bytes};
-        g.X = x;
-        g.x_dtype = x_dtype;
-        g.ldx = ldx;
-        if (gemm_skinny_applicable(g)) {
+        GemmArgs g{xq, K, Wq, ldw, sx, sW, bias, bias_dtype, C, ldc, out_dtype, nullptr, M, N, K, block, flags, workspace, workspace_bytes};
+        const bool x_vec = aligned(x, 16) && (ldx * dtype_size(x_dtype)) % 16 == 0 && K % 8 == 0;   // 8 elements per load
+        const bool chained = !(flags & BI8_GEMM_QUANT_IN_KERNEL) && x_vec && xq && sx && K % 16 == 0 && aligned(xq, 16) &&
+                             gemm_skinny_applicable(g);
+        bool in_kernel = false;
+        if (!chained) {
+            g.A = nullptr;
+            g.sA = nullptr;
+            g.X = x;
+            g.x_dtype = x_dtype;
+            g.ldx = ldx;
+            in_kernel = gemm_skinny_applicable(g);
+        }
+        if (chained || in_kernel) {
             if (!Wq || !sW || !C) return fail(BI8_ERR_NULL, "gemm_dequant_fused_quant: null pointer");
             if (ldw < K || ldc < N) return fail(BI8_ERR_SHAPE, "gemm_dequant_fused_quant: row pitch smaller than the row");
             if (!dtype_ok(out_dtype) || (bias && !dtype_ok(bias_dtype))) return fail(BI8_ERR_DTYPE, "gemm_dequant_fused_quant: unknown dtype code");
             if (!aligned(C, dtype_size(out_dtype))) return fail(BI8_ERR_ALIGN, "gemm_dequant_fused_quant: output not element aligned");
-            const bool in_kernel = (flags & BI8_GEMM_QUANT_IN_KERNEL) || !xq || !sx || K % 16 != 0 || !aligned(xq, 16);
             if (in_kernel) return launch_gemm_skinny(g, static_cast<cudaStream_t>(stream));
             int rc = launch_skinny_quantize(x, x_dtype, ldx, xq, sx, M, K, block, static_cast<cudaStream_t>(stream));
             if (rc != BI8_OK) return rc;
-            g.X = nullptr;
-            g.A = xq;
-            g.sA = sx;
             g.after_own_quantizer = true;
             return launch_gemm_skinny(g, static_cast<cudaStream_t>(stream));
         }

@@ -1,12 +1,12 @@
-// Int8 block GEMM with fused dequantize for a handful of activation rows (decode: M <= 32), on the sm_100a tensor
+// Int8 block GEMM with fused dequantize for few activation rows (decode and small batches: M <= 64), on the sm_100a tensor
 // cores with the operand roles exchanged.
 //
 // Same contract as the reference kernel at triton_functions.py:69-139 (path inside the reference project).  With so few
 // rows of A the work is one pass over the weights Bt[N, K]: the kernel is bound by streaming them from HBM, and is
 // organised around that stream.
-//   * The weights are the M operand of the MMA: a tile is 128 weight rows, the activations (padded to 16 or 32 rows by
-//     the TMA's zero fill) are the N operand, so one tcgen05.mma kind::i8 (M128 N16|32 K32) covers 128 weight rows
-//     and every activation row, and the s32 accumulator of a quantisation block is only 16|32 tensor-memory columns.
+//   * The weights are the M operand of the MMA: a tile is 128 weight rows, the activations (padded to 16, 32 or 64
+//     rows by the TMA's zero fill) are the N operand, so one tcgen05.mma kind::i8 (M128 N16..64 K32) covers 128 weight
+//     rows and every activation row, and the s32 accumulator of a quantisation block is only 16..64 tensor-memory columns.
 //   * All (tile, K stage) pairs form one sequence that is cut into equal contiguous ranges, one per CTA and one CTA
 //     per SM, so every SM streams the same number of bytes whatever N and K are.  A range may begin or end inside a
 //     tile: such a part of a tile goes to an fp32 workspace slot (at most two per CTA) and a second kernel adds the
@@ -15,7 +15,8 @@
 //     griddepcontrol.wait releases it when this grid has completed.  (Adding the parts inside the GEMM, by whichever
 //     CTA finishes a tile last, was measured slower than the second launch: the fence, the arrival count and the
 //     read-back are three dependent trips to L2 at the end of every CTA.)
-//   * Warp roles: promotion warps (four per 16 activation rows, one per tensor-memory lane quarter) convert and scale;
+//   * Warp roles: promotion warps (four per 16 activation rows, or per 32 for 64 rows; one per tensor-memory lane
+//     quarter) convert and scale;
 //     one producer warp issues, per stage, three TMA copies that complete on one barrier: 128 weight rows x 128
 //     K-bytes, the activation rows of the same K range, and the stage's weight scales (a [blocks, 128] fp32 box of
 //     sB); two MMA issuer warps take the stages in turn (one accumulator range per quantisation block, one commit per
@@ -38,8 +39,9 @@ namespace {
 using namespace ptx;
 
 constexpr int kTileRows = 128;    // weight rows per tile (the MMA's M)
-constexpr int kSkMaxM = 32;
-constexpr size_t kSxMaxBytes = 48 * 1024;   // activation scales staged per CTA (with the stage ring: under 227 KiB)
+constexpr int kSkMaxM = 64;       // beyond 64 activation rows the promotion (5 instructions per element and block, in the
+                                  // reference's order) costs more than the weights take to arrive: measured slower than
+                                  // the general kernel at 128 rows
 
 constexpr int pow2_at_least(int x) {
     int p = 32;
@@ -57,8 +59,10 @@ struct SkGeo {
     static constexpr int STAGES = BNS == 16 ? 8 : 6;
     static constexpr int BPS = kBK / QB;                  // quantisation blocks per stage
     static constexpr int MMAS = QB / 32;                  // MMAs (K = 32) per block
-    static constexpr int CHUNKS = BNS / 16;               // groups of 16 activation rows
+    static constexpr int CW = BNS <= 32 ? 16 : 32;        // activation rows (accumulator columns) per promotion warp
+    static constexpr int CHUNKS = BNS / CW;
     static constexpr int PROMO_WARPS = 4 * CHUNKS;
+    static constexpr int VB = CW == 16 ? BPS : 1;         // blocks whose accumulators a promotion thread loads at once
     static constexpr int THREADS = (PROMO_WARPS + 1 + kMmaWarps + (FUSED ? kQuantWarps : 0)) * 32;
     static constexpr int ACC_STRIDE = BPS * BNS;          // tensor-memory columns of one stage's accumulators
     static constexpr int NBUF = (512 / ACC_STRIDE) < 4 ? (512 / ACC_STRIDE) : 4;
@@ -75,6 +79,12 @@ struct SkGeo {
     static constexpr uint32_t sx_off = (misc_off + 32 + 15) & ~15u;       // activation scales [nb][BNS]
 };
 
+// dynamic shared memory of a launch: stage ring, barriers, activation scales [nb][BNS], alignment slack
+template <int QB, int BNS, bool FUSED>
+constexpr size_t smem_of(int nb) {
+    return (size_t)SkGeo<QB, BNS, FUSED>::sx_off + (size_t)nb * BNS * 4 + 1024;
+}
+
 struct SkParams {
     const float* sA;
     const void* X;          // FUSED: activations before quantization, row pitch ldx elements
@@ -88,7 +98,7 @@ struct SkParams {
     long long total_stages;
     int M, N, K, nb, nks;
     int out_dtype, bias_dtype;
-    int live_chunks;    // groups of 16 activation rows that hold a valid row
+    int live_chunks;    // groups of CW activation rows that hold a valid row
     int early_weights;  // the weight copies of the first stages may be issued before the preceding kernel has completed
 };
 
@@ -382,7 +392,8 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         // ---------------- promotion + epilogue: warp = 4 * chunk + lane quarter ----------------
         const int quarter = warp & 3, chunk = warp >> 2;
         const int row = quarter * 32 + lane;                       // weight row inside the tile
-        const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(chunk * 16);
+        constexpr int CW = G::CW;
+        const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(chunk * CW);
         const float div = 1.0f / (127.0f * 127.0f);
         asm volatile("griddepcontrol.wait;" ::: "memory");      // activation scales, and every store, after the previous kernel
 
@@ -413,9 +424,9 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
             const long long left = s_end - s;
             const int len = (long long)(p.nks - ks0) < left ? (p.nks - ks0) : (int)left;
             const int ks1 = ks0 + len;
-            float acc[16];
+            float acc[CW];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) acc[i] = 0.0f;
+            for (int i = 0; i < CW; ++i) acc[i] = 0.0f;
 
             for (int ks = ks0; ks < ks1; ++ks) {
                 // the stage's barrier is waited on here as well: this warp reads the scales the TMA wrote
@@ -430,37 +441,45 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
                     break;
                 }
                 tc_fence_after();
-                uint32_t v[G::BPS][16];
+                uint32_t v[G::VB][CW];
                 float sw[G::BPS];
                 const uint32_t sc_u32 = base + (uint32_t)stage * G::STAGE_BYTES + G::W_BYTES + G::X_BYTES + (uint32_t)(row * 4);
 #pragma unroll
-                for (int blk = 0; blk < G::BPS; ++blk) {
-                    tmem_ld16(t_lane + (uint32_t)(buf * G::ACC_STRIDE + blk * BNS), v[blk]);
-                    sw[blk] = lds_f32(sc_u32 + (uint32_t)(blk * kTileRows * 4));
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar(G::EMPTY_AB + stage));       // scales are in registers
-                tmem_wait_ld();
+                for (int b0 = 0; b0 < G::BPS; b0 += G::VB) {
 #pragma unroll
-                for (int blk = 0; blk < G::BPS; ++blk) {
-                    const int j = ks * G::BPS + blk;
-                    if (j < p.nb) {
-                        const uint32_t sxa = sx_u32 + (uint32_t)((j * BNS + chunk * 16) * 4);
+                    for (int vb = 0; vb < G::VB; ++vb) {
+                        const uint32_t ta = t_lane + (uint32_t)(buf * G::ACC_STRIDE + (b0 + vb) * BNS);
+                        if constexpr (CW == 16) tmem_ld16(ta, v[vb]);
+                        else tmem_ld32(ta, v[vb]);
+                    }
+                    if (b0 == 0) {
 #pragma unroll
-                        for (int q = 0; q < 2; ++q) {
-                            uint64_t a0, a1, a2, a3;
-                            lds_2xb64(sxa + (uint32_t)(q * 32), a0, a1);
-                            lds_2xb64(sxa + (uint32_t)(q * 32 + 16), a2, a3);
-                            float sv[8];
-                            unpack_f32x2(a0, sv[0], sv[1]);
-                            unpack_f32x2(a1, sv[2], sv[3]);
-                            unpack_f32x2(a2, sv[4], sv[5]);
-                            unpack_f32x2(a3, sv[6], sv[7]);
+                        for (int blk = 0; blk < G::BPS; ++blk) sw[blk] = lds_f32(sc_u32 + (uint32_t)(blk * kTileRows * 4));
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar(G::EMPTY_AB + stage));       // scales are in registers
+                    }
+                    tmem_wait_ld();
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                // the reference's order for one term: sB * (sA * (float(P) * 1/127^2))
-                                const float pf = __fmul_rn((float)(int32_t)v[blk][q * 8 + i], div);
-                                acc[q * 8 + i] = __fadd_rn(acc[q * 8 + i], __fmul_rn(sw[blk], __fmul_rn(sv[i], pf)));
+                    for (int vb = 0; vb < G::VB; ++vb) {
+                        const int blk = b0 + vb, j = ks * G::BPS + blk;
+                        if (j < p.nb) {
+                            const uint32_t sxa = sx_u32 + (uint32_t)((j * BNS + chunk * CW) * 4);
+#pragma unroll
+                            for (int q = 0; q < CW / 8; ++q) {
+                                uint64_t a0, a1, a2, a3;
+                                lds_2xb64(sxa + (uint32_t)(q * 32), a0, a1);
+                                lds_2xb64(sxa + (uint32_t)(q * 32 + 16), a2, a3);
+                                float sv[8];
+                                unpack_f32x2(a0, sv[0], sv[1]);
+                                unpack_f32x2(a1, sv[2], sv[3]);
+                                unpack_f32x2(a2, sv[4], sv[5]);
+                                unpack_f32x2(a3, sv[6], sv[7]);
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) {
+                                    // the reference's order for one term: sB * (sA * (float(P) * 1/127^2))
+                                    const float pf = __fmul_rn((float)(int32_t)v[vb][q * 8 + i], div);
+                                    acc[q * 8 + i] = __fadd_rn(acc[q * 8 + i], __fmul_rn(sw[blk], __fmul_rn(sv[i], pf)));
+                                }
                             }
                         }
                     }
@@ -477,18 +496,18 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
             if (ks0 == 0 && ks1 == p.nks) {
                 if (n < p.N) {
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const int m = chunk * 16 + i;
+                    for (int i = 0; i < CW; ++i) {
+                        const int m = chunk * CW + i;
                         if (m < p.M) finish_store(acc[i], m, n, p.bias, p.bias_dtype, p.C, p.ldc, p.out_dtype);
                     }
                 }
             } else {
                 // part of a tile: slot 0 of this CTA if the part begins where the CTA's range begins, else slot 1
                 const long long slot = 2ll * blockIdx.x + (s == s_begin ? 0 : 1);
-                float* w = p.ws + (slot * BNS + chunk * 16) * kTileRows + row;
+                float* w = p.ws + (slot * BNS + chunk * CW) * kTileRows + row;
 #pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    if (chunk * 16 + i < p.M) w[i * kTileRows] = acc[i];
+                for (int i = 0; i < CW; ++i)
+                    if (chunk * CW + i < p.M) w[i * kTileRows] = acc[i];
             }
             s += len;
         }
@@ -607,7 +626,7 @@ int launch_skinny(const GemmArgs& g, const SkParams& p, int grid, cudaStream_t s
     }
     rc = make_scale_map(&ms, g.sB, p.nb, g.N, kTileRows, G::BPS);
     if (rc != BI8_OK) return rc;
-    const size_t smem = (size_t)G::sx_off + (size_t)p.nb * BNS * 4 + 1024;
+    const size_t smem = smem_of<QB, BNS, FUSED>(p.nb);
     BI8_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_skinny_kernel<QB, BNS, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     cudaLaunchConfig_t cfg;
     std::memset(&cfg, 0, sizeof(cfg));
@@ -624,15 +643,32 @@ int launch_skinny(const GemmArgs& g, const SkParams& p, int grid, cudaStream_t s
     return BI8_OK;
 }
 
-int bns_for(int64_t M) { return M <= 16 ? 16 : 32; }
+int bns_for(int64_t M) { return M <= 16 ? 16 : M <= 32 ? 32 : 64; }
+
+// dynamic shared memory of a launch; 0 for combinations that are not built
+size_t skinny_smem(int block, int bns, bool fused, int nb);
+
+size_t skinny_smem(int block, int bns, bool fused, int nb) {
+#define BI8_SM(QB, BNS) \
+    if (block == QB && bns == BNS) return fused ? (BNS <= 32 ? smem_of<QB, (BNS <= 32 ? BNS : 16), true>(nb) : 0) : smem_of<QB, BNS, false>(nb)
+    BI8_SM(32, 16); BI8_SM(32, 32); BI8_SM(32, 64);
+    BI8_SM(64, 16); BI8_SM(64, 32); BI8_SM(64, 64);
+    BI8_SM(128, 16); BI8_SM(128, 32); BI8_SM(128, 64);
+#undef BI8_SM
+    return 0;
+}
+
+constexpr size_t kSmemLimit = 227 * 1024;
 
 // conditions that depend on the shape only (the workspace query knows nothing else)
-bool skinny_shape_ok(int64_t M, int64_t N, int64_t K, int block) {
+bool skinny_shape_ok(int64_t M, int64_t N, int64_t K, int block, bool fused = false) {
     if (M < 1 || M > kSkMaxM || N < 1 || K < 1) return false;
     if (block != 32 && block != 64 && block != 128) return false;
     if (N % 4 != 0 || N >= (1ll << 30) || K >= (1ll << 30)) return false;
     const int64_t nb = (K + block - 1) / block;
-    return (size_t)nb * bns_for(M) * 4 <= kSxMaxBytes;
+    if (nb > (1 << 20)) return false;
+    const size_t smem = skinny_smem(block, bns_for(M), fused, (int)nb);
+    return smem != 0 && smem <= kSmemLimit;
 }
 
 }  // namespace
@@ -660,7 +696,7 @@ int launch_skinny_quantize(const void* x, int x_dtype, int64_t ldx, int8_t* q, f
 }
 
 bool gemm_skinny_applicable(const GemmArgs& g) {
-    if (g.partials != nullptr || !skinny_shape_ok(g.M, g.N, g.K, g.block)) return false;
+    if (g.partials != nullptr || !skinny_shape_ok(g.M, g.N, g.K, g.block, g.X != nullptr)) return false;
     if (!device_info().ok) return false;
     if (!aligned(g.Bt, 16) || g.ldb % 16 != 0 || !aligned(g.sB, 16)) return false;
     if (g.X != nullptr) {
@@ -696,22 +732,22 @@ int launch_gemm_skinny(const GemmArgs& g, cudaStream_t st) {
     p.nks = (int)((g.K + kBK - 1) / kBK);
     p.out_dtype = g.out_dtype;
     p.bias_dtype = g.bias_dtype;
-    p.live_chunks = (int)((g.M + 15) / 16);
+    const int bns = bns_for(g.M), cw = bns <= 32 ? 16 : 32;
+    p.live_chunks = (int)((g.M + cw - 1) / cw);
     p.early_weights = g.after_own_quantizer ? 1 : 0;
     const long long tiles = (g.N + kTileRows - 1) / kTileRows;
     p.total_stages = tiles * p.nks;
     const int grid = (int)(p.total_stages < di.sms ? p.total_stages : di.sms);
-    const bool wide = g.M > 16, fused = g.X != nullptr;
-    int rc;
-#define BI8_SK(QB)                                                                                                    \
-    rc = fused ? (wide ? launch_skinny<QB, 32, true>(g, p, grid, st) : launch_skinny<QB, 16, true>(g, p, grid, st))  \
-               : (wide ? launch_skinny<QB, 32, false>(g, p, grid, st) : launch_skinny<QB, 16, false>(g, p, grid, st))
-    switch (g.block) {
-        case 32: BI8_SK(32); break;
-        case 64: BI8_SK(64); break;
-        case 128: BI8_SK(128); break;
-        default: return fail(BI8_ERR_BLOCK, "tensor-core GEMM supports block 32, 64, 128 (got %d)", g.block);
+    const bool fused = g.X != nullptr;
+    int rc = BI8_ERR_SHAPE;
+#define BI8_SK(QB, BNS)                                                                                               \
+    if (g.block == QB && bns == BNS) {                                                                                \
+        if (fused) rc = launch_skinny<QB, (BNS <= 32 ? BNS : 16), true>(g, p, grid, st);                              \
+        else rc = launch_skinny<QB, BNS, false>(g, p, grid, st);                                                      \
     }
+    BI8_SK(32, 16) BI8_SK(32, 32) BI8_SK(32, 64)
+    BI8_SK(64, 16) BI8_SK(64, 32) BI8_SK(64, 64)
+    BI8_SK(128, 16) BI8_SK(128, 32) BI8_SK(128, 64)
 #undef BI8_SK
     if (rc != BI8_OK) return rc;
     if (p.total_stages % grid == 0 && (p.total_stages / grid) % p.nks == 0) return BI8_OK;   // no tile is divided
@@ -726,7 +762,7 @@ int launch_gemm_skinny(const GemmArgs& g, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    BI8_CUDA_TRY(cudaLaunchKernelEx(&cfg, skinny_reduce_kernel, (const float*)p.ws, p.total_stages, grid, p.nks, wide ? 32 : 16,
+    BI8_CUDA_TRY(cudaLaunchKernelEx(&cfg, skinny_reduce_kernel, (const float*)p.ws, p.total_stages, grid, p.nks, bns,
                                     g.bias, g.bias_dtype, g.C, g.ldc, g.out_dtype, (int)g.M, (int)g.N));
     return BI8_OK;
 }

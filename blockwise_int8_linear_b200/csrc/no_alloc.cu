@@ -60,18 +60,27 @@ size_t bi8_gemm_static_scratch_bytes(void) { return bi8::kScratchBytes; }
 int bi8_gemm_dequant_static(const int8_t* A, int64_t lda, const int8_t* Bt, int64_t ldb, const float* sA, const float* sB,
                             const void* bias, int bias_dtype, void* C, int64_t ldc, int out_dtype, int64_t M, int64_t N,
                             int64_t K, int block, int flags, void* stream) {
-    const size_t need = bi8_gemm_workspace_bytes(M, N, K, block);
+    // the plan that cannot be left out: split-K of the general kernel.  (The decode kernel for M <= 64 asks for more
+    // rows of scratch as M grows; where the array does not hold that, the dispatcher simply takes the general kernel.)
+    bi8::GemmArgs shape{};
+    shape.M = M;
+    shape.N = N;
+    shape.K = K;
+    shape.block = block;
+    const size_t need = (M > 0 && N > 0 && K > 0 && (block == 32 || block == 64 || block == 128)) ? bi8::gemm_tc_workspace_bytes(shape) : 0;
     if (need > bi8::kScratchBytes)
         return bi8::fail(BI8_ERR_LIMIT,
                          "gemm_dequant_static: this shape needs %zu bytes of split-K scratch, the built-in array holds %zu; "
                          "use bi8_gemm_dequant with a caller workspace",
                          need, bi8::kScratchBytes);
     void* scratch = nullptr;
-    if (need > 0) {
+    size_t given = 0;
+    if (bi8_gemm_workspace_bytes(M, N, K, block) > 0) {
         scratch = bi8::scratch_ptr();
         if (!scratch) return BI8_ERR_CUDA;
+        given = bi8::kScratchBytes;
     }
-    return bi8_gemm_dequant(A, lda, Bt, ldb, sA, sB, bias, bias_dtype, C, ldc, out_dtype, M, N, K, block, scratch, need, flags,
+    return bi8_gemm_dequant(A, lda, Bt, ldb, sA, sB, bias, bias_dtype, C, ldc, out_dtype, M, N, K, block, scratch, given, flags,
                             stream);
 }
 

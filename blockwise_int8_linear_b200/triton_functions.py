@@ -207,8 +207,8 @@ def int8_matmul_block64_rowwise_dequantize(a, b, state_x, state_w, bias=None, *,
 def quantize_matmul_block_rowwise_dequantize(x, b, state_w, bias=None, *, flags: int = 0):
     """``int8_matmul_block64_rowwise_dequantize(*quantize_block_rowwise(x), ...)`` in one library call: the two steps
     of the layer's forward (``block_linear.py:141-143``).  ``x [M, K]`` floating point, ``b [K, N]`` int8 (the ``.t()``
-    view of the ``[N, K]`` weights), ``state_w [ceil(K/block), N]``.  For ``M <= 32`` the activations are quantized
-    inside the GEMM kernel (quantize-on-load); the result is bit-identical to the two separate calls either way."""
+    view of the ``[N, K]`` weights), ``state_w [ceil(K/block), N]``.  For ``M <= 64`` a decode quantizer runs
+    overlapped with the start of the weight-streaming GEMM; the result is bit-identical to the two separate calls either way."""
     block = _block()
     assert x.is_cuda
     if x.dim() != 2:

@@ -58,7 +58,7 @@ extern "C" {
 #define BI8_GEMM_FORCE_TC 2        /* fail with BI8_ERR_ALIGN instead of falling back */
 #define BI8_GEMM_NO_SEED 4         /* tensor-core kernel: convert partial sums with cvt instead of seeded TMEM */
 #define BI8_GEMM_FORCE_SMALLM 8    /* weight-streaming CUDA-core kernel, M <= 16 (the default choice for M <= 8) */
-#define BI8_GEMM_FORCE_SKINNY 16   /* weight-streaming tensor-core kernel with exchanged operand roles, M <= 32 */
+#define BI8_GEMM_FORCE_SKINNY 16   /* weight-streaming tensor-core kernel with exchanged operand roles, M <= 64 */
 #define BI8_GEMM_QUANT_IN_KERNEL 32 /* bi8_gemm_dequant_fused_quant, M <= 32: quantize inside the GEMM kernel */
 
 BI8_API int bi8_version(void);
@@ -115,7 +115,8 @@ BI8_API size_t bi8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int blo
  * more returns BI8_ERR_LIMIT.  No cudaMalloc/cudaFree or allocating library call is made.  The first call on a
  * device looks up the array's device address: make it outside any stream capture.  All calls share the array
  * (nothing needs clearing between calls); calls that can overlap on one GPU race on it and must be serialised by
- * the caller.  Arguments and results are those of bi8_gemm_dequant. */
+ * the caller.  Arguments and results are those of bi8_gemm_dequant (bit-identical where both select the same kernel;
+ * for 33 <= M <= 64 this entry point's scratch is too small for the decode kernel and the general kernel runs). */
 BI8_API int bi8_gemm_dequant_static(const int8_t* A, int64_t lda, const int8_t* Bt, int64_t ldb,
                             const float* sA, const float* sB, const void* bias, int bias_dtype,
                             void* C, int64_t ldc, int out_dtype, int64_t M, int64_t N, int64_t K, int block,
@@ -130,9 +131,9 @@ BI8_API int bi8_gemm_block_partials(const int8_t* A, int64_t lda, const int8_t* 
 /* Forward of the layer in one call (block_linear.py:78-80 / 141-143): quantize-on-load GEMM.  x [M,K] of x_dtype, row
  * stride ldx, is quantized per row and block exactly as bi8_quantize_rowwise does and multiplied with the
  * pre-quantized weights Wq [N,K] / sW; the result equals bi8_quantize_rowwise followed by bi8_gemm_dequant.
- * For M <= 32 (N a multiple of 4, K a multiple of 8, 16-byte aligned rows, workspace given) the weight-streaming
+ * For M <= 64 (N a multiple of 4, K a multiple of 16, 16-byte aligned rows, workspace given) the weight-streaming
  * tensor-core GEMM runs behind a small quantizer kernel and is launched so that its set-up and first weight
- * loads overlap that kernel; with BI8_GEMM_QUANT_IN_KERNEL (or without scratch) the GEMM kernel itself quantizes
+ * loads overlap that kernel; with BI8_GEMM_QUANT_IN_KERNEL (or without scratch; M <= 32) the GEMM kernel itself quantizes
  * the activations as it loads its stages: one kernel, no scratch, but measured slower.  Every other shape runs the
  * standalone quantizer and the GEMM back to back.  xq [M,K] int8 and sx [ceil(K/block),M] fp32 are scratch, which
  * may be NULL only when the M <= 32 conditions hold.  The scratch contents after the call are

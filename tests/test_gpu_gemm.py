@@ -279,12 +279,15 @@ SKINNY_SHAPES = [
     (3, 192, 36, 32), (8, 1056, 132, 32), (16, 2048, 256, 128), (7, 416, 52, 128), (2, 11008, 64, 64),
     (17, 512, 384, 64), (32, 4096, 640, 64), (25, 1056, 260, 32), (32, 2048, 128, 128), (8, 4096, 11008, 64),
     (4, 128, 40000, 64), (12, 80, 24, 32),
+    # 33..64 activation rows: promotion warps of 32 columns
+    (33, 512, 384, 64), (64, 4096, 640, 64), (50, 1056, 260, 64), (64, 2048, 256, 128), (48, 4096, 1024, 64),
+    (64, 1056, 132, 32), (41, 11008, 128, 64),
 ]
 
 
 @pytest.mark.parametrize("shape", SKINNY_SHAPES)
 def test_skinny_tensor_core_kernel(shape):
-    """M <= 32 (decode): tensor-core kernel with exchanged operand roles.  Terms are evaluated in the reference's order;
+    """M <= 64 (decode, small batches): tensor-core kernel with exchanged operand roles.  Terms are evaluated in the reference's order;
     a tile whose K range is divided over CTAs adds its parts in a fixed order, so the tensor-core tolerance applies and
     repeated calls are bit-identical."""
     m, k, n, block = shape
@@ -299,7 +302,7 @@ def test_skinny_tensor_core_kernel(shape):
     _check_bf16(_gemm(xq, wq, xs, ws, bias, flags=SKINNY), xq, wq, xs, ws, block, bias)
     from blockwise_int8_linear_b200._lib import Bi8Error
     with pytest.raises(Bi8Error):
-        big = quantized_pair(33, 128, 32, block, seed=1)
+        big = quantized_pair(65, 128, 32, block, seed=1)
         _gemm(big[0], big[2], big[1], big[3], flags=SKINNY)
     assert_clean_device()
     set_config(64)
@@ -311,7 +314,8 @@ FUSED_SHAPES = [
     (16, 4096, 1024, 64, torch.float16), (7, 416, 52, 128, torch.float32), (3, 208, 36, 32, torch.bfloat16),
     (17, 512, 384, 64, torch.bfloat16), (32, 1056, 260, 32, torch.float32), (32, 2048, 128, 128, torch.float16),
     (8, 4096, 11008, 64, torch.bfloat16), (2, 11008, 4096, 64, torch.bfloat16),
-    (40, 512, 256, 64, torch.bfloat16), (4, 512, 50, 64, torch.bfloat16),      # not eligible: run as two kernels
+    (40, 512, 256, 64, torch.bfloat16), (64, 4096, 512, 64, torch.bfloat16), (50, 1056, 260, 128, torch.float16),
+    (4, 512, 50, 64, torch.bfloat16), (200, 512, 256, 64, torch.bfloat16),     # not eligible: run as two kernels
 ]
 
 

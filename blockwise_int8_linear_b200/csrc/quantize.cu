@@ -280,6 +280,48 @@ __global__ void __launch_bounds__(kThreads, 2) quantize_rowwise_stream_kernel(
 }
 
 // Row-wise quantize, any type / block / alignment: one warp per (row, block).
+// Row-wise quantize for rows that are not 16-byte aligned (row length not a multiple of 8, e.g. a 50257-wide vocabulary),
+// block <= 64.  A warp takes kRagGroup consecutive blocks of one row; lane l handles elements l and l + 32 of every block, so
+// all loads of the group (2-byte, coalesced) are in flight before the first absmax reduction, and the stores are runs of 32
+// consecutive bytes.  Same arithmetic as every other quantizer (BlockQ).
+constexpr int kRagGroup = 8;
+template <typename T>
+__global__ void __launch_bounds__(kThreads) quantize_rowwise_ragged_kernel(
+    const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ q, float* __restrict__ s, int64_t M, int64_t K, int B,
+    int64_t nb, int64_t groups_per_row) {
+    const int lane = threadIdx.x & 31;
+    const int64_t task = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+    if (task >= M * groups_per_row) return;
+    const int64_t row = task / groups_per_row, j0 = (task % groups_per_row) * kRagGroup;
+    const T* xr = x + row * ldx;
+    float v[kRagGroup][2];
+#pragma unroll
+    for (int b = 0; b < kRagGroup; ++b) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int64_t k = (j0 + b) * B + lane + 32 * e;
+            const bool valid = (j0 + b) < nb && lane + 32 * e < B && k < K;
+            v[b][e] = valid ? to_f32<T>(xr[k]) : 0.0f;
+        }
+    }
+#pragma unroll
+    for (int b = 0; b < kRagGroup; ++b) {
+        float amax = fmaxf(fabsf(v[b][0]), fabsf(v[b][1]));
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        const int64_t j = j0 + b;
+        if (j >= nb) continue;
+        BlockQ bq;
+        bq.set(amax, sizeof(T) == 2);
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int64_t k = j * B + lane + 32 * e;
+            if (lane + 32 * e < B && k < K) q[row * K + k] = (int8_t)(bq.q(v[b][e]) & 0xffu);
+        }
+        if (lane == 0) s[j * M + row] = amax;
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads) quantize_rowwise_generic_kernel(
     const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ q, float* __restrict__ s, int64_t M, int64_t K, int B,
@@ -389,6 +431,42 @@ __global__ void __launch_bounds__(kThreads) quantize_colwise_vec_kernel(
             for (int u = 0; u < 16; ++u)
                 if (rr + u < R) o[u] = (int8_t)((w[u / 4] >> (8 * (u % 4))) & 0xffu);
         }
+    }
+}
+
+// Column-wise quantize when rows of the input or of the output are not 16-byte aligned (e.g. 50257 columns).  A CTA takes
+// one block of B rows x kThreads columns: thread t reads its column down the block twice (absmax, then quantize; the
+// second pass hits L1/L2; consecutive threads read consecutive columns), parks the B bytes in shared memory, and the
+// warps then write each output row's B bytes as runs of 32 consecutive bytes.  (With one thread storing its column byte
+// by byte, every warp store touched 32 sectors.)  Dynamic shared memory: kThreads * (B + 4) bytes.
+template <typename T>
+__global__ void __launch_bounds__(kThreads) quantize_colwise_ragged_kernel(
+    const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ q, float* __restrict__ s, int64_t R, int64_t C, int B,
+    int64_t col_tiles) {
+    extern __shared__ unsigned char tile[];                 // [kThreads][B + 4]
+    const int pitch = B + 4;
+    const int64_t j = blockIdx.x / col_tiles, c0 = (blockIdx.x % col_tiles) * kThreads;
+    const int64_t lo = j * B;
+    const int rows = (int)((lo + B < R) ? B : R - lo);
+    const int64_t c = c0 + threadIdx.x;
+    if (c < C) {
+        const T* xc = x + lo * ldx + c;
+        float amax = 0.0f;
+        for (int r = 0; r < rows; ++r) amax = fmaxf(amax, fabsf(to_f32<T>(xc[(int64_t)r * ldx])));
+        BlockQ bq;
+        bq.set(amax, sizeof(T) == 2);
+        unsigned char* mine = tile + (size_t)threadIdx.x * pitch;
+        for (int r = 0; r < rows; ++r) mine[r] = (unsigned char)(bq.q(to_f32<T>(xc[(int64_t)r * ldx])) & 0xffu);
+        s[j * C + c] = amax;
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int t = warp; t < kThreads; t += kThreads / 32) {
+        const int64_t cc = c0 + t;
+        if (cc >= C) break;
+        int8_t* dst = q + cc * R + lo;
+        const unsigned char* src = tile + (size_t)t * pitch;
+        for (int r = lane; r < rows; r += 32) dst[r] = (int8_t)src[r];
     }
 }
 
@@ -551,6 +629,15 @@ int quantize_rowwise_t(const T* x, int64_t ldx, int8_t* q, float* s, int64_t M, 
         }
     }
 #undef BI8_QROW
+    if (block <= 64) {
+        const int64_t gpr = (nb + kRagGroup - 1) / kRagGroup;
+        const int64_t rgrid = (M * gpr + kThreads / 32 - 1) / (kThreads / 32);
+        if (rgrid < (1ll << 31)) {
+            quantize_rowwise_ragged_kernel<T><<<(unsigned)rgrid, kThreads, 0, st>>>(x, ldx, q, s, M, K, block, nb, gpr);
+            BI8_CUDA_TRY(cudaGetLastError());
+            return BI8_OK;
+        }
+    }
     const int64_t tasks = M * nb;
     const int64_t grid = (tasks + kThreads / 32 - 1) / (kThreads / 32);
     if (grid >= (1ll << 31)) return fail(BI8_ERR_SHAPE, "quantize_rowwise: %lld blocks exceed the grid limit", (long long)tasks);
@@ -586,6 +673,17 @@ int quantize_colwise_t(const T* x, int64_t ldx, int8_t* q, float* s, int64_t R, 
         }
     }
     const int64_t nb = (R + block - 1) / block;
+    if (block <= 256) {
+        const int64_t col_tiles = (C + kThreads - 1) / kThreads;
+        const size_t smem = (size_t)kThreads * (block + 4);
+        if (nb * col_tiles < (1ll << 31)) {
+            if (smem > 48 * 1024)
+                BI8_CUDA_TRY(cudaFuncSetAttribute(quantize_colwise_ragged_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            quantize_colwise_ragged_kernel<T><<<(unsigned)(nb * col_tiles), kThreads, smem, st>>>(x, ldx, q, s, R, C, block, col_tiles);
+            BI8_CUDA_TRY(cudaGetLastError());
+            return BI8_OK;
+        }
+    }
     const int64_t grid = (nb * C + kThreads - 1) / kThreads;
     if (grid >= (1ll << 31)) return fail(BI8_ERR_SHAPE, "quantize_colwise: grid too large");
     quantize_colwise_generic_kernel<T><<<(unsigned)grid, kThreads, 0, st>>>(x, ldx, q, s, R, C, block, nb);

@@ -69,7 +69,7 @@ def test_largest_config_shape_sampled():
 
 
 @pytest.mark.parametrize("block", [32, 64, 128, 256])
-@pytest.mark.parametrize("shape", [(1, 256), (33, 512), (40, 1040), (257, 72), (31, 1000), (5, 150), (64, 17)])
+@pytest.mark.parametrize("shape", [(1, 256), (33, 512), (40, 1040), (257, 72), (31, 1000), (5, 150), (64, 17), (40, 50257)])
 def test_ragged_shapes_and_blocks(shape, block):
     # K % 16 == 0: 32-byte lanes; K % 8 == 0: 16-byte lanes; otherwise the generic kernel; K tails in every case
     _check_quant(randn_bf16(shape, shape[0] * 131 + shape[1], outliers=0.01), block)
@@ -122,7 +122,7 @@ def test_row_strided_input():
 
 
 @pytest.mark.parametrize("block", [32, 64, 128, 256, 48])
-@pytest.mark.parametrize("shape", [(128, 128), (200, 136), (64, 1000), (1000, 64), (70, 33), (8192, 768)])
+@pytest.mark.parametrize("shape", [(128, 128), (200, 136), (64, 1000), (1000, 64), (70, 33), (8192, 768), (130, 50257), (50257, 40)])
 def test_colwise_equals_transpose_then_rowwise(shape, block):
     from triton_functions import quantize_block_colwise
     x = randn_bf16(shape, shape[0] + 7 * shape[1], outliers=0.01)

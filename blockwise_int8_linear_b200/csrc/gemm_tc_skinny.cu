@@ -737,7 +737,10 @@ int launch_gemm_skinny(const GemmArgs& g, cudaStream_t st) {
     p.early_weights = g.after_own_quantizer ? 1 : 0;
     const long long tiles = (g.N + kTileRows - 1) / kTileRows;
     p.total_stages = tiles * p.nks;
-    const int grid = (int)(p.total_stages < di.sms ? p.total_stages : di.sms);
+    int grid = (int)(p.total_stages < di.sms ? p.total_stages : di.sms);
+    // with at least three quarters as many tiles as SMs, one whole tile per CTA (no divided tile, no reduction kernel) is
+    // faster than an even split (measured: 112 tiles 14.8 against 15.7 us; 96 tiles and fewer lose)
+    if (tiles <= di.sms && tiles * 4 >= (long long)di.sms * 3) grid = (int)tiles;
     const bool fused = g.X != nullptr;
     int rc = BI8_ERR_SHAPE;
 #define BI8_SK(QB, BNS)                                                                                               \

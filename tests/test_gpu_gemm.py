@@ -278,7 +278,7 @@ SKINNY_SHAPES = [
     (1, 64, 4, 64), (1, 4096, 512, 64), (5, 1056, 76, 64), (8, 2048, 1000, 64), (9, 256, 260, 64), (16, 4096, 1024, 64),
     (3, 192, 36, 32), (8, 1056, 132, 32), (16, 2048, 256, 128), (7, 416, 52, 128), (2, 11008, 64, 64),
     (17, 512, 384, 64), (32, 4096, 640, 64), (25, 1056, 260, 32), (32, 2048, 128, 128), (8, 4096, 11008, 64),
-    (4, 128, 40000, 64), (12, 80, 24, 32),
+    (4, 128, 40000, 64), (12, 80, 24, 32), (8, 256, 14336, 64),      # the last: 112 tiles, one whole tile per CTA
     # 33..64 activation rows: promotion warps of 32 columns
     (33, 512, 384, 64), (64, 4096, 640, 64), (50, 1056, 260, 64), (64, 2048, 256, 128), (48, 4096, 1024, 64),
     (64, 1056, 132, 32), (41, 11008, 128, 64),

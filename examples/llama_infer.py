@@ -75,17 +75,24 @@ class Int8Linear(nn.Module):
         self.lin.prepare_for_eval()
         self.lin.weight.data = torch.empty(0, device=dev, dtype=torch.bfloat16)      # keep only the int8 copy resident
 
-    def forward(self, x):
+    def partial(self, x):
+        """This rank's contribution: the finished result for a column-parallel layer (or one rank), an fp32 partial sum for
+        a row-parallel one (to be summed over the group by the caller)."""
         if self.mode == "col" or self.world == 1:
             return self.lin.infer(x)
         prev = cfg.INPUT_OUTPUT_TORCH_TYPE
         cfg.INPUT_OUTPUT_TORCH_TYPE = torch.float32
         try:
-            part = self.lin.infer(x)
+            return self.lin.infer(x)
         finally:
             cfg.INPUT_OUTPUT_TORCH_TYPE = prev
+
+    def forward(self, x):
+        part = self.partial(x)
+        if self.mode == "col" or self.world == 1:
+            return part
         dist.all_reduce(part)
-        return part.to(prev)
+        return part.to(cfg.INPUT_OUTPUT_TORCH_TYPE)
 
 
 def rms_norm(x, eps=1e-5):
@@ -118,8 +125,9 @@ class Layer(nn.Module):
         self.head_dim = a.head_dim
         self.kcache = self.vcache = None
 
-    def forward(self, x, pos0, max_len, cis, mask=None, pos_dev=None):
-        """Prefill: pos0 is a Python int and the cache is sliced.  Decode (pos_dev given, T == 1): the position is a device
+    def attn_partial(self, x, pos0, max_len, cis, mask=None, pos_dev=None):
+        """Attention half of the layer up to the output projection, without the sum over ranks and the residual add.
+        Prefill: pos0 is a Python int and the cache is sliced.  Decode (pos_dev given, T == 1): the position is a device
         tensor, the cache is written with index_copy_ and attended in full under a mask, so that every shape is static and
         the step can be captured in a CUDA graph.  `cis` holds the rotary factors of this call's positions."""
         B, T, _ = x.shape
@@ -140,10 +148,23 @@ class Layer(nn.Module):
             self.vcache.index_copy_(2, pos_dev, v)
             att = F.scaled_dot_product_attention(q, self.kcache, self.vcache, attn_mask=mask)
         att = att.transpose(1, 2).reshape(B, T, hl * hd)
-        x = x + self.o(att)
+        return self.o.partial(att)
+
+    def mlp_partial(self, x):
         gate, up = self.gate_up(rms_norm(x)).split(self.gate_up.widths, dim=-1)
-        x = x + self.down(F.silu(gate) * up)
-        return x
+        return self.down.partial(F.silu(gate) * up)
+
+    def forward(self, x, pos0, max_len, cis, mask=None, pos_dev=None):
+        x = x + group_sum(self.attn_partial(x, pos0, max_len, cis, mask, pos_dev), x.dtype, self.o.world)
+        return x + group_sum(self.mlp_partial(x), x.dtype, self.down.world)
+
+
+def group_sum(part, dtype, world):
+    """Sum of the ranks' row-parallel partial results (fp32 over NCCL), cast to the activation type."""
+    if world == 1:
+        return part
+    dist.all_reduce(part)
+    return part.to(dtype)
 
 
 class Llama(nn.Module):
@@ -157,26 +178,86 @@ class Llama(nn.Module):
         self.cis = rope_table(a.prompt + a.decode, a.head_dim, dev)
         self.positions = torch.arange(a.prompt + a.decode, device=dev)
 
+    def positions_of(self, ids, pos0, max_len, pos_dev):
+        if pos_dev is None:
+            return self.cis[pos0:pos0 + ids.shape[1]], None
+        return self.cis.index_select(0, pos_dev), (self.positions[:max_len] <= pos_dev).view(1, 1, 1, max_len)
+
+    def local_logits(self, x):
+        """[B, 1, V_local] of this rank, padded with -inf to the widest shard (all_gather wants equal sizes)."""
+        logits = self.head(rms_norm(x[:, -1:]))
+        if self.world == 1:
+            return logits
+        sizes = [hi - lo for lo, hi in block_aligned_bounds(self.vocab, self.world, self.block)]
+        pad = torch.full((logits.shape[0], 1, max(sizes)), float("-inf"), device=logits.device, dtype=logits.dtype)
+        pad[..., : logits.shape[-1]] = logits
+        return pad
+
+    def join_logits(self, bufs):
+        sizes = [hi - lo for lo, hi in block_aligned_bounds(self.vocab, self.world, self.block)]
+        return torch.cat([b[..., :n] for b, n in zip(bufs, sizes)], dim=-1)
+
     @torch.no_grad()
     def forward(self, ids, pos0, max_len, pos_dev=None):
         x = self.emb[ids]
-        if pos_dev is None:
-            cis, mask = self.cis[pos0:pos0 + ids.shape[1]], None
-        else:
-            cis = self.cis.index_select(0, pos_dev)
-            mask = (self.positions[:max_len] <= pos_dev).view(1, 1, 1, max_len)
+        cis, mask = self.positions_of(ids, pos0, max_len, pos_dev)
         for layer in self.layers:
             x = layer(x, pos0, max_len, cis, mask, pos_dev)
-        logits = self.head(rms_norm(x[:, -1:]))                    # [B, 1, V_local]
+        logits = self.local_logits(x)                              # [B, 1, V_local]
         if self.world > 1:
-            sizes = [hi - lo for lo, hi in block_aligned_bounds(self.vocab, self.world, self.block)]
-            width = max(sizes)
-            pad = torch.full((logits.shape[0], 1, width), float("-inf"), device=logits.device, dtype=logits.dtype)
-            pad[..., : logits.shape[-1]] = logits
-            bufs = [torch.empty_like(pad) for _ in range(self.world)]
-            dist.all_gather(bufs, pad)
-            logits = torch.cat([b[..., :n] for b, n in zip(bufs, sizes)], dim=-1)
+            bufs = [torch.empty_like(logits) for _ in range(self.world)]
+            dist.all_gather(bufs, logits)
+            logits = self.join_logits(bufs)
         return logits
+
+    @torch.no_grad()
+    def decode_pieces(self, tok, pos_dev, max_len):
+        """The decode step of a tensor-parallel group as a list of (compute, bind) pairs: every compute piece is free of
+        communication and can be captured in a CUDA graph of its own, the NCCL calls run between the replays.  The
+        pieces hand their tensors to each other through `st`; `bind()`, called right after its piece has been captured,
+        returns the collective on exactly the tensors that piece produced (later pieces put new tensors under the same
+        keys)."""
+        st = {}
+        dtype = self.emb.dtype
+
+        def reduce_part():
+            part = st["part"]
+            return lambda: dist.all_reduce(part)
+
+        def first():
+            st["cis"], st["mask"] = self.positions_of(tok, 0, max_len, pos_dev)
+            st["x"] = self.emb[tok]
+            st["part"] = self.layers[0].attn_partial(st["x"], 0, max_len, st["cis"], st["mask"], pos_dev)
+
+        pieces = [(first, reduce_part)]
+        for i, layer in enumerate(self.layers):
+            def mlp(layer=layer):
+                st["x"] = st["x"] + st["part"].to(dtype)
+                st["part"] = layer.mlp_partial(st["x"])
+
+            pieces.append((mlp, reduce_part))
+            if i + 1 < len(self.layers):
+                def attn(nxt=self.layers[i + 1]):
+                    st["x"] = st["x"] + st["part"].to(dtype)
+                    st["part"] = nxt.attn_partial(st["x"], 0, max_len, st["cis"], st["mask"], pos_dev)
+
+                pieces.append((attn, reduce_part))
+
+        def head():
+            st["logits"] = self.local_logits(st["x"] + st["part"].to(dtype))
+            st["bufs"] = [torch.empty_like(st["logits"]) for _ in range(self.world)]
+
+        def last():
+            tok.copy_(self.join_logits(st["bufs"]).argmax(-1))
+            pos_dev.add_(1)
+
+        def gather_logits():
+            bufs, logits = st["bufs"], st["logits"]
+            return lambda: dist.all_gather(bufs, logits)
+
+        pieces.append((head, gather_logits))
+        pieces.append((last, None))
+        return pieces
 
 
 def main():
@@ -192,10 +273,6 @@ def main():
     ap.add_argument("--block", type=int, default=64)
     ap.add_argument("--eager", action="store_true", help="do not capture the decode step in a CUDA graph")
     a = ap.parse_args()
-    if int(os.environ.get("WORLD_SIZE", 1)) > 1:
-        # the captured decode step has only been validated on one GPU; with tensor parallelism (NCCL collectives inside the
-        # step) the driver decodes eagerly
-        a.eager = True
     a.head_dim = a.hidden // a.heads
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -229,7 +306,7 @@ def main():
         tok.copy_(lg.argmax(-1))
         pos_dev.add_(1)
 
-    graph = None
+    graph, pieces = None, None
     if not a.eager:
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -239,9 +316,22 @@ def main():
         torch.cuda.current_stream().wait_stream(side)
         tok.copy_(nxt)
         pos_dev.fill_(a.prompt)
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            decode_step()
+        if world == 1:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                decode_step()
+        else:
+            # Tensor parallel: NCCL stays outside the graphs.  The step is cut at its collectives (two sums per layer, one
+            # gather of the logits); every communication-free piece is captured in a graph of its own (one shared memory
+            # pool, so a piece reads the tensors the piece before it wrote) and the collectives are issued between the
+            # replays.  (Capturing the whole step with the collectives inside did not complete on this system.)
+            pieces, pool = [], None
+            for compute, bind in model.decode_pieces(tok, pos_dev, max_len):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, pool=pool):
+                    compute()
+                pool = g.pool()
+                pieces.append((g, bind() if bind is not None else None))
         tok.copy_(nxt)                                            # the capture itself does not execute the step
         pos_dev.fill_(a.prompt)
     else:
@@ -253,6 +343,11 @@ def main():
     for step in range(a.decode - 1):
         if graph is not None:
             graph.replay()
+        elif pieces is not None:
+            for g, collective in pieces:
+                g.replay()
+                if collective is not None:
+                    collective()
         else:
             decode_step()
         out.append(tok.clone())
@@ -264,7 +359,7 @@ def main():
             "model": f"llama-arch {a.layers}x{a.hidden} ffn {a.ffn} vocab {a.vocab}, random init N(0,0.02), BlockInt8Linear block {a.block}",
             "n_gpus": world, "batch": a.batch, "prompt": a.prompt, "decode": a.decode,
             "prefill_tokens_per_s": a.batch * a.prompt / t_prefill, "prefill_s": t_prefill, "first_prefill_s": t_first,
-            "decode_tokens_per_s": a.batch * (a.decode - 1) / t_decode, "decode_ms_per_step": 1e3 * t_decode / (a.decode - 1), "decode_mode": "eager" if a.eager else "cuda graph",
+            "decode_tokens_per_s": a.batch * (a.decode - 1) / t_decode, "decode_ms_per_step": 1e3 * t_decode / (a.decode - 1), "decode_mode": "eager" if a.eager else ("cuda graph" if world == 1 else "cuda graphs between the collectives"),
             "first_tokens": toks[0, :8].tolist(),
         }))
     if world > 1:

@@ -87,6 +87,7 @@ def stream_ptr() -> ctypes.c_void_p:
 
 
 _workspaces: dict = {}
+_captured: list = []        # buffers whose addresses live in captured CUDA graphs: never released
 
 
 def workspace(device: torch.device, nbytes: int):
@@ -94,14 +95,20 @@ def workspace(device: torch.device, nbytes: int):
 
     The workspace is scratch for split-K partial results; one buffer per stream is reused by all GEMMs queued on that
     stream (they run one after the other), which saves an allocator round trip per call.  A larger request replaces
-    the buffer."""
+    the buffer.  A buffer handed out while the stream is being captured ends up as an address inside a CUDA graph: such
+    buffers are kept apart from the ones used eagerly and are never released, so a replay cannot find its scratch reused
+    by somebody else."""
     if nbytes <= 0:
         return None
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    stream = torch.cuda.current_stream(device)
+    capturing = torch.cuda.is_current_stream_capturing()
+    key = (device.index, stream.cuda_stream, capturing)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
         ws = torch.empty(max(nbytes, 2 * ws.numel() if ws is not None else 0), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
+        if capturing:
+            _captured.append(ws)
     return ws
 
 

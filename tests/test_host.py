@@ -55,6 +55,24 @@ def test_argument_validation_happens_before_cuda(L):
     assert L.bi8_gemm_workspace_bytes(128, 128, 128, 64) == 0
 
 
+def test_fused_entry_point_validates_and_flags_match_the_header(L):
+    from blockwise_int8_linear_b200 import _lib
+    header = open(os.path.join(ROOT, "include", "bi8.h")).read()
+    flags = {name: int(value) for name, value in re.findall(r"#define BI8_GEMM_(\w+)\s+(\d+)", header)}
+    assert flags == {"DEFAULT": 0, "FORCE_GENERIC": 1, "FORCE_TC": 2, "NO_SEED": 4, "FORCE_SMALLM": 8, "FORCE_SKINNY": 16,
+                     "QUANT_IN_KERNEL": 32}
+    assert (_lib.GEMM_FORCE_GENERIC, _lib.GEMM_FORCE_TC, _lib.GEMM_NO_SEED, _lib.GEMM_FORCE_SMALLM, _lib.GEMM_FORCE_SKINNY,
+            _lib.GEMM_QUANT_IN_KERNEL) == (1, 2, 4, 8, 16, 32)
+    vp = ctypes.c_void_p
+    one = vp(256)
+    f = lambda **kw: L.bi8_gemm_dequant_fused_quant(one, kw.get("xdt", 0), 64, kw.get("xq", one), kw.get("sx", one), one, 64, one,
+                                                    None, 0, one, 64, 0, kw.get("M", 8), 64, 64, 64, None, 0, 0, None)
+    assert f(xdt=9) == -1
+    # without a GPU (or a workspace) the one-kernel form does not apply, so the scratch is required
+    assert f(xq=None) == -7 and "scratch" in L.bi8_last_error_string().decode()
+    assert f(M=0) == 0
+
+
 def test_python_surface_mirrors_reference_names():
     import block_linear
     import block_linear_config

@@ -11,12 +11,18 @@ reference's own (``triton_functions.py:565``): 2*M*N*K / time, in tera-ops per s
 With N > 1 (launched by torchrun, one rank per GPU) every rank runs the same step on its own
 batch of tokens: the layer is data-parallel in the token dimension, there is no collective on the
 path, so scaling is weak and ``value`` is the sum over ranks divided by the slowest rank's time.
+The partitionings that do communicate are measured beside it at the same N (``roofline.tp``,
+``roofline.models``): the Llama MLP pair sharded column-/row-parallel with its NCCL all-reduce, the
+Llama-architecture inference driver (tensor parallel) and the GPT-2 training driver (data parallel).
 
 Prints ONE JSON line.  Besides the headline it carries
-  roofline      the GEMM kernel alone (CUDA events around its launches inside the timed region)
+  roofline      the GEMM kernel alone (CUDA events around its launches inside the timed region), and inside it
+                kernels (memory-bound kernels and the small-M GEMM rows against the HBM roof), sustained (the GEMM
+                back to back for two seconds), cublas_bf16_ms (torch.matmul on the same shape, comparator only),
+                tp and models (see above)
   e2e           the same step through the public Python API with host buffers (pinned H2D of x, D2H of y)
   cpu_baseline  the CPU restatement of the reference timed on this host on a bounded sample (rank 0, N = 1)
-  extra         the memory-bound kernels (quantize / dequantize sweep) and the other GEMM shapes
+  extra         the full sweep tables the rows in roofline.kernels are taken from
 ``--impl reference`` times the CPU restatement only (the reference has no CPU path of its own and
 cannot be imported without a GPU and Triton 2.3; the restatement is pinned to its kernels by golden vectors).
 """
@@ -45,6 +51,7 @@ WORKLOADS = {
 }
 DEFAULT_WORKLOAD = "llama7b_up_proj_m8192"
 INT8_NOMINAL_TOPS = 4500.0
+NSETS = 3            # rotating input/output sets of the timed step
 HBM_FALLBACK, BF16_FALLBACK = 6650.0, 1590.0
 
 
@@ -111,6 +118,15 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def bench_config(workload: str, world: int):
+    """The `config` object of the JSON line; both arms print the same one."""
+    M, K, N = WORKLOADS[workload]
+    return {"workload": workload, "M_per_gpu": M, "K": K, "N": N, "block": BLOCK, "in": "bf16", "out": "bf16",
+            "step": "block-quantize x + int8 block GEMM with fused dequantize (weights pre-quantized)",
+            "l2": f"{NSETS} rotating input/output sets of {(M * K * 2 + M * N * 2) >> 20} MiB each (larger than L2)",
+            "parallelism": f"dp{world} over tokens, no collective"}
+
+
 def dist_env():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -160,13 +176,13 @@ def run_reference(args):
     torch.set_num_threads(os.cpu_count() or 1)
     w = O.synthetic((N, K), 3100, std=0.02, outlier_frac=0.0)
     wq, ws = O.quantize(w, BLOCK)
-    # size one step so that warmup + steps stay within a couple of minutes
+    # one step is the whole batch when warmup + steps of it fit in about 200 s, else a bounded row sample
     x = O.synthetic((256, K), 3000, outlier_frac=0.0)
     cpu_step(O, x[:64], wq, ws)                  # warm the thread pool
     t0 = time.perf_counter()
     cpu_step(O, x, wq, ws)
     t256 = time.perf_counter() - t0
-    budget = 100.0 / max(1, args.steps + args.warmup)
+    budget = 200.0 / max(1, args.steps + args.warmup)
     rows = int(max(64, min(M, 256 * budget / max(t256, 1e-3))))
     rows -= rows % 64
     x = O.synthetic((rows, K), 3001, outlier_frac=0.0)
@@ -177,14 +193,16 @@ def run_reference(args):
         cpu_step(O, x, wq, ws)
     dt = (time.perf_counter() - t0) / args.steps
     tops = 2.0 * rows * N * K / dt / 1e12
-    sample = f"{rows} of {M} rows per step of {args.workload}; torch CPU fp32 restatement of the reference kernels"
+    sample = (f"{rows} of {M} rows per step of {args.workload} (throughput does not depend on the row count); torch CPU fp32 "
+              f"restatement of the reference kernels")
     line = {
         "impl": "reference", "metric": "int8_block_gemm_tops", "value": tops, "unit": "TOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {"workload": args.workload, "M": M, "K": K, "N": N, "block": BLOCK, "rows_per_step": rows},
+        "config": bench_config(args.workload, args.gpus),
         "cpu_baseline": {"value": tops, "unit": "TOP/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": tops, "unit": "TOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "rows_per_step": rows,
         "note": "the reference has no CPU implementation (its wrappers assert CUDA tensors); this arm times the CPU "
                 "restatement that the golden vectors pin to the reference's kernels",
     }
@@ -310,6 +328,176 @@ def extras(dev, hbm_gbs, flush):
     return out
 
 
+def kernel_rows(extra, hbm_gbs):
+    """The rows of the sweep that stand against the HBM roof (quantizers, dequantizer, GEMM with M <= 128) and the
+    tensor-bound GEMM rows, in the compact form kept under roofline.kernels."""
+    rows = []
+    for key, name in (("quantize", "quantize_rowwise"), ("quantize_colwise", "quantize_colwise"), ("dequantize", "dequantize_rowwise")):
+        for r in extra.get(key, []):
+            rows.append({"name": name, "shape": r["shape"], "us": round(r["us"], 2), "bound": "hbm", "frac": round(r["frac_hbm"], 3)})
+    for r in extra.get("quantize_dual", []):
+        rows.append({"name": "quantize_dual", "shape": r["shape"], "us": round(r["us"], 2), "bound": "hbm", "frac": round(r["frac_hbm"], 3)})
+    for r in extra.get("gemm", []):
+        hbm_bound = r["M"] <= 128
+        rows.append({"name": "gemm", "shape": [r["M"], r["K"], r["N"]], "us": round(r["us"], 2), "bound": "hbm" if hbm_bound else "tensor",
+                     "frac": round(r["frac_hbm"] if hbm_bound else r["frac_int8_nominal"], 3)})
+    return rows
+
+
+def sustained_gemm(step_gemm, ops, local, seconds=2.0):
+    """The GEMM back to back for `seconds` with the SM clock sampled: the number a long training or prefill run sees."""
+    sampler = ClockSampler(local)
+    for _ in range(3):
+        step_gemm(0)
+    torch.cuda.synchronize()
+    sampler.start()
+    t0 = time.perf_counter()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    n = 0
+    while True:
+        for i in range(50):
+            step_gemm(n + i)
+        n += 50
+        torch.cuda.synchronize()
+        if time.perf_counter() - t0 >= seconds:
+            break
+    e1.record()
+    e1.synchronize()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / n
+    return {"seconds": round(time.perf_counter() - t0, 2), "launches": n, "gemm_ms": ms, "tops": ops / ms / 1e9,
+            "frac_of_nominal_int8_4500": ops / ms / 1e9 / INT8_NOMINAL_TOPS, "sm_mhz_median": clocks.get("sm_mhz"),
+            "reasons": clocks.get("reasons")}
+
+
+def tp_bench(dev, rank, world, hbm_gbs):
+    """The Llama-2-7B MLP pair sharded as blockwise_int8_linear_b200.parallel shards it: column-parallel gate_up
+    (2 x 11008 / p output features per rank) -> SiLU * mul -> row-parallel down (block-aligned 11008 / p input features,
+    fp32 partial result) -> NCCL all-reduce of [M, 4096] -> cast.  M = 4096 (prefill) and M = 8 (decode)."""
+    import torch.distributed as dist
+    import torch.nn.functional as F
+    import block_linear_config as cfg
+    from blockwise_int8_linear_b200.parallel import block_aligned_bounds
+    from triton_functions import (int8_matmul_block64_rowwise_dequantize as mm, quantize_block_rowwise,
+                                  quantize_matmul_block_rowwise_dequantize as qmm)
+    d, f = 4096, 11008
+    lo, hi = block_aligned_bounds(f, world, BLOCK)[rank]
+    fr = hi - lo
+    out = {"layer_pair": "gate_up [2*11008/p, 4096] column-parallel + down [4096, 11008/p] row-parallel, block 64",
+           "ffn_columns_of_rank0": fr, "collective": "none" if world == 1 else "ncclAllReduce fp32 [M, 4096]"}
+    for tag, M in (("prefill", 4096), ("decode", 8)):
+        shard_bytes = 3 * fr * d
+        copies = max(2, -(-(300 << 20) // shard_bytes)) if M <= 64 else 2
+        gus, dns = [], []
+        for c in range(copies):
+            g = torch.Generator(device=dev).manual_seed(7100 + c)
+            wgu = (torch.randn((2 * fr, d), device=dev, generator=g) * 0.02).to(torch.bfloat16)
+            wdn = (torch.randn((d, fr), device=dev, generator=g) * 0.02).to(torch.bfloat16)
+            gus.append(quantize_block_rowwise(wgu))
+            dns.append(quantize_block_rowwise(wdn))
+            del wgu, wdn
+        x = torch.randn((M, d), device=dev, generator=torch.Generator(device=dev).manual_seed(7000)).to(torch.bfloat16)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+
+        def pair(i, timed=False):
+            wq_gu, s_gu = gus[i % copies]
+            wq_dn, s_dn = dns[i % copies]
+            if timed:
+                ev[0].record()
+            cfg.INPUT_OUTPUT_TORCH_TYPE = torch.bfloat16
+            if M <= 64:
+                h = qmm(x, wq_gu.t(), s_gu)
+            else:
+                xq, sx = quantize_block_rowwise(x)
+                h = mm(xq, wq_gu.t(), sx, s_gu)
+            a = F.silu(h[:, :fr]) * h[:, fr:]
+            cfg.INPUT_OUTPUT_TORCH_TYPE = torch.float32 if world > 1 else torch.bfloat16
+            try:
+                if M <= 64:
+                    part = qmm(a, wq_dn.t(), s_dn)
+                else:
+                    aq, sa = quantize_block_rowwise(a)
+                    part = mm(aq, wq_dn.t(), sa, s_dn)
+            finally:
+                cfg.INPUT_OUTPUT_TORCH_TYPE = torch.bfloat16
+            if timed:
+                ev[1].record()
+            if world > 1:
+                dist.all_reduce(part)
+                y = part.to(torch.bfloat16)
+            else:
+                y = part
+            if timed:
+                ev[2].record()
+            return y
+
+        for i in range(5):
+            pair(i)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        tot, comp = [], []
+        for i in range(15):
+            if world > 1:
+                dist.barrier()
+            pair(i, timed=True)
+            ev[2].synchronize()
+            comp.append(ev[0].elapsed_time(ev[1]))
+            tot.append(ev[0].elapsed_time(ev[2]))
+        tot.sort()
+        comp.sort()
+        t = torch.tensor([tot[len(tot) // 2], comp[len(comp) // 2]], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_pair, ms_compute = t.tolist()
+        ops = 2.0 * M * d * (2 * fr) + 2.0 * M * fr * d
+        nbytes = 3 * fr * d + M * d * 2 + 2 * M * fr * 2 * 2 + M * d * 4
+        roof_ms = max(ops / (INT8_NOMINAL_TOPS * 1e9), nbytes / (hbm_gbs * 1e6))
+        out[tag] = {"M": M, "ms_per_pair": ms_pair, "ms_compute": ms_compute, "ms_allreduce": ms_pair - ms_compute,
+                    "allreduce_share": (ms_pair - ms_compute) / ms_pair if ms_pair > 0 else None,
+                    "tokens_per_s": M / (ms_pair * 1e-3), "rank_roofline_ms": roof_ms, "frac_of_rank_roofline": roof_ms / ms_pair,
+                    "timing": "CUDA events, median of 15 eager steps, max over ranks; " +
+                              ("weights rotate over copies larger than L2" if M <= 64 else "operands larger than L2")}
+        del gus, dns
+    return out
+
+
+def _load_example(name):
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(name, os.path.join(ROOT, "examples", name + ".py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def models_bench(dev, rank, world, local):
+    """The two model drivers of examples/ at this GPU count, bounded to a couple of minutes: Llama-2-7B architecture
+    (tensor parallel over the ranks; full depth, 512-token prompt, 32 greedy steps) and GPT-2 small training (data parallel,
+    6 timed steps), int8 layers and the same model with bf16 nn.Linear."""
+    import gc
+    out = {}
+    L = _load_example("llama_infer")
+    a = argparse.Namespace(layers=32, hidden=4096, heads=32, head_dim=128, ffn=11008, vocab=32000, batch=8, prompt=512,
+                           decode=33, block=BLOCK)
+    r = L.run(a, rank, world, dev)
+    out["llama7b_infer"] = {k: r[k] for k in ("n_gpus", "batch", "prompt", "decode", "prefill_tokens_per_s", "decode_tokens_per_s",
+                                              "decode_ms_per_step", "decode_mode", "first_tokens")}
+    out["llama7b_infer"]["parallelism"] = f"tp{world}"
+    del r
+    gc.collect()
+    torch.cuda.empty_cache()
+    G = _load_example("gpt2_train")
+    for tag, dense in (("gpt2_small_train_int8", False), ("gpt2_small_train_bf16_dense", True)):
+        ga = argparse.Namespace(steps=6, warmup=2, batch=8, seq=1024, layers=12, block=BLOCK, dense=dense)
+        r = G.run(ga, rank, world, local, dev)
+        out[tag] = {k: r[k] for k in ("n_gpus", "batch_per_gpu", "steps", "tokens_per_s", "ms_per_step", "loss_first", "loss_last")}
+        out[tag]["parallelism"] = f"dp{world} (DistributedDataParallel, NCCL gradient all-reduce)"
+        gc.collect()
+        torch.cuda.empty_cache()
+    return out
+
+
 def run_ours(args):
     rank, world, local = dist_env()
     if not torch.cuda.is_available():
@@ -330,7 +518,6 @@ def run_ours(args):
 
     # Synthetic data of the benchmark configuration: activations N(0,1), weights N(0, 0.02), both bf16.
     # Three rotating buffer sets (x, y) so that consecutive steps do not find their inputs in the 126 MB L2.
-    NSETS = 3
     gen = torch.Generator(device=dev).manual_seed(3000 + rank)
     xs_dev = [torch.randn((M, K), device=dev, generator=gen).to(torch.bfloat16) for _ in range(NSETS)]
     w = (torch.randn((N, K), device=dev, generator=torch.Generator(device=dev).manual_seed(3100)) * 0.02).to(torch.bfloat16)

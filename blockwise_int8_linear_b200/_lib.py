@@ -23,7 +23,8 @@ _DTYPE_CODE = {torch.bfloat16: BI8_BF16, torch.float32: BI8_F32, torch.float16: 
 EXPORTS = [
     "bi8_version", "bi8_last_error_string", "bi8_device_status", "bi8_quantize_rowwise", "bi8_quantize_colwise",
     "bi8_dequantize_rowwise", "bi8_gemm_dequant", "bi8_gemm_workspace_bytes", "bi8_gemm_block_partials",
-    "bi8_linear_forward", "bi8_gemm_dequant_fused_quant", "bi8_mma_peak_probe", "bi8_gemm_dequant_static", "bi8_gemm_static_scratch_bytes",
+    "bi8_gemm_dequant_fused_quant", "bi8_mma_peak_probe", "bi8_gemm_dequant_static", "bi8_gemm_static_scratch_bytes",
+    "bi8_gemm_wait_selftest", "bi8_stream_capture_id",
 ]
 
 _lib = None
@@ -53,9 +54,10 @@ def lib() -> ctypes.CDLL:
         L.bi8_gemm_workspace_bytes.argtypes = [i64, i64, i64, i32]
         L.bi8_gemm_workspace_bytes.restype = sz
         L.bi8_gemm_block_partials.argtypes = [vp, i64, vp, i64, vp, i64, i64, i64, i32, i32, vp]
-        L.bi8_linear_forward.argtypes = [vp, i32, i64, vp, vp, vp, i64, vp, vp, i32, vp, i64, i32, i64, i64, i64, i32, vp, sz,
-                                         i32, vp]
-        L.bi8_gemm_dequant_fused_quant.argtypes = L.bi8_linear_forward.argtypes
+        L.bi8_gemm_dequant_fused_quant.argtypes = [vp, i32, i64, vp, vp, vp, i64, vp, vp, i32, vp, i64, i32, i64, i64, i64, i32, vp,
+                                                   sz, i32, vp]
+        L.bi8_gemm_wait_selftest.argtypes = [vp, i64, vp, i64, vp, vp, vp, i64, i32, i64, i64, i64, i32, c.c_uint, i32, vp]
+        L.bi8_stream_capture_id.argtypes = [vp, c.POINTER(c.c_ulonglong)]
         L.bi8_mma_peak_probe.argtypes = [i32, c.POINTER(c.c_float), c.POINTER(i32)]
         for name in EXPORTS:
             fn = getattr(L, name)
@@ -86,29 +88,37 @@ def stream_ptr() -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-_workspaces: dict = {}
-_captured: list = []        # buffers whose addresses live in captured CUDA graphs: never released
+_workspaces: dict = {}       # (device, stream handle) -> buffer, eager launches
+_capture_ws: dict = {}       # (device, capture id) -> buffer, launches recorded into the CUDA graph being captured
+
+
+def _capture_id(stream) -> int:
+    cid = ctypes.c_ulonglong(0)
+    check(lib().bi8_stream_capture_id(ctypes.c_void_p(stream.cuda_stream), ctypes.byref(cid)), "bi8_stream_capture_id")
+    return int(cid.value)
 
 
 def workspace(device: torch.device, nbytes: int):
     """GEMM workspace of at least ``nbytes`` for (device, current stream), or None for 0 bytes.
 
-    The workspace is scratch for split-K partial results; one buffer per stream is reused by all GEMMs queued on that
-    stream (they run one after the other), which saves an allocator round trip per call.  A larger request replaces
-    the buffer.  A buffer handed out while the stream is being captured ends up as an address inside a CUDA graph: such
-    buffers are kept apart from the ones used eagerly and are never released, so a replay cannot find its scratch reused
-    by somebody else."""
+    The workspace is scratch for split-K partial results.  Eager launches: one buffer per stream is reused by all GEMMs
+    queued on that stream (they run one after the other), which saves an allocator round trip per call; a larger request
+    replaces the buffer.  While the stream is being captured, the buffer's address is baked into the CUDA graph, so every
+    capture gets a buffer of its own (keyed by the capture's sequence number): two graphs never share scratch and may be
+    replayed on different streams.  All GEMMs of one graph share its buffer, which is correct because a graph's kernels
+    run in capture order.  The buffer is allocated from the capture's memory pool, which keeps it reserved for the graph's
+    lifetime; this module drops its own reference when it sees the next capture (or an eager call)."""
     if nbytes <= 0:
         return None
     stream = torch.cuda.current_stream(device)
-    capturing = torch.cuda.is_current_stream_capturing()
-    key = (device.index, stream.cuda_stream, capturing)
-    ws = _workspaces.get(key)
+    cid = _capture_id(stream) if torch.cuda.is_current_stream_capturing() else 0
+    for k in [k for k in _capture_ws if k != (device.index, cid)]:
+        del _capture_ws[k]
+    table, key = (_capture_ws, (device.index, cid)) if cid else (_workspaces, (device.index, stream.cuda_stream))
+    ws = table.get(key)
     if ws is None or ws.numel() < nbytes:
         ws = torch.empty(max(nbytes, 2 * ws.numel() if ws is not None else 0), dtype=torch.uint8, device=device)
-        _workspaces[key] = ws
-        if capturing:
-            _captured.append(ws)
+        table[key] = ws
     return ws
 
 

@@ -50,19 +50,47 @@ def fast_matmul(a, b):
     return int8_matmul_block64_rowwise_dequantize(a_int8, b_int8.t(), a_state, b_state)
 
 
+def _weight_cache(W):
+    """The int8 copies of a weight that are still valid, or None when caching is off.
+
+    With ``block_linear_config.CACHE_QUANTIZED_WEIGHTS`` the K-blocked copy (forward) and the N-blocked copy (dX) of a
+    weight are kept on the tensor object until the weight changes: the key holds the tensor's version counter, which
+    every in-place update (an optimizer step) advances, its storage address, shape, dtype and the block size.  Several
+    micro-steps between optimizer steps, or evaluation passes in train mode, then quantize the weight once instead of
+    twice per call (the reference re-quantizes in every call, ``block_linear.py:79,93-94``)."""
+    if not getattr(block_linear_config, "CACHE_QUANTIZED_WEIGHTS", False):
+        return None
+    key = (W._version, W.data_ptr(), tuple(W.shape), W.dtype, block_linear_config.GROUP_SIZE)
+    cache = getattr(W, "_bi8_quantized", None)
+    if cache is None or cache.get("key") != key:
+        cache = {"key": key}
+        try:
+            W._bi8_quantized = cache
+        except AttributeError:
+            return None
+    return cache
+
+
 class blockwise_int8_linear(torch.autograd.Function):
     """``y = x @ W^T + bias`` with every GEMM (forward, dX, dW) done in blockwise int8
-    (``block_linear.py:69-112``).  X and W are re-quantized on every call, as in the reference; the
-    transposed operands of the backward GEMMs are quantized straight from the row-major tensors by the
-    fused column-wise quantizer, which is bit-identical to ``t().contiguous()`` + row-wise quantize."""
+    (``block_linear.py:69-112``).  X and W are re-quantized on every call, as in the reference (unless
+    ``CACHE_QUANTIZED_WEIGHTS`` is set); the transposed operands of the backward GEMMs are quantized straight from
+    the row-major tensors by the fused column-wise quantizer, which is bit-identical to ``t().contiguous()`` +
+    row-wise quantize."""
 
     @staticmethod
     def forward(ctx, X_3D, W, bias):
         X = X_3D.reshape(-1, X_3D.size(-1))
         ctx.save_for_backward(X, W)
         ctx.has_bias = bias is not None
+        ctx.wcache = cache = _weight_cache(W)
         X_int8, state_X = quantize_block_rowwise(X)
-        W_int8, state_W = quantize_block_rowwise(W)
+        if cache is not None and "row" in cache:
+            W_int8, state_W = cache["row"]
+        else:
+            W_int8, state_W = quantize_block_rowwise(W)
+            if cache is not None:
+                cache["row"] = (W_int8, state_W)
         out = int8_matmul_block64_rowwise_dequantize(X_int8, W_int8.t(), state_X, state_W, bias)
         return out.view(*X_3D.size()[:-1], -1)
 
@@ -74,7 +102,13 @@ class blockwise_int8_linear(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             # contraction over N: both operands blocked along N (block_linear.py:92-95)
             g_int8, g_state = quantize_block_rowwise(G)
-            Wt_int8, w_state = quantize_block_colwise(W)                     # [K, N], state [N/B, K]
+            cache = ctx.wcache         # still valid: autograd refuses to run backward on a weight modified since forward
+            if cache is not None and "col" in cache:
+                Wt_int8, w_state = cache["col"]
+            else:
+                Wt_int8, w_state = quantize_block_colwise(W)                 # [K, N], state [N/B, K]
+                if cache is not None:
+                    cache["col"] = (Wt_int8, w_state)
             grad_X = int8_matmul_block64_rowwise_dequantize(g_int8, Wt_int8.t(), g_state, w_state)
             grad_X = grad_X.view(*G_3D.size()[:-1], -1)
         if ctx.needs_input_grad[1]:
@@ -109,10 +143,23 @@ class BlockInt8Linear(nn.Linear):
         else:
             super().__init__(in_features, out_features, bias, device, dtype)
 
-    def prepare_for_eval(self):
+    def prepare_for_eval(self, drop_weight: bool = None):
+        """Quantizes the weight into the buffers ``W_int8`` / ``state_W`` (``block_linear.py:125-128``).  With
+        ``drop_weight`` (default: ``block_linear_config.DROP_WEIGHT_IN_EVAL``, off like the reference) the floating-point
+        weight is released afterwards: the parameter stays in place with zero elements, so ``state_dict()`` keeps its
+        key, and inference runs from the int8 copy alone (a 7B model then holds 6.7 GB instead of 20 GB).  Training, or
+        changing ``GROUP_SIZE``, needs the weight back: load a state dict that carries it."""
+        if self.weight.numel() == 0:
+            if not hasattr(self, "W_int8"):
+                raise RuntimeError("BlockInt8Linear has neither a floating-point weight nor int8 buffers")
+            return
         W_int8, state_W = quantize_block_rowwise(self.weight.detach())
         self.register_buffer("W_int8", W_int8)
         self.register_buffer("state_W", state_W)
+        if drop_weight is None:
+            drop_weight = getattr(block_linear_config, "DROP_WEIGHT_IN_EVAL", False)
+        if drop_weight:
+            self.weight.data = torch.empty(0, device=self.weight.device, dtype=self.weight.dtype)
 
     def dequantized_weight(self):
         """The weight after a quantize/dequantize round trip, in ``INPUT_OUTPUT_TORCH_TYPE`` (the working part of
@@ -135,6 +182,8 @@ class BlockInt8Linear(nn.Linear):
     def forward(self, x):
         if not self.training:
             return self.infer(x)
+        if self.weight.numel() == 0:
+            raise RuntimeError("this BlockInt8Linear dropped its floating-point weight for inference; training needs it")
         return blockwise_int8_linear.apply(x, self.weight, self.bias)
 
     def _load_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs):
@@ -143,6 +192,11 @@ class BlockInt8Linear(nn.Linear):
             key = prefix + name
             if key in state_dict and not hasattr(self, name):
                 self.register_buffer(name, torch.empty_like(state_dict[key], device=self.weight.device))
+        # a checkpoint saved after the floating-point weight was dropped carries an empty `weight` (and the other way
+        # round): take the shape the checkpoint has
+        key = prefix + "weight"
+        if key in state_dict and state_dict[key].shape != self.weight.shape:
+            self.weight.data = torch.empty_like(state_dict[key], device=self.weight.device, dtype=self.weight.dtype)
         super()._load_from_state_dict(state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs)
 
 

@@ -5,9 +5,15 @@ callers change by assignment (``block_linear_config.GROUP_SIZE = 64``).  All thr
 at call time by every operation of this package, so one assignment takes effect everywhere
 (the reference froze the GEMM's block size at import, ``triton_functions.py:30,43-56``, which
 let the quantizer and the GEMM disagree after a later assignment).
+
+Two more knobs belong to this package alone (the reference keeps the floating-point weight in eval mode and
+re-quantizes the weight in every training call, ``block_linear.py:78-79,93-94,125-128``); both default to the
+reference's behaviour.
 """
 import torch
 
 GROUP_SIZE = 128                              # elements per quantisation block along the contraction axis
 SHARED_EXP_TORCH_TYPE = torch.float32         # dtype of the block scales; only float32 is supported
 INPUT_OUTPUT_TORCH_TYPE = torch.bfloat16      # dtype of GEMM / dequantize outputs: bfloat16, float16 or float32
+DROP_WEIGHT_IN_EVAL = False                   # prepare_for_eval() releases the floating-point weight (int8-resident inference)
+CACHE_QUANTIZED_WEIGHTS = False               # training: keep both int8 blockings of a weight until the weight changes

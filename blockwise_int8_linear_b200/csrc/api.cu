@@ -226,11 +226,26 @@ int bi8_gemm_dequant_fused_quant(const void* x, int x_dtype, int64_t ldx, int8_t
                             workspace_bytes, flags & ~BI8_GEMM_FORCE_SKINNY, stream);
 }
 
-int bi8_linear_forward(const void* x, int x_dtype, int64_t ldx, int8_t* xq, float* sx, const int8_t* Wq, int64_t ldw,
-                       const float* sW, const void* bias, int bias_dtype, void* C, int64_t ldc, int out_dtype, int64_t M,
-                       int64_t N, int64_t K, int block, void* workspace, size_t workspace_bytes, int flags, void* stream) {
-    return bi8_gemm_dequant_fused_quant(x, x_dtype, ldx, xq, sx, Wq, ldw, sW, bias, bias_dtype, C, ldc, out_dtype, M, N, K, block,
-                                        workspace, workspace_bytes, flags, stream);
+int bi8_stream_capture_id(void* stream, unsigned long long* id) {
+    if (!id) return fail(BI8_ERR_NULL, "stream_capture_id: null output");
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    unsigned long long cid = 0;
+    BI8_CUDA_TRY(cudaStreamGetCaptureInfo(static_cast<cudaStream_t>(stream), &st, &cid));
+    *id = (st == cudaStreamCaptureStatusActive) ? cid : 0ull;
+    return BI8_OK;
+}
+
+int bi8_gemm_wait_selftest(const int8_t* A, int64_t lda, const int8_t* Bt, int64_t ldb, const float* sA, const float* sB, void* C,
+                           int64_t ldc, int out_dtype, int64_t M, int64_t N, int64_t K, int block, unsigned wait_limit_us,
+                           int skip_stage, void* stream) {
+    GemmArgs g{A, lda, Bt, ldb, sA, sB, nullptr, 0, C, ldc, out_dtype, nullptr, M, N, K, block, BI8_GEMM_FORCE_TC, nullptr, 0};
+    int rc = check_gemm(g, false);
+    if (rc != BI8_OK) return rc;
+    if (M == 0 || N == 0 || K == 0) return fail(BI8_ERR_SHAPE, "gemm_wait_selftest: empty problem");
+    if (wait_limit_us > 2000000u) return fail(BI8_ERR_LIMIT, "gemm_wait_selftest: wait limit above two seconds");
+    g.wait_limit_us = wait_limit_us;
+    g.skip_stage = skip_stage;
+    return dispatch_gemm(g, static_cast<cudaStream_t>(stream));
 }
 
 int bi8_mma_peak_probe(int iters, float* ms, int* sm_count) {

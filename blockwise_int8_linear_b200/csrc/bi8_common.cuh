@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "../../include/bi8.h"
 
 namespace bi8 {
@@ -23,6 +25,25 @@ inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_
         cudaError_t e__ = (expr);                                                             \
         if (e__ != cudaSuccess) return ::bi8::fail(BI8_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e__)); \
     } while (0)
+
+// The opt-in to more than 48 KiB of dynamic shared memory is an attribute of a kernel ON A DEVICE.  A launcher keeps
+// one SmemOptIn per kernel instance (a function-local static) and calls ensure() before every launch: the attribute
+// is set the first time the instance is used on each device, under a mutex (launchers run on several host threads).
+struct SmemOptIn {
+    std::mutex mu;
+    size_t bytes[64] = {0};
+    template <typename Kern>
+    int ensure(Kern kern, size_t want) {
+        int dev = 0;
+        BI8_CUDA_TRY(cudaGetDevice(&dev));
+        if (dev < 0 || dev >= 64) return fail(BI8_ERR_CUDA, "device ordinal %d out of range", dev);
+        std::lock_guard<std::mutex> lock(mu);
+        if (bytes[dev] >= want) return BI8_OK;
+        BI8_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)want));
+        bytes[dev] = want;
+        return BI8_OK;
+    }
+};
 
 // ---- launchers implemented in the other translation units -------------------------------------
 int launch_quantize_rowwise(const void* x, int dt, int64_t ldx, int8_t* q, float* s, int64_t M, int64_t K,
@@ -54,6 +75,8 @@ struct GemmArgs {
     int x_dtype = 0;
     int64_t ldx = 0;
     bool after_own_quantizer = false;   // the kernel launched just before is this library's decode quantizer
+    unsigned wait_limit_us = 0;         // diagnostic: limit of the general kernel's bounded waits (0 = default, about 2 s)
+    int skip_stage = -1;                // diagnostic: the general kernel's producer leaves this stage of its first item out
 };
 
 bool gemm_tc_applicable(const GemmArgs& g, const char** why);

@@ -235,7 +235,9 @@ int launch_gemm_smallm(const GemmArgs& g, cudaStream_t st) {
     for (int m_base = 0; m_base < g.M; m_base += kMT) {
 #define BI8_SMALLM(QB)                                                                                                  \
     {                                                                                                                   \
-        BI8_CUDA_TRY(cudaFuncSetAttribute(gemm_smallm_kernel<QB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        static SmemOptIn opt_in;                                                                                        \
+        const int orc = opt_in.ensure(gemm_smallm_kernel<QB>, smem);                                                    \
+        if (orc != BI8_OK) return orc;                                                                                  \
         gemm_smallm_kernel<QB><<<(unsigned)ctas, kWarps * 32, smem, st>>>(g.A, g.lda, g.Bt, g.ldb, g.sA, g.sB, g.bias,    \
                                                                           g.bias_dtype, g.C, g.ldc, g.out_dtype, m_base,  \
                                                                           (int)g.M, (int)g.N, (int)g.K, nb, chunks);      \

@@ -5,23 +5,35 @@
 //   acc += sB[j,n] * sA[j,m] * float(P_j) / 127^2   fp32, j ascending (line 120)
 //   C = cast(acc) (+ cast(bias))                    (lines 125-131)
 //
-// One persistent CTA per SM works on 128 x 160 output tiles.  Warp roles:
-//   warp 0      TMA producer: 128-byte-swizzled K-major tiles of A (128 rows) and Bt (160 rows), 128 K-bytes
-//               per stage, ring of kStages stages
-//   warp 1      issues tcgen05.mma kind::i8 (M128 N160 K32): the MMAs of one quantisation block accumulate
-//               into one of three s32 accumulators in tensor memory (the hand-off latency of a block is
-//               several times its MMA time, so more than two blocks have to be in flight), then a commit hands that
-//               accumulator to the promotion warps
-//   warps 2-3   stage the block scales of the tile (sA: 128 rows, sB: 160 columns per block) in shared memory
-//   warps 4-19  promotion + epilogue: read an accumulator from tensor memory (each warp owns 32 rows x 40
-//               columns), fold it into fp32 accumulators held in registers, release the accumulator; after
-//               the last block convert, add bias and store
-// Registers are moved from warps 0-3 to warps 4-19 with setmaxnreg (40 fp32 accumulators per thread); four
-// promotion warps per scheduler cover each other's tensor-memory load latency.
+// One persistent CTA per SM works on 128 x BN output tiles.  Warp roles:
+//   warp 0      producer.  Per stage two TMA copies of 128-byte-swizzled K-major operand tiles (A: 128 rows, Bt: BN
+//               rows, 128 K-bytes) into a ring of kStages slots, and two TMA copies of the stage's block scales (an
+//               fp32 box [blocks, 128] of sA and [blocks, BN] of sB) into a ring of kScaleStages slots, all four on the
+//               stage's one "full" barrier.  Scale tensors that a tensor map cannot describe (base or row length not
+//               16-byte aligned) are copied with cp.async by the warp's 32 lanes instead, arriving on the same barrier.
+//               The scale ring needs no barriers of its own: the promotion warps read a stage's scales only after
+//               they have seen one of its accumulators complete (the MMAs were issued after the stage's barrier), and
+//               the ring is deep enough that a slot is never rewritten while in use (see kScaleStages).
+//   warp 1      issues tcgen05.mma kind::i8 (M128 N=BN K32): the MMAs of one quantisation block accumulate into one of
+//               three s32 accumulators in tensor memory, then a commit hands that accumulator to the promotion warps.
+//   warps 2-3   spare (they only take part in set-up and teardown; see the register note below)
+//   warps 4..   promotion + epilogue, PW warps per tensor-memory lane quarter.  A warp owns 32 rows x BN/PW columns of
+//               the tile.  Per block it reads its part of the finished accumulator in two halves, re-seeds what it has
+//               read, folds the values into fp32 accumulators in registers and releases the accumulator; the first half
+//               of the NEXT block is already being read while the second half of the current one is folded, so a warp
+//               always has arithmetic to issue while its tensor-memory loads are in flight.  After the last block of a
+//               tile it casts, adds bias and stores.
+// The fold costs two FMAs per element and block (t = P*s_row, acc += s_col*t): 2*128*BN FMAs per block on 128 FMA lanes
+// is twice the time the MMAs of a 64-deep block need, so the FMA pipes, not the tensor pipe, bound this kernel; what
+// the code around the FMAs must do is stay out of their way (few instructions, no waiting that is not overlapped).
 //
-// Seeded conversion (default): the promotion warps refill a drained accumulator with the bit pattern of
-// 1.5*2^23 and every MMA accumulates on top of it.  Integer addition on that pattern is exact float
-// arithmetic while |P| < 2^22, so the word read back is the float 1.5*2^23 + P and
+// Registers: a scheduler (SM sub-partition) owns a quarter of the register file and every fourth warp, and setmaxnreg can
+// only move registers between warps of the same scheduler.  Each scheduler has exactly one of warps 0-3, which shrinks,
+// and PW promotion warps, which grow: PW = 4: 96 at launch -> 32 / 112; PW = 3: 128 -> 32 / 160; PW = 2: 168 -> 40 / 232.
+//
+// Seeded conversion (default): the promotion warps refill a drained accumulator with the bit pattern of 1.5*2^23 and
+// every MMA accumulates on top of it.  Integer addition on that pattern is exact float arithmetic while |P| < 2^22
+// (127^2 * 128 < 2^22), so the word read back is the float 1.5*2^23 + P and
 //   t = fma(word, s, -1.5*2^23 * s) = fl(P * s)
 // needs no int->float conversion.  s = sA[j,m]/127^2 rounded to 22 significant bits makes 1.5*2^23*s exact.
 #include "bi8_common.cuh"
@@ -30,25 +42,58 @@
 #include <cstdlib>
 #include <cstring>
 
+#ifndef BI8_TC_VARIANTS
+#define BI8_TC_VARIANTS 0
+#endif
+
 namespace bi8 {
 namespace {
 
 using namespace ptx;
 
 constexpr int kBM = 128;                 // tile rows
-constexpr int kBN = 160;                 // tile columns (40 per promotion warp: accumulators fit the register budget)
-constexpr int kAccBufs = 3;              // s32 accumulators in tensor memory (3 x 160 of the 512 columns)
-constexpr int kAccStride = kBN;          // tensor-memory columns between consecutive accumulators
+constexpr int kAccBufs = 3;              // s32 accumulators in tensor memory
 constexpr int kProbeN = 256;             // N of the issue-rate probe's MMAs
 constexpr int kStages = 5;
-constexpr int kScaleStages = 4;
-constexpr int kEpiWarps = 16;             // 4 lane quarters x 4 column slices of 64
-constexpr int kThreadsTc = (4 + kEpiWarps) * 32;
-constexpr int kEpiCols = kBN / (kEpiWarps / 4);   // columns owned by one promotion warp
+// Scale ring depth.  The producer fills the slot of stage s after the MMA warp has committed stage s - kStages, whose last
+// block was issued into an accumulator that the promotion warps had released three blocks earlier: with 2 blocks per
+// stage they are then done with every stage up to s - kStages - 2, with 1 block per stage up to s - kStages - 3, with 4
+// up to s - kStages - 1.  A ring of kStages + 3 slots is therefore never overwritten while a promotion warp reads it.
+constexpr int kScaleStages = 8;
+static_assert(kScaleStages >= kStages + 3, "scale ring too shallow for the lag of the promotion warps");
+constexpr int kRoleWarps = 4;            // producer, MMA issuer, two spare: one warp per scheduler gives its registers away
 constexpr uint32_t kABytes = kBM * kBK;  // 16 KiB
-constexpr uint32_t kBBytes = kBN * kBK;  // 20 KiB
 constexpr uint32_t kSeedBits = 0x4B400000u;   // float 1.5 * 2^23
 constexpr float kSeedF = 12582912.0f;
+
+// Geometry that depends on the number of promotion warps per lane quarter.
+template <int PW>
+struct Cfg {
+    static_assert(PW == 2 || PW == 3 || PW == 4, "2, 3 or 4 promotion warps per lane quarter");
+    static constexpr int BN = PW == 3 ? 144 : 160;        // tile columns: kAccBufs * BN <= 512 tensor-memory columns
+    static constexpr int COLS = BN / PW;                  // columns owned by one promotion thread: 80, 48, 40
+    static constexpr int H0 = PW == 2 ? 40 : 24;          // the accumulator is read as columns [0, H0) and [H0, COLS)
+    static constexpr int H1 = COLS - H0;                  // 40, 24, 16
+    // the first half of the next block is requested while the second half of the current one is folded; with 112
+    // registers (PW = 4) the two halves, 40 accumulators and the seed registers leave no room for that
+    static constexpr bool PREFETCH = PW != 4;
+    static constexpr int EPI_WARPS = 4 * PW;
+    static constexpr int THREADS = (kRoleWarps + EPI_WARPS) * 32;
+    static constexpr int LAUNCH_REGS = PW == 2 ? 168 : PW == 3 ? 128 : 96;     // 65536 / THREADS, rounded down to a multiple of 8
+    static constexpr int ROLE_REGS = PW == 2 ? 40 : 32;
+    static constexpr int EPI_REGS = PW == 2 ? 232 : PW == 3 ? 160 : 112;
+    static constexpr uint32_t B_BYTES = BN * kBK;
+    static constexpr uint32_t STAGE_BYTES = kABytes + B_BYTES;
+    static constexpr uint32_t scale_off = kStages * STAGE_BYTES;
+    // setmaxnreg moves registers inside a scheduler's share of the CTA's launch-time allocation: the total after the
+    // moves must not exceed it, or setmaxnreg.inc blocks forever.  (The launcher also checks the register count the
+    // compiler really chose for the kernel.)
+    static_assert(ROLE_REGS + PW * EPI_REGS <= (1 + PW) * LAUNCH_REGS, "register budget of a scheduler exceeds its launch allocation");
+    static_assert((1 + PW) * 32 * LAUNCH_REGS <= 16384, "launch allocation exceeds a scheduler's register file");
+    static_assert(kAccBufs * BN <= 512 && COLS % 8 == 0 && H0 % 8 == 0 && H1 % 8 == 0 && BN % 16 == 0, "tile geometry");
+    __host__ __device__ static constexpr uint32_t a_off(int s) { return (uint32_t)s * STAGE_BYTES; }
+    __host__ __device__ static constexpr uint32_t b_off(int s) { return a_off(s) + kABytes; }
+};
 
 struct TcParams {
     const float* sA;
@@ -62,32 +107,34 @@ struct TcParams {
     int tiles_m, tiles_n;
     int out_dtype, bias_dtype;
     int vec_store;      // C base and row pitch allow 16-byte stores
-    int vec_scales;     // sA, sB and their row lengths allow 16-byte loads
+    int tma_scales;     // sA and sB are described by the tensor maps tmSA / tmSB
     int ksplit;         // > 1: the K stages are divided over ksplit work items per tile (split-K)
     int stages_per_split;
     float* ws;          // split-K: fp32 partial results [ksplit, M, N]
+    unsigned wait_limit_us;   // 0: default limit of the bounded waits (about two seconds)
+    int skip_stage;     // >= 0: diagnostic, the producer leaves this stage of its first work item out
 };
 
-struct Smem {
-    // byte offsets from the 1024-aligned base of dynamic shared memory
-    __host__ __device__ static constexpr uint32_t a_off(int s) { return (uint32_t)s * (kABytes + kBBytes); }
-    __host__ __device__ static constexpr uint32_t b_off(int s) { return a_off(s) + kABytes; }
-    static constexpr uint32_t scale_off = kStages * (kABytes + kBBytes);
-};
-
-template <int QB>
+template <int QB, int PW>
 struct Geo {
+    using C = Cfg<PW>;
     static constexpr int BPS = kBK / QB;                        // quantisation blocks per stage
     static constexpr int MMAS = QB / 32;                        // MMAs (K = 32) per block
-    static constexpr int SC_FLOATS = BPS * (kBM + kBN);         // scale floats per stage
-    static constexpr uint32_t bar_off = Smem::scale_off + kScaleStages * SC_FLOATS * 4;
+    static constexpr int SC_FLOATS = (BPS * (kBM + C::BN) + 31) / 32 * 32;   // scale floats per stage, [BPS][128] of sA then [BPS][BN] of sB, padded to 128 bytes
+    static constexpr int SB_OFF = BPS * kBM;                    // first sB float of a stage
+    static constexpr uint32_t bar_off = C::scale_off + kScaleStages * SC_FLOATS * 4;
     // barrier slots (8 bytes each)
     static constexpr int FULL_AB = 0, EMPTY_AB = kStages, ACC_FULL = 2 * kStages, ACC_EMPTY = 2 * kStages + kAccBufs,
-                         SC_FULL = 2 * kStages + 2 * kAccBufs, SC_EMPTY = 2 * kStages + 2 * kAccBufs + kScaleStages,
-                         NBARS = 2 * kStages + 2 * kAccBufs + 2 * kScaleStages;
-    static constexpr uint32_t misc_off = bar_off + NBARS * 8;   // tmem holder (4 B) + abort flag (4 B)
-    static constexpr uint32_t total = misc_off + 16;
+                         NBARS = 2 * kStages + 2 * kAccBufs;
+    static constexpr uint32_t misc_off = bar_off + NBARS * 8;   // tmem holder (4 B) + abort flag (4 B) + never-raised flag (4 B)
+    static constexpr uint32_t prof_off = misc_off + 16;         // diagnostic build: cycle counters [20 warps][12]
+    static constexpr uint32_t total = prof_off + 20 * 12 * 4;
+    static_assert((SC_FLOATS * 4) % 128 == 0 && (SB_OFF * 4) % 128 == 0 && C::scale_off % 1024 == 0, "TMA destinations of the scale boxes are 128-byte aligned");
 };
+
+#if BI8_TC_VARIANTS
+__device__ unsigned int g_prof[160 * 20 * 12];
+#endif
 
 // Work item -> tile and K-stage range.  Items of one split are consecutive, so CTAs that run together work on
 // different tiles of the same K range.
@@ -100,52 +147,139 @@ __device__ __forceinline__ void item_range(int item, int num_tiles, int nks, int
     if (ks1 > nks) ks1 = nks;
 }
 
+template <int BN>
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int& m0, int& n0) {
     // consecutive tiles (CTAs that run together) share a column panel of Bt and sweep the rows of A
     m0 = (tile % tiles_m) * kBM;
-    n0 = (tile / tiles_m) * kBN;
+    n0 = (tile / tiles_m) * BN;
 }
 
-template <int QB, int MODE, bool SEED>
-__global__ void __launch_bounds__(kThreadsTc, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcParams p) {
-    using G = Geo<QB>;
+// Bounded wait of a converged warp: one poll by every lane, then (phase not complete yet, or the lanes disagree) the
+// bounded loop.  The result is the same in all lanes, so a warp-aligned instruction after the wait is never reached by
+// only some of them.  (Not a function call: the callers run under different setmaxnreg budgets.)
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, uint32_t abort_flag, long long limit) {
+    if (__builtin_expect(__all_sync(0xffffffffu, mbar_test(bar, parity)), 1)) return true;
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, limit));
+}
+
+// NC (a multiple of 8, at most 40) consecutive accumulator columns of this thread's lane -> registers.
+template <int NC>
+__device__ __forceinline__ void tmem_load_cols(uint32_t taddr, uint32_t (&S)[NC]) {
+    static_assert(NC == 40 || NC == 24 || NC == 16, "supported part widths");
+    if constexpr (NC == 40) {
+        tmem_ld32(taddr, reinterpret_cast<uint32_t(&)[32]>(S[0]));
+        tmem_ld8(taddr + 32u, reinterpret_cast<uint32_t(&)[8]>(S[32]));
+    } else if constexpr (NC == 24) {
+        tmem_ld16(taddr, reinterpret_cast<uint32_t(&)[16]>(S[0]));
+        tmem_ld8(taddr + 16u, reinterpret_cast<uint32_t(&)[8]>(S[16]));
+    } else {
+        tmem_ld16(taddr, reinterpret_cast<uint32_t(&)[16]>(S[0]));
+    }
+}
+
+// A value the compiler must treat as unknown from here on.  Loop-invariant addresses of the promotion loop go through
+// this: left alone, the compiler recomputes them (from the warp index, the thread index, the shared-memory base ...)
+// inside every block instead of keeping a register, which costs more instructions than the fold itself has to spare.
+__device__ __forceinline__ uint32_t keep(uint32_t v) {
+    asm volatile("" : "+r"(v));
+    return v;
+}
+
+// Folds NC s32 words a thread has read from an accumulator (its row, columns C0 .. C0+NC-1 of its COLS, one quantisation
+// block) into its fp32 accumulators: acc[n] += sB[n] * (P[n] * s), both products as packed FMAs on column pairs (PACK1
+// false: the first one as scalar FMAs).  `sw` is the shared address of the block's column scales of this thread (16-byte
+// aligned).
+template <bool SEED, bool PACK1, int C0, int NC, int COLS>
+__device__ __forceinline__ void fold_columns(const uint32_t (&S)[NC], uint32_t sw, float sxd, float negc, uint64_t (&acc2)[COLS / 2]) {
+    const uint64_t sxd2 = pack_f32x2(sxd, sxd), negc2 = pack_f32x2(negc, negc);
+#pragma unroll
+    for (int q = 0; q < NC / 4; ++q) {
+        uint64_t w0, w1, t0, t1;
+        lds_2xb64(sw + (uint32_t)((C0 / 4 + q) * 16), w0, w1);
+        if (SEED && PACK1) {
+            t0 = fma_f32x2(pack_u32x2(S[4 * q], S[4 * q + 1]), sxd2, negc2);
+            t1 = fma_f32x2(pack_u32x2(S[4 * q + 2], S[4 * q + 3]), sxd2, negc2);
+        } else {
+            float t[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (SEED) t[u] = __fmaf_rn(__uint_as_float(S[4 * q + u]), sxd, negc);
+                else t[u] = __fmul_rn((float)(int32_t)S[4 * q + u], sxd);
+            }
+            t0 = pack_f32x2(t[0], t[1]);
+            t1 = pack_f32x2(t[2], t[3]);
+        }
+        acc2[C0 / 2 + 2 * q] = fma_f32x2(w0, t0, acc2[C0 / 2 + 2 * q]);
+        acc2[C0 / 2 + 2 * q + 1] = fma_f32x2(w1, t1, acc2[C0 / 2 + 2 * q + 1]);
+    }
+}
+
+// VAR (development builds only): bit 0 = request the next block's first half early for every PW; bit 1 = first product
+// as scalar FMAs instead of packed ones; bit 4 = cycle counters.
+template <int QB, int MODE, bool SEED, int PW, int VAR>
+__global__ void __launch_bounds__(Cfg<PW>::THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmSA, const __grid_constant__ CUtensorMap tmSB, const TcParams p) {
+    using C = Cfg<PW>;
+    using G = Geo<QB, PW>;
+    constexpr int BN = C::BN, COLS = C::COLS, H0 = C::H0, H1 = C::H1;
+    constexpr bool kPrefetch = Cfg<PW>::PREFETCH || (VAR & 1);
+    constexpr bool kScales = (MODE == 0);           // the partial-sum dump uses no scales
+    constexpr bool kPack1 = (VAR & 2) == 0;
     extern __shared__ __align__(1024) unsigned char smem_dyn[];
     // dynamic shared memory is only guaranteed 16-byte aligned: round up to the swizzle atom
     const uint32_t raw = smem_u32(smem_dyn);
     const uint32_t base = (raw + 1023u) & ~1023u;
     unsigned char* base_ptr = smem_dyn + (base - raw);
-    float* sc_ring = reinterpret_cast<float*>(base_ptr + Smem::scale_off);
-    const uint32_t sc_ring_u32 = base + Smem::scale_off;
+    const float* sc_ring = reinterpret_cast<const float*>(base_ptr + C::scale_off);
+    const uint32_t sc_ring_u32 = base + C::scale_off;
     const uint32_t bars = base + G::bar_off;
     volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(base_ptr + G::misc_off);
     const uint32_t abort_flag = base + G::misc_off + 4;
+    const uint32_t never_flag = base + G::misc_off + 8;
     auto bar = [&](int slot) -> uint32_t { return bars + 8u * (uint32_t)slot; };
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // diagnostic (VAR bit 4): cycles between consecutive tick() calls of a warp, summed per call site in shared memory
+    uint32_t* prof = reinterpret_cast<uint32_t*>(base_ptr + G::prof_off);
+    uint32_t tprev = 0;
+    auto tick = [&](int slot) {
+        if (VAR & 16) {
+            const uint32_t now = (uint32_t)clock64();
+            if ((threadIdx.x & 31) == 0) atomicAdd(&prof[(threadIdx.x >> 5) * 12 + slot], now - tprev);
+            tprev = now;
+        }
+    };
+    if (VAR & 16) {
+        for (int i = threadIdx.x; i < 20 * 12; i += blockDim.x) prof[i] = 0;
+    }
+
+    // the warp index through a shuffle: known to be the same in all lanes, so what is derived from it lives in uniform registers
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
+    const int lane = threadIdx.x & 31;
     const int num_tiles = p.tiles_m * p.tiles_n;
     const int nks = (p.K + kBK - 1) / kBK;
     const int num_items = num_tiles * p.ksplit;
-
+    // limit of the bounded waits in SM cycles: about two seconds, or the diagnostic's shorter one.  The MMA warp's waits
+    // get the limit itself and all others four times as much, so that a missing operand stage is reported by the wait
+    // that misses it and not by a warp that starves behind it.
+    const long long wait_limit_mma = p.wait_limit_us ? (long long)p.wait_limit_us * 2000ll : 4000000000ll;
+    const long long wait_limit = p.wait_limit_us ? 4 * wait_limit_mma : wait_limit_mma;
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(bar(G::FULL_AB + s), 1);
+            // the lane that issues the TMA copies; with scales copied by cp.async, every lane of the producer warp as well
+            mbar_init(bar(G::FULL_AB + s), (kScales && !p.tma_scales) ? 33 : 1);
             mbar_init(bar(G::EMPTY_AB + s), 1);
         }
         for (int b = 0; b < kAccBufs; ++b) {
             mbar_init(bar(G::ACC_FULL + b), 1);
-            mbar_init(bar(G::ACC_EMPTY + b), kEpiWarps);
-        }
-        for (int s = 0; s < kScaleStages; ++s) {
-            mbar_init(bar(G::SC_FULL + s), 64);      // every lane of the two scale warps
-            mbar_init(bar(G::SC_EMPTY + s), kEpiWarps);
+            mbar_init(bar(G::ACC_EMPTY + b), C::EPI_WARPS);
         }
         sts_u32(abort_flag, 0u);
-        sts_u32(base + G::misc_off + 8, 0u);       // a flag nobody raises, for waits that must not be cut short
+        sts_u32(never_flag, 0u);                     // a flag nobody raises, for waits that must not be cut short
         mbar_fence_init();
         fence_proxy_async_smem();
     }
-    if (warp == 2) {
+    if (warp == 1) {
         tmem_alloc(smem_u32((const void*)tmem_holder), 512);
         tmem_relinquish();
     }
@@ -153,56 +287,82 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
+    if (VAR & 16) tprev = (uint32_t)clock64();
 
-    // setmaxnreg moves registers inside the CTA's launch-time allocation (kThreadsTc * 96): the totals after
-    // the moves must not exceed it, or setmaxnreg.inc blocks forever.
-    static_assert(128 * 24 + (kThreadsTc - 128) * 112 <= kThreadsTc * 96, "register budget exceeds the launch allocation");
-    if (warp < 4) {
-        setmaxnreg_dec<24>();
+    if (warp < kRoleWarps) {
+        setmaxnreg_dec<C::ROLE_REGS>();
         // Whole warps run the producer and MMA loops convergently and one lane issues: lanes parked at the final
         // barrier while a sibling lane loops make that loop crawl.
         if (warp == 0) {
-            // ---------------- TMA producer ----------------
-            int stage = 0;
+            // ---------------- producer: operand tiles and block scales ----------------
+            int stage = 0, sslot = 0;
             uint32_t phase = 0;
             int last_parity[kStages];
 #pragma unroll
             for (int s = 0; s < kStages; ++s) last_parity[s] = -1;
             bool ok = true;
+            bool first_item = true;
+            constexpr uint32_t kScaleBytes = (uint32_t)(G::BPS * (kBM + BN) * 4);
             for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
                 int tile, split, ks0, ks1, m0, n0;
                 item_range(item, num_tiles, nks, p.stages_per_split, tile, split, ks0, ks1);
-                tile_coords(tile, p.tiles_m, m0, n0);
+                tile_coords<BN>(tile, p.tiles_m, m0, n0);
                 for (int ks = ks0; ks < ks1; ++ks) {
-                    ok = __all_sync(0xffffffffu, mbar_wait(bar(G::EMPTY_AB + stage), phase ^ 1u, abort_flag));
+                    ok = warp_wait(bar(G::EMPTY_AB + stage), phase ^ 1u, abort_flag, wait_limit);
                     if (!ok) {
                         if (lane == 0) report_timeout(p.status, abort_flag, W_EMPTY_AB);
                         break;
                     }
-                    if (lane == 0) {
-                        mbar_expect_tx(bar(G::FULL_AB + stage), kABytes + kBBytes);
-                        tma_load_2d(base + Smem::a_off(stage), &tmA, bar(G::FULL_AB + stage), ks * kBK, m0);
-                        tma_load_2d(base + Smem::b_off(stage), &tmB, bar(G::FULL_AB + stage), ks * kBK, n0);
+                    const bool skip = first_item && p.skip_stage >= 0 && ks - ks0 == p.skip_stage;   // diagnostic only
+                    const uint32_t fb = bar(G::FULL_AB + stage);
+                    const uint32_t sdst = sc_ring_u32 + (uint32_t)(sslot * G::SC_FLOATS * 4);
+                    if (lane == 0 && !skip) {
+                        mbar_expect_tx(fb, C::STAGE_BYTES + ((kScales && p.tma_scales) ? kScaleBytes : 0u));
+                        tma_load_2d(base + C::a_off(stage), &tmA, fb, ks * kBK, m0);
+                        tma_load_2d(base + C::b_off(stage), &tmB, fb, ks * kBK, n0);
+                        if (kScales && p.tma_scales) {
+                            // boxes [BPS, 128] of sA and [BPS, BN] of sB; rows and blocks outside the tensors read as zero
+                            tma_load_2d(sdst, &tmSA, fb, m0, ks * G::BPS);
+                            tma_load_2d(sdst + (uint32_t)(G::SB_OFF * 4), &tmSB, fb, n0, ks * G::BPS);
+                        }
+                    }
+                    if (kScales && !p.tma_scales && !skip) {
+                        // asynchronous 4-byte copies: the warp does not wait for the data; each lane's arrival on the
+                        // stage's barrier fires when its copies have landed
+                        for (int idx = lane; idx < G::BPS * (kBM + BN); idx += 32) {
+                            const bool is_a = idx < G::SB_OFF;
+                            const int rel = is_a ? idx : idx - G::SB_OFF;
+                            const int width = is_a ? kBM : BN;
+                            const int blk = rel / width, c = rel % width;
+                            const int j = ks * G::BPS + blk;
+                            const int x = (is_a ? m0 : n0) + c, extent = is_a ? p.M : p.N;
+                            const float* src = is_a ? p.sA : p.sB;
+                            const bool live = j < p.nb && x < extent;
+                            const float* g = live ? src + (int64_t)j * extent + x : src;
+                            cp_async_4(sdst + (uint32_t)(idx * 4), g, live ? 4u : 0u);
+                        }
+                        cp_async_arrive(fb);
                     }
                     __syncwarp();
+                    if (!skip) {
 #pragma unroll
-                    for (int s = 0; s < kStages; ++s)
-                        if (s == stage) last_parity[s] = (int)phase;
+                        for (int s = 0; s < kStages; ++s)
+                            if (s == stage) last_parity[s] = (int)phase;
+                    }
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                    if (++sslot == kScaleStages) sslot = 0;
                 }
+                first_item = false;
             }
             if (!ok) {
                 // do not leave while our own copies may still land in this CTA's shared memory
 #pragma unroll
-                for (int s = 0; s < kStages; ++s) {
-                    if (last_parity[s] >= 0) {
-                        (void)mbar_wait(bar(G::FULL_AB + s), (uint32_t)last_parity[s], base + G::misc_off + 8, 200000000ll);
-                    }
-                }
+                for (int s = 0; s < kStages; ++s)
+                    if (last_parity[s] >= 0) (void)mbar_wait(bar(G::FULL_AB + s), (uint32_t)last_parity[s], never_flag, 200000000ll);
             }
         } else if (warp == 1) {
             // ---------------- MMA issuer ----------------
-            constexpr uint32_t idesc = umma_idesc_i8(kBM, kBN);
+            constexpr uint32_t idesc = umma_idesc_i8(kBM, BN);
             int stage = 0, accbuf = 0;
             uint32_t phase = 0, accphase = 0;
             bool ok = true;
@@ -210,33 +370,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 int tile, split, ks0, ks1;
                 item_range(item, num_tiles, nks, p.stages_per_split, tile, split, ks0, ks1);
                 for (int ks = ks0; ks < ks1 && ok; ++ks) {
-                    ok = __all_sync(0xffffffffu, mbar_wait(bar(G::FULL_AB + stage), phase, abort_flag));
+                    tick(3);
+                    ok = warp_wait(bar(G::FULL_AB + stage), phase, abort_flag, wait_limit_mma);
                     if (!ok) {
                         if (lane == 0) report_timeout(p.status, abort_flag, W_FULL_AB);
                         break;
                     }
+                    tick(0);
                     tc_fence_after();
-                    const uint64_t adesc = umma_desc_k_sw128(base + Smem::a_off(stage));
-                    const uint64_t bdesc = umma_desc_k_sw128(base + Smem::b_off(stage));
+                    const uint64_t adesc = umma_desc_k_sw128(base + C::a_off(stage));
+                    const uint64_t bdesc = umma_desc_k_sw128(base + C::b_off(stage));
 #pragma unroll
                     for (int blk = 0; blk < G::BPS; ++blk) {
                         if (ks * G::BPS + blk >= p.nb) break;
-                        ok = __all_sync(0xffffffffu, mbar_wait(bar(G::ACC_EMPTY + accbuf), accphase, abort_flag));
+                        ok = warp_wait(bar(G::ACC_EMPTY + accbuf), accphase, abort_flag, wait_limit_mma);
                         if (!ok) {
                             if (lane == 0) report_timeout(p.status, abort_flag, W_ACC_EMPTY);
                             break;
                         }
+                        tick(1);
                         tc_fence_after();
                         if (lane == 0) {
 #pragma unroll
                             for (int i = 0; i < G::MMAS; ++i) {
                                 const uint64_t koff = (uint64_t)((blk * G::MMAS + i) * 32 / 16);
-                                mma_i8(tmem_base + (uint32_t)accbuf * kAccStride, adesc + koff, bdesc + koff, idesc,
-                                       (SEED || i > 0) ? 1u : 0u);
+                                mma_i8(tmem_base + (uint32_t)(accbuf * BN), adesc + koff, bdesc + koff, idesc, (SEED || i > 0) ? 1u : 0u);
                             }
                             tc_commit(bar(G::ACC_FULL + accbuf));
                         }
                         __syncwarp();
+                        tick(2);
                         if (++accbuf == kAccBufs) { accbuf = 0; accphase ^= 1u; }
                     }
                     if (!ok) break;
@@ -245,73 +408,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
             }
-        } else {
-            // ---------------- scale loaders: warp 2 stages sA (128 rows per block), warp 3 sB (160 columns) ----------
-            const bool is_a = (warp == 2);
-            const float* src = is_a ? p.sA : p.sB;
-            const int extent = is_a ? p.M : p.N;          // row length of the scale tensor
-            const int width = is_a ? kBM : kBN;           // floats per block taken by this warp
-            const int dst_off = is_a ? 0 : kBM;
-            int sstage = 0;
-            uint32_t sphase = 0;
-            bool ok = true;
-            for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-                int tile, split, ks0, ks1, m0, n0;
-                item_range(item, num_tiles, nks, p.stages_per_split, tile, split, ks0, ks1);
-                tile_coords(tile, p.tiles_m, m0, n0);
-                const int x0 = is_a ? m0 : n0;
-                for (int ks = ks0; ks < ks1; ++ks) {
-                    ok = __all_sync(0xffffffffu, mbar_wait(bar(G::SC_EMPTY + sstage), sphase ^ 1u, abort_flag));
-                    if (!ok) {
-                        if (lane == 0) report_timeout(p.status, abort_flag, W_SC_EMPTY);
-                        break;
-                    }
-                    // asynchronous copies: the warp does not wait for the data, so the loads of several stages are
-                    // in flight at once; each lane's arrival on the stage's barrier fires when its copies have landed
-                    const uint32_t dst = sc_ring_u32 + (uint32_t)((sstage * G::SC_FLOATS + dst_off) * 4);
-                    if (src == nullptr) {
-                        // partial-sum dump: no scales, the ring content is never used
-                    } else if (p.vec_scales) {
-                        const int nv = G::BPS * width / 4;                   // 16-byte pieces in this warp's part
-                        for (int idx = lane; idx < nv; idx += 32) {
-                            const int blk = idx / (width / 4), c4 = (idx % (width / 4)) * 4;
-                            const int j = ks * G::BPS + blk;
-                            const bool live = j < p.nb && x0 + c4 < extent;
-                            const float* g = live ? src + (int64_t)j * extent + x0 + c4 : src;
-                            cp_async_16(dst + (uint32_t)((blk * (kBM + kBN) + c4) * 4), g, live ? 16u : 0u);
-                        }
-                    } else {
-                        for (int idx = lane; idx < G::BPS * width; idx += 32) {
-                            const int blk = idx / width, c = idx % width;
-                            const int j = ks * G::BPS + blk;
-                            const bool live = j < p.nb && x0 + c < extent;
-                            const float* g = live ? src + (int64_t)j * extent + x0 + c : src;
-                            cp_async_4(dst + (uint32_t)((blk * (kBM + kBN) + c) * 4), g, live ? 4u : 0u);
-                        }
-                    }
-                    cp_async_arrive(bar(G::SC_FULL + sstage));
-                    if (++sstage == kScaleStages) { sstage = 0; sphase ^= 1u; }
-                }
-            }
         }
     } else {
-        // ---------------- promotion + epilogue (warps 4..19) ----------------
-        setmaxnreg_inc<112>();
-        const int quarter = warp & 3;            // tensor-memory lanes 32*quarter .. +31 belong to this warp
-        const int slice = (warp - 4) >> 2;       // columns kEpiCols*slice .. of the tile
+        // ---------------- promotion + epilogue ----------------
+        setmaxnreg_inc<C::EPI_REGS>();
+        const int quarter = warp & 3;                     // tensor-memory lanes 32*quarter .. +31 belong to this warp
+        const int slice = (warp - kRoleWarps) >> 2;       // columns COLS*slice .. of the tile
         const int row = quarter * 32 + lane;
-        const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(slice * kEpiCols);
+        const uint32_t t_lane = keep(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(slice * COLS));
+        // shared addresses of this thread's row scale and of its first column scale in scale stage 0, block 0
+        const uint32_t sa_addr = keep(sc_ring_u32 + (uint32_t)(row * 4));
+        const uint32_t sw_addr = keep(sc_ring_u32 + (uint32_t)((G::SB_OFF + slice * COLS) * 4));
+        const uint32_t bar0 = keep(bars);
+        const uint32_t leader = keep(lane == 0 ? 1u : 0u);
         const float div = 1.0f / (127.0f * 127.0f);
         uint32_t seedv[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) seedv[i] = opaque_u32(kSeedBits);
+        for (int i = 0; i < 8; ++i) seedv[i] = kSeedBits;
 
         if (SEED) {
 #pragma unroll
             for (int b = 0; b < kAccBufs; ++b)
 #pragma unroll
-                for (int c = 0; c < kEpiCols / 8; ++c) tmem_st8(t_lane + (uint32_t)(b * kAccStride + c * 8), seedv);
+                for (int c = 0; c < COLS / 8; ++c) tmem_st8(t_lane + (uint32_t)(b * BN + c * 8), seedv);
             tmem_wait_st();
+            // The seed registers are re-read from tensor memory: as the result of one load they are a tuple of consecutive
+            // registers that stays resident.  Left as eight constants the compiler rebuilds the tuple with eight moves
+            // in front of every store.
+            tmem_ld8(t_lane, seedv);
+            tmem_wait_ld();
         }
         tc_fence_before();
         __syncwarp();
@@ -319,51 +444,68 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
             for (int b = 0; b < kAccBufs; ++b) mbar_arrive(bar(G::ACC_EMPTY + b));
         }
+        auto reseed = [&](uint32_t taddr, int c0, int nc) {
+            if (SEED) {
+#pragma unroll
+                for (int c = 0; c < nc / 8; ++c) tmem_st8(taddr + (uint32_t)(c0 + c * 8), seedv);
+            }
+        };
+
+        // blocks this CTA's promotion warps will see: the read of a block's first half is issued during the block before it
+        int blocks_left = 0;
+        for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
+            int tile, split, ks0, ks1;
+            item_range(item, num_tiles, nks, p.stages_per_split, tile, split, ks0, ks1);
+            const int jend = ks1 * G::BPS < p.nb ? ks1 * G::BPS : p.nb;
+            blocks_left += jend - ks0 * G::BPS;
+        }
 
         int accbuf = 0, sstage = 0;
-        uint32_t accphase = 0, sphase = 0;
+        uint32_t accphase = 0;
+        uint32_t t_acc = t_lane;                  // this thread's part of accumulator `accbuf`
+        uint32_t sc_off = 0;                      // byte offset of scale stage `sstage`
         bool ok = true;
+        uint32_t S0[H0], S1[H1];
+        if (MODE == 0 && kPrefetch && blocks_left > 0) {
+            ok = warp_wait(bar0 + 8u * (uint32_t)(G::ACC_FULL + 0), 0u, abort_flag, wait_limit);
+            if (!ok) {
+                if (lane == 0) report_timeout(p.status, abort_flag, W_ACC_FULL);
+            } else {
+                tc_fence_after();
+                tmem_load_cols<H0>(t_lane, S0);
+            }
+        }
         for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
             int tile, split, ks0, ks1, m0, n0;
             item_range(item, num_tiles, nks, p.stages_per_split, tile, split, ks0, ks1);
-            tile_coords(tile, p.tiles_m, m0, n0);
+            tile_coords<BN>(tile, p.tiles_m, m0, n0);
+            tick(10);
             const int m = m0 + row;
-            const bool warp_live = (m0 + quarter * 32) < p.M;      // small M: most warps own no valid row
-            const int nbase = n0 + slice * kEpiCols;
-            // kEpiCols fp32 accumulators per thread, kept as packed pairs for fma.rn.f32x2
-            uint64_t acc2[kEpiCols / 2];
+            const int nbase = n0 + slice * COLS;
+            // COLS fp32 accumulators per thread, kept as packed pairs for fma.rn.f32x2
+            uint64_t acc2[COLS / 2];
 #pragma unroll
-            for (int i = 0; i < kEpiCols / 2; ++i) acc2[i] = 0ull;
+            for (int i = 0; i < COLS / 2; ++i) acc2[i] = 0ull;
 
             for (int ks = ks0; ks < ks1 && ok; ++ks) {
-                ok = __all_sync(0xffffffffu, mbar_wait(bar(G::SC_FULL + sstage), sphase, abort_flag));
-                if (!ok) {
-                    if (lane == 0) report_timeout(p.status, abort_flag, W_SC_FULL);
-                    break;
-                }
-                const float* sc = sc_ring + sstage * G::SC_FLOATS;
-                const uint32_t sc_u32 = sc_ring_u32 + (uint32_t)(sstage * G::SC_FLOATS * 4);
-#pragma unroll 1
+                tick(0);
+#pragma unroll
                 for (int blk = 0; blk < G::BPS; ++blk) {
                     const int j = ks * G::BPS + blk;
                     if (j >= p.nb) break;
-                    ok = __all_sync(0xffffffffu, mbar_wait(bar(G::ACC_FULL + accbuf), accphase, abort_flag));
-                    if (!ok) {
-                        if (lane == 0) report_timeout(p.status, abort_flag, W_ACC_FULL);
-                        break;
-                    }
-                    tc_fence_after();
-                    const uint32_t t_acc = t_lane + (uint32_t)(accbuf * kAccStride);
-                    if (!warp_live) {
-                        // all 32 rows of this warp lie beyond M: nothing to fold, and what the MMAs leave in these
-                        // tensor-memory lanes is never read
-                    } else if (MODE == 1) {
+                    if (MODE == 1) {
+                        ok = warp_wait(bar0 + 8u * (uint32_t)(G::ACC_FULL + accbuf), accphase, abort_flag, wait_limit);
+                        if (!ok) {
+                            if (lane == 0) report_timeout(p.status, abort_flag, W_ACC_FULL);
+                            break;
+                        }
+                        tc_fence_after();
 #pragma unroll
-                        for (int c = 0; c < kEpiCols / 8; ++c) {
+                        for (int c = 0; c < COLS / 8; ++c) {
                             uint32_t pv[8];
                             tmem_ld8(t_acc + (uint32_t)(c * 8), pv);
                             tmem_wait_ld();
-                            if (SEED) tmem_st8(t_acc + (uint32_t)(c * 8), seedv);
+                            reseed(t_acc, c * 8, 8);
                             if (m < p.M) {
                                 int32_t* dst = p.partials + ((int64_t)j * p.M + m) * p.N + nbase + c * 8;
 #pragma unroll
@@ -374,63 +516,75 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         }
                         if (SEED) tmem_wait_st();
                     } else {
-                        float sxd = __fmul_rn(lds_f32(sc_u32 + (uint32_t)((blk * (kBM + kBN) + row) * 4)), div);
+                        if (!kPrefetch) {
+                            ok = warp_wait(bar0 + 8u * (uint32_t)(G::ACC_FULL + accbuf), accphase, abort_flag, wait_limit);
+                            if (!ok) {
+                                if (lane == 0) report_timeout(p.status, abort_flag, W_ACC_FULL);
+                                break;
+                            }
+                            tc_fence_after();
+                            tmem_load_cols<H0>(t_acc, S0);
+                        }
+                        // the row's scale, while the read of the first half is in flight
+                        float sxd = __fmul_rn(lds_f32(sa_addr + sc_off + (uint32_t)(blk * kBM * 4)), div);
                         float negc = 0.0f;
                         if (SEED) {
                             sxd = __uint_as_float((__float_as_uint(sxd) + 2u) & 0xFFFFFFFCu);   // 22 significant bits
                             negc = -__fmul_rn(kSeedF, sxd);                                      // exact
                         }
-                        const uint64_t sxd2 = pack_f32x2(sxd, sxd), negc2 = pack_f32x2(negc, negc);
-                        const uint32_t sw_u32 = sc_u32 + (uint32_t)((blk * (kBM + kBN) + kBM + slice * kEpiCols) * 4);
-                        // 8 columns per step: one load, one re-seed store (8 resident seed registers), two 16-byte scale
-                        // loads, eight packed FMAs; the next load is issued before the current chunk is folded.
-                        uint32_t pa[8], pb[8];
-                        tmem_ld8(t_acc, pa);
-#pragma unroll
-                        for (int c = 0; c < kEpiCols / 8; ++c) {
-                            uint32_t(&cur)[8] = (c & 1) ? pb : pa;
-                            uint32_t(&nxt)[8] = (c & 1) ? pa : pb;
-                            tmem_wait_ld();
-                            if (c + 1 < kEpiCols / 8) tmem_ld8(t_acc + (uint32_t)((c + 1) * 8), nxt);
-                            if (SEED) tmem_st8(t_acc + (uint32_t)(c * 8), seedv);
-#pragma unroll
-                            for (int q = 0; q < 2; ++q) {
-                                uint64_t w0, w1;
-                                lds_2xb64(sw_u32 + (uint32_t)((c * 2 + q) * 16), w0, w1);
-                                uint64_t t0, t1;
-                                if (SEED) {
-                                    t0 = fma_f32x2(pack_u32x2(cur[4 * q], cur[4 * q + 1]), sxd2, negc2);
-                                    t1 = fma_f32x2(pack_u32x2(cur[4 * q + 2], cur[4 * q + 3]), sxd2, negc2);
-                                } else {
-                                    t0 = fma_f32x2(pack_f32x2((float)(int32_t)cur[4 * q], (float)(int32_t)cur[4 * q + 1]), sxd2, 0ull);
-                                    t1 = fma_f32x2(pack_f32x2((float)(int32_t)cur[4 * q + 2], (float)(int32_t)cur[4 * q + 3]), sxd2, 0ull);
-                                }
-                                acc2[c * 4 + q * 2] = fma_f32x2(w0, t0, acc2[c * 4 + q * 2]);
-                                acc2[c * 4 + q * 2 + 1] = fma_f32x2(w1, t1, acc2[c * 4 + q * 2 + 1]);
+                        const uint32_t sw = sw_addr + sc_off + (uint32_t)(blk * BN * 4);
+                        tmem_wait_ld();                                  // first half of this block
+                        tick(1);
+                        tmem_load_cols<H1>(t_acc + (uint32_t)H0, S1);    // second half, in flight during the fold
+                        reseed(t_acc, 0, H0);
+                        fold_columns<SEED, kPack1, 0, H0, COLS>(S0, sw, sxd, negc, acc2);
+                        tmem_wait_ld();
+                        tick(2);
+                        reseed(t_acc, H0, H1);
+                        // the next block's first half (the next accumulator, whichever tile it belongs to) is requested before
+                        // this block's second half is folded
+                        const int nbuf = accbuf + 1 == kAccBufs ? 0 : accbuf + 1;
+                        const uint32_t nphase = accbuf + 1 == kAccBufs ? accphase ^ 1u : accphase;
+                        --blocks_left;
+                        if (kPrefetch && blocks_left > 0) {
+                            ok = warp_wait(bar0 + 8u * (uint32_t)(G::ACC_FULL + nbuf), nphase, abort_flag, wait_limit);
+                            if (!ok) {
+                                if (lane == 0) report_timeout(p.status, abort_flag, W_ACC_FULL);
+                                break;
                             }
+                            tc_fence_after();
+                            tick(3);
+                            tmem_load_cols<H0>(t_lane + (uint32_t)(nbuf * BN), S0);
                         }
+                        fold_columns<SEED, kPack1, H0, H1, COLS>(S1, sw, sxd, negc, acc2);
+                        tick(4);
                         if (SEED) tmem_wait_st();
+                        tick(5);
                     }
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(bar(G::ACC_EMPTY + accbuf));
-                    if (++accbuf == kAccBufs) { accbuf = 0; accphase ^= 1u; }
+                    if (leader) mbar_arrive(bar0 + 8u * (uint32_t)(G::ACC_EMPTY + accbuf));
+                    tick(6);
+                    t_acc += (uint32_t)BN;
+                    if (++accbuf == kAccBufs) { accbuf = 0; accphase ^= 1u; t_acc = t_lane; }
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar(G::SC_EMPTY + sstage));
-                if (++sstage == kScaleStages) { sstage = 0; sphase ^= 1u; }
+                if (kScales) {
+                    sc_off += (uint32_t)(G::SC_FLOATS * 4);
+                    if (++sstage == kScaleStages) { sstage = 0; sc_off = 0; }
+                }
+                tick(7);
             }
             if (!ok) break;
 
             if (MODE == 0 && m < p.M) {
-                float acc[kEpiCols];
+                float acc[COLS];
 #pragma unroll
-                for (int i = 0; i < kEpiCols / 2; ++i) unpack_f32x2(acc2[i], acc[2 * i], acc[2 * i + 1]);
+                for (int i = 0; i < COLS / 2; ++i) unpack_f32x2(acc2[i], acc[2 * i], acc[2 * i + 1]);
                 if (p.ksplit > 1) {
                     // split-K: raw fp32 partial result of this K range; cast and bias happen in the reduction
                     float* wrow = p.ws + ((int64_t)split * p.M + m) * p.N;
 #pragma unroll
-                    for (int g = 0; g < kEpiCols / 4; ++g) {
+                    for (int g = 0; g < COLS / 4; ++g) {
                         const int n = nbase + g * 4;
                         if ((p.N & 3) == 0 && n + 4 <= p.N) {
                             *reinterpret_cast<float4*>(wrow + n) = make_float4(acc[g * 4], acc[g * 4 + 1], acc[g * 4 + 2], acc[g * 4 + 3]);
@@ -451,7 +605,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 if (p.out_dtype == BI8_F32) {
                     float* crow = static_cast<float*>(p.C) + (int64_t)m * p.ldc;
 #pragma unroll
-                    for (int g = 0; g < kEpiCols / 4; ++g) {
+                    for (int g = 0; g < COLS / 4; ++g) {
                         const int n = nbase + g * 4;
                         float v[4];
 #pragma unroll
@@ -471,7 +625,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const bool bf = p.out_dtype == BI8_BF16;
                     uint16_t* crow = static_cast<uint16_t*>(p.C) + (int64_t)m * p.ldc;
 #pragma unroll
-                    for (int g = 0; g < kEpiCols / 8; ++g) {
+                    for (int g = 0; g < COLS / 8; ++g) {
                         const int n = nbase + g * 8;
                         uint32_t w[4];
 #pragma unroll
@@ -505,12 +659,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 }
             }
         }
+        // a read that was requested for a block this warp never reached (only after a wait gave up)
+        if (MODE == 0) tmem_wait_ld();
     }
 
     // ---------------- teardown ----------------
+    tick(9);
     tc_fence_before();
     __syncthreads();
-    if (warp == 2) {
+#if BI8_TC_VARIANTS
+    if (VAR & 16) {
+        for (int i = threadIdx.x; i < 20 * 12; i += blockDim.x) g_prof[blockIdx.x * 240 + i] = prof[i];
+    }
+#endif
+    if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
     }
@@ -590,20 +752,68 @@ __global__ void __launch_bounds__(128, 1) mma_peak_probe_kernel(int iters, int* 
     }
 }
 
-template <int QB, int MODE, bool SEED>
-int launch_one(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int grid, cudaStream_t st) {
-    constexpr size_t smem = Geo<QB>::total + 1024;
-    BI8_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<QB, MODE, SEED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    gemm_tc_kernel<QB, MODE, SEED><<<grid, kThreadsTc, smem, st>>>(ma, mb, p);
+struct TcMaps {
+    CUtensorMap a, b, sa, sb;
+};
+
+template <int QB, int MODE, bool SEED, int PW, int VAR>
+int launch_one(const TcMaps& tm, const TcParams& p, int grid, cudaStream_t st) {
+    using C = Cfg<PW>;
+    constexpr size_t smem = Geo<QB, PW>::total + 1024;
+    static SmemOptIn opt_in;
+    const int rc = opt_in.ensure(gemm_tc_kernel<QB, MODE, SEED, PW, VAR>, smem);
+    if (rc != BI8_OK) return rc;
+    // setmaxnreg.inc waits for registers that the role warps of the same scheduler give up: if the compiler gave the
+    // kernel fewer registers per thread than the budget was written for, the wait would never end.  Checked once.
+    static int regs_ok = 0;       // 0 unknown, 1 fine, -1 refused
+    if (regs_ok == 0) {
+        cudaFuncAttributes fa;
+        BI8_CUDA_TRY(cudaFuncGetAttributes(&fa, gemm_tc_kernel<QB, MODE, SEED, PW, VAR>));
+        regs_ok = ((1 + PW) * fa.numRegs >= C::ROLE_REGS + PW * C::EPI_REGS && (1 + PW) * 32 * fa.numRegs <= 16384) ? 1 : -1;
+    }
+    if (regs_ok < 0) return fail(BI8_ERR_CUDA, "tensor-core GEMM: the kernel was compiled with a register count its register moves do not fit");
+    gemm_tc_kernel<QB, MODE, SEED, PW, VAR><<<grid, C::THREADS, smem, st>>>(tm.a, tm.b, tm.sa, tm.sb, p);
     BI8_CUDA_TRY(cudaGetLastError());
     return BI8_OK;
 }
 
+// Promotion warps per lane quarter (and with it the tile width) of the kernel that runs.
+int tc_pw() {
+#if BI8_TC_VARIANTS
+    if (const char* e = std::getenv("BI8_TC_PW")) {
+        const int v = std::atoi(e);
+        if (v >= 2 && v <= 4) return v;
+    }
+#endif
+    return 4;
+}
+int tc_bn() {
+    const int pw = tc_pw();
+    return pw == 3 ? Cfg<3>::BN : Cfg<4>::BN;
+}
+
+template <int QB, int PW>
+int launch_pw(const TcMaps& tm, const TcParams& p, int grid, bool partials, bool seed, int var, cudaStream_t st) {
+    if (partials) return seed ? launch_one<QB, 1, true, PW, 0>(tm, p, grid, st) : launch_one<QB, 1, false, PW, 0>(tm, p, grid, st);
+    if (!seed) return launch_one<QB, 0, false, PW, 0>(tm, p, grid, st);
+#if BI8_TC_VARIANTS
+    if (QB == 64 && var == 16) return launch_one<64, 0, true, PW, 16>(tm, p, grid, st);
+    if (QB == 64 && var == 1) return launch_one<64, 0, true, PW, 1>(tm, p, grid, st);
+    if (QB == 64 && var == 17) return launch_one<64, 0, true, PW, 17>(tm, p, grid, st);
+    if (QB == 64 && var == 2) return launch_one<64, 0, true, PW, 2>(tm, p, grid, st);
+#endif
+    (void)var;
+    return launch_one<QB, 0, true, PW, 0>(tm, p, grid, st);
+}
+
 template <int QB>
-int launch_qb(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int grid, bool partials, bool seed,
-              cudaStream_t st) {
-    if (partials) return seed ? launch_one<QB, 1, true>(ma, mb, p, grid, st) : launch_one<QB, 1, false>(ma, mb, p, grid, st);
-    return seed ? launch_one<QB, 0, true>(ma, mb, p, grid, st) : launch_one<QB, 0, false>(ma, mb, p, grid, st);
+int launch_qb(const TcMaps& tm, const TcParams& p, int grid, bool partials, bool seed, int var, cudaStream_t st) {
+#if BI8_TC_VARIANTS
+    const int pw = tc_pw();
+    if (pw == 2) return launch_pw<QB, 2>(tm, p, grid, partials, seed, var, st);
+    if (pw == 3) return launch_pw<QB, 3>(tm, p, grid, partials, seed, var, st);
+#endif
+    return launch_pw<QB, 4>(tm, p, grid, partials, seed, var, st);
 }
 
 }  // namespace
@@ -619,7 +829,8 @@ struct SplitPlan {
 };
 SplitPlan plan_split(int64_t M, int64_t N, int64_t K, int sms) {
     SplitPlan pl;
-    const int64_t tiles = ((M + kBM - 1) / kBM) * ((N + kBN - 1) / kBN);
+    const int bn = tc_bn();
+    const int64_t tiles = ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn);
     const int nks = (int)((K + kBK - 1) / kBK);
     pl.stages_per_split = nks;
     if (tiles <= 0 || nks <= 1 || tiles * 2 > sms) return pl;
@@ -658,13 +869,31 @@ bool gemm_tc_applicable(const GemmArgs& g, const char** why) {
 int launch_gemm_tc(const GemmArgs& g, cudaStream_t st) {
     const DeviceInfo di = device_info();
     if (!di.ok) return fail(BI8_ERR_CUDA, "tensor-core GEMM needs a compute capability 10.x device");
-    CUtensorMap ma, mb;
-    int rc = make_operand_map(&ma, g.A, g.M, g.K, g.lda, kBM);
+    int dev = 0;
+    BI8_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(BI8_ERR_CUDA, "device ordinal %d out of range", dev);
+    const int bps = kBK / g.block;
+    const int nb = (int)((g.K + g.block - 1) / g.block);
+    TcMaps tm;
+    int rc = cached_operand_map(&tm.a, dev, g.A, g.M, g.K, g.lda, kBM);
     if (rc != BI8_OK) return rc;
-    rc = make_operand_map(&mb, g.Bt, g.N, g.K, g.ldb, kBN);
+    const int bn = tc_bn();
+    rc = cached_operand_map(&tm.b, dev, g.Bt, g.N, g.K, g.ldb, bn);
     if (rc != BI8_OK) return rc;
     TcParams p;
     std::memset(&p, 0, sizeof(p));
+    const bool partials = g.partials != nullptr;
+    // the scale tensors go through TMA when a tensor map can describe them: 16-byte aligned base and row length
+    p.tma_scales = (!partials && aligned(g.sA, 16) && aligned(g.sB, 16) && g.M % 4 == 0 && g.N % 4 == 0) ? 1 : 0;
+    if (p.tma_scales) {
+        rc = cached_scale_map(&tm.sa, dev, g.sA, nb, g.M, kBM, bps);
+        if (rc != BI8_OK) return rc;
+        rc = cached_scale_map(&tm.sb, dev, g.sB, nb, g.N, bn, bps);
+        if (rc != BI8_OK) return rc;
+    } else {
+        tm.sa = tm.a;      // never dereferenced
+        tm.sb = tm.b;
+    }
     p.sA = g.sA;
     p.sB = g.sB;
     p.bias = g.bias;
@@ -676,17 +905,17 @@ int launch_gemm_tc(const GemmArgs& g, cudaStream_t st) {
     p.M = (int)g.M;
     p.N = (int)g.N;
     p.K = (int)g.K;
-    p.nb = (int)((g.K + g.block - 1) / g.block);
+    p.nb = nb;
     p.tiles_m = (int)((g.M + kBM - 1) / kBM);
-    p.tiles_n = (int)((g.N + kBN - 1) / kBN);
+    p.tiles_n = (int)((g.N + bn - 1) / bn);
     p.out_dtype = g.out_dtype;
     p.bias_dtype = g.bias_dtype;
     const int esz = g.out_dtype == BI8_F32 ? 4 : 2;
     p.vec_store = (g.C != nullptr && aligned(g.C, 16) && (g.ldc * esz) % 16 == 0) ? 1 : 0;
-    p.vec_scales = (g.partials == nullptr && aligned(g.sA, 16) && aligned(g.sB, 16) && g.M % 4 == 0 && g.N % 4 == 0) ? 1 : 0;
+    p.wait_limit_us = g.wait_limit_us;
+    p.skip_stage = g.skip_stage;
     const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
     if (tiles >= (1ll << 31) / 32) return fail(BI8_ERR_SHAPE, "too many output tiles");
-    const bool partials = g.partials != nullptr;
     SplitPlan pl;
     pl.stages_per_split = (int)((g.K + kBK - 1) / kBK);
     if (!partials) {
@@ -700,10 +929,14 @@ int launch_gemm_tc(const GemmArgs& g, cudaStream_t st) {
     const int64_t items = tiles * pl.ksplit;
     const int grid = (int)(items < di.sms ? items : di.sms);
     const bool seed = (g.flags & BI8_GEMM_NO_SEED) == 0;
+    int var = 0;
+#if BI8_TC_VARIANTS
+    if (const char* e = std::getenv("BI8_TC_VAR")) var = std::atoi(e);
+#endif
     switch (g.block) {
-        case 32: rc = launch_qb<32>(ma, mb, p, grid, partials, seed, st); break;
-        case 64: rc = launch_qb<64>(ma, mb, p, grid, partials, seed, st); break;
-        case 128: rc = launch_qb<128>(ma, mb, p, grid, partials, seed, st); break;
+        case 32: rc = launch_qb<32>(tm, p, grid, partials, seed, var, st); break;
+        case 64: rc = launch_qb<64>(tm, p, grid, partials, seed, var, st); break;
+        case 128: rc = launch_qb<128>(tm, p, grid, partials, seed, var, st); break;
         default: return fail(BI8_ERR_BLOCK, "tensor-core GEMM supports block 32, 64, 128 (got %d)", g.block);
     }
     if (rc != BI8_OK || pl.ksplit == 1) return rc;
@@ -713,6 +946,12 @@ int launch_gemm_tc(const GemmArgs& g, cudaStream_t st) {
     BI8_CUDA_TRY(cudaGetLastError());
     return BI8_OK;
 }
+
+#if BI8_TC_VARIANTS
+extern "C" __attribute__((visibility("default"))) int bi8_debug_read_prof(unsigned int* host, int n) {
+    return cudaMemcpyFromSymbol(host, g_prof, (size_t)n * 4) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 int run_mma_peak_probe(int iters, float* ms, int* sm_count) {
     const DeviceInfo di = device_info();

@@ -616,18 +616,22 @@ template <int QB, int BNS, bool FUSED>
 int launch_skinny(const GemmArgs& g, const SkParams& p, int grid, cudaStream_t st) {
     using G = SkGeo<QB, BNS, FUSED>;
     CUtensorMap mw, mx, ms;
-    int rc = make_operand_map(&mw, g.Bt, g.N, g.K, g.ldb, kTileRows);
+    int dev = 0;
+    BI8_CUDA_TRY(cudaGetDevice(&dev));
+    int rc = cached_operand_map(&mw, dev, g.Bt, g.N, g.K, g.ldb, kTileRows);
     if (rc != BI8_OK) return rc;
     if (FUSED) {
         mx = mw;                    // not used: the quantizer warps write the activation tile
     } else {
-        rc = make_operand_map(&mx, g.A, g.M, g.K, g.lda, BNS);
+        rc = cached_operand_map(&mx, dev, g.A, g.M, g.K, g.lda, BNS);
         if (rc != BI8_OK) return rc;
     }
-    rc = make_scale_map(&ms, g.sB, p.nb, g.N, kTileRows, G::BPS);
+    rc = cached_scale_map(&ms, dev, g.sB, p.nb, g.N, kTileRows, G::BPS);
     if (rc != BI8_OK) return rc;
     const size_t smem = smem_of<QB, BNS, FUSED>(p.nb);
-    BI8_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_skinny_kernel<QB, BNS, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    static SmemOptIn opt_in;
+    rc = opt_in.ensure(gemm_tc_skinny_kernel<QB, BNS, FUSED>, smem);
+    if (rc != BI8_OK) return rc;
     cudaLaunchConfig_t cfg;
     std::memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3((unsigned)grid);

@@ -73,6 +73,10 @@ int bi8_gemm_dequant_static(const int8_t* A, int64_t lda, const int8_t* Bt, int6
                          "gemm_dequant_static: this shape needs %zu bytes of split-K scratch, the built-in array holds %zu; "
                          "use bi8_gemm_dequant with a caller workspace",
                          need, bi8::kScratchBytes);
+    // The array is offered to the dispatcher at its full size.  That is safe because every kernel that takes scratch
+    // checks the size it is given against its own plan before using it: gemm_skinny_applicable() compares
+    // workspace_bytes with gemm_skinny_workspace_bytes() and declines when the array is too small (the general kernel
+    // then runs, whose plan was checked above), and launch_gemm_tc() runs unsplit unless workspace_bytes covers its plan.
     void* scratch = nullptr;
     size_t given = 0;
     if (bi8_gemm_workspace_bytes(M, N, K, block) > 0) {

@@ -652,11 +652,9 @@ int colwise_vec(const T* x, int64_t ldx, int8_t* q, float* s, int64_t R, int64_t
     const int64_t ctiles = (C + TC - 1) / TC, rtiles = (R + TR - 1) / TR;
     if (ctiles * rtiles >= (1ll << 31)) return fail(BI8_ERR_SHAPE, "quantize_colwise: grid too large");
     const size_t smem = (size_t)TR * (TC + 2) * 2;
-    static bool attr_done = false;          // per instantiation; idempotent
-    if (!attr_done) {
-        BI8_CUDA_TRY(cudaFuncSetAttribute(quantize_colwise_vec_kernel<T, B>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_done = true;
-    }
+    static SmemOptIn opt_in;                // per kernel instance; set once per device
+    const int rc = opt_in.ensure(quantize_colwise_vec_kernel<T, B>, smem);
+    if (rc != BI8_OK) return rc;
     quantize_colwise_vec_kernel<T, B><<<(unsigned)(ctiles * rtiles), kThreads, smem, st>>>(x, ldx, q, s, (int)R, (int)C, (int)ctiles);
     BI8_CUDA_TRY(cudaGetLastError());
     return BI8_OK;
@@ -677,8 +675,11 @@ int quantize_colwise_t(const T* x, int64_t ldx, int8_t* q, float* s, int64_t R, 
         const int64_t col_tiles = (C + kThreads - 1) / kThreads;
         const size_t smem = (size_t)kThreads * (block + 4);
         if (nb * col_tiles < (1ll << 31)) {
-            if (smem > 48 * 1024)
-                BI8_CUDA_TRY(cudaFuncSetAttribute(quantize_colwise_ragged_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            if (smem > 48 * 1024) {
+                static SmemOptIn opt_in;
+                const int rc = opt_in.ensure(quantize_colwise_ragged_kernel<T>, smem);
+                if (rc != BI8_OK) return rc;
+            }
             quantize_colwise_ragged_kernel<T><<<(unsigned)(nb * col_tiles), kThreads, smem, st>>>(x, ldx, q, s, R, C, block, col_tiles);
             BI8_CUDA_TRY(cudaGetLastError());
             return BI8_OK;

@@ -72,6 +72,81 @@ inline int make_scale_map(CUtensorMap* map, const float* ptr, int64_t nb, int64_
     return BI8_OK;
 }
 
+// ---- tensor-map cache ---------------------------------------------------------------------------------
+// Encoding a tensor map is a driver call of a few microseconds; a layer calls the GEMM with the same weight and scale
+// tensors every step.  A map depends only on (device, base address, extents, pitch, box), so encoded maps are kept in
+// a small table guarded by a mutex and looked up by those values (a stale entry for a freed and re-used address is
+// still a correct description of that address).
+struct MapKey {
+    int dev, kind;            // kind 0: int8 operand, 1: fp32 scales
+    const void* ptr;
+    int64_t rows, cols, ld;
+    int box_rows, box_cols;
+    bool operator==(const MapKey& o) const {
+        return dev == o.dev && kind == o.kind && ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld &&
+               box_rows == o.box_rows && box_cols == o.box_cols;
+    }
+};
+
+struct MapCache {
+    static constexpr int kSlots = 256, kWays = 4;
+    struct Entry {
+        MapKey key;
+        CUtensorMap map;
+        bool used;
+    };
+    Entry table[kSlots];
+    unsigned hand[kSlots / kWays];
+    std::mutex mu;
+
+    static int set_of(const MapKey& key) {
+        uint64_t h = reinterpret_cast<uintptr_t>(key.ptr) * 0x9E3779B97F4A7C15ull;
+        h ^= (uint64_t)key.rows * 0xC2B2AE3D27D4EB4Full + (uint64_t)key.cols * 0x165667B19E3779F9ull + (uint64_t)key.ld * 31u +
+             (uint64_t)(key.box_rows * 131 + key.box_cols * 7 + key.kind * 3 + key.dev);
+        return (int)((h >> 33) % (kSlots / kWays));
+    }
+    bool find(const MapKey& key, CUtensorMap* out) {
+        const int set = set_of(key);
+        std::lock_guard<std::mutex> lock(mu);
+        for (int w = 0; w < kWays; ++w) {
+            const Entry& e = table[set * kWays + w];
+            if (e.used && e.key == key) {
+                *out = e.map;
+                return true;
+            }
+        }
+        return false;
+    }
+    void put(const MapKey& key, const CUtensorMap& map) {
+        const int set = set_of(key);
+        std::lock_guard<std::mutex> lock(mu);
+        Entry& e = table[set * kWays + (int)(hand[set]++ % kWays)];
+        e.key = key;
+        e.map = map;
+        e.used = true;
+    }
+};
+inline MapCache& map_cache() {
+    static MapCache c{};
+    return c;
+}
+
+inline int cached_operand_map(CUtensorMap* map, int dev, const int8_t* ptr, int64_t rows, int64_t K, int64_t ld, int box_rows) {
+    const MapKey key{dev, 0, ptr, rows, K, ld, box_rows, kBK};
+    if (map_cache().find(key, map)) return BI8_OK;
+    const int rc = make_operand_map(map, ptr, rows, K, ld, box_rows);
+    if (rc == BI8_OK) map_cache().put(key, *map);
+    return rc;
+}
+
+inline int cached_scale_map(CUtensorMap* map, int dev, const float* ptr, int64_t nb, int64_t cols, int box_cols, int box_blocks) {
+    const MapKey key{dev, 1, ptr, nb, cols, cols, box_blocks, box_cols};
+    if (map_cache().find(key, map)) return BI8_OK;
+    const int rc = make_scale_map(map, ptr, nb, cols, box_cols, box_blocks);
+    if (rc == BI8_OK) map_cache().put(key, *map);
+    return rc;
+}
+
 struct DeviceInfo {
     int sms = 0;
     bool ok = false;

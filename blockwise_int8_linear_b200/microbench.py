@@ -6,7 +6,7 @@
     python -m blockwise_int8_linear_b200.microbench gemm 4096 4096 11008          # M K N, int8 operands given
     python -m blockwise_int8_linear_b200.microbench gemm 16 4096 4096 --block 64
 
-Also the command the profiler captures in profiles/ were taken with (one kernel, a few launches).
+One kernel and a few launches per invocation, so the command is also suitable for a profiler capture.
 """
 from __future__ import annotations
 

@@ -70,22 +70,9 @@ class GPT2(nn.Module):
         return self.lm_head(self.ln_f(x))
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--seq", type=int, default=1024)
-    ap.add_argument("--layers", type=int, default=12)
-    ap.add_argument("--block", type=int, default=64)
-    ap.add_argument("--dense", action="store_true", help="keep nn.Linear (bf16 cuBLAS) for comparison")
-    a = ap.parse_args()
-    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
-    local = int(os.environ.get("LOCAL_RANK", 0))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+def run(a, rank, world, local, dev):
+    """Trains the model described by `a` (fields as the command line options below) for a.warmup + a.steps steps on this
+    rank and returns the measurements.  The process group, if any, is the caller's."""
     cfg.GROUP_SIZE, cfg.INPUT_OUTPUT_TORCH_TYPE = a.block, torch.bfloat16
     torch.manual_seed(0)
     model = GPT2(layers=a.layers, seq=a.seq).to(dev).to(torch.bfloat16)
@@ -118,13 +105,38 @@ def main():
     if world > 1:
         dist.barrier()
     dt = time.perf_counter() - t0
+    return {
+        "model": f"gpt2-small-arch {a.layers} layers, seq {a.seq}, {'nn.Linear bf16' if a.dense else f'BlockInt8Linear block {a.block} fwd+bwd'}",
+        "n_gpus": world, "batch_per_gpu": a.batch, "steps": a.steps,
+        "tokens_per_s": world * a.batch * a.seq * a.steps / dt, "ms_per_step": 1e3 * dt / a.steps,
+        "loss_first": float(losses[0]), "loss_last": float(losses[-1]),
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--seq", type=int, default=1024)
+    ap.add_argument("--layers", type=int, default=12)
+    ap.add_argument("--block", type=int, default=64)
+    ap.add_argument("--dense", action="store_true", help="keep nn.Linear (bf16 cuBLAS) for comparison")
+    ap.add_argument("--out", default=None, help="also append the JSON line to this file")
+    a = ap.parse_args()
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    res = run(a, rank, world, local, dev)
     if rank == 0:
-        print(json.dumps({
-            "model": f"gpt2-small-arch {a.layers} layers, seq {a.seq}, {'nn.Linear bf16' if a.dense else f'BlockInt8Linear block {a.block} fwd+bwd'}",
-            "n_gpus": world, "batch_per_gpu": a.batch, "steps": a.steps,
-            "tokens_per_s": world * a.batch * a.seq * a.steps / dt, "ms_per_step": 1e3 * dt / a.steps,
-            "loss_first": float(losses[0]), "loss_last": float(losses[-1]),
-        }))
+        line = json.dumps(res)
+        print(line)
+        if a.out:
+            with open(a.out, "a") as f:
+                f.write(line + "\n")
     if world > 1:
         dist.destroy_process_group()
 

@@ -53,9 +53,9 @@ class Int8Linear(nn.Module):
     GEMM for them; each part keeps its own seed, so the model is the same function as with separate layers), local output.
     mode 'row': columns [lo,hi), fp32 partial output summed over the group."""
 
-    def __init__(self, in_f, out_fs, seeds, dev, mode, rank, world, block):
+    def __init__(self, in_f, out_fs, seeds, dev, mode, rank, world, block, ops=None):
         super().__init__()
-        self.mode, self.world = mode, world
+        self.mode, self.world, self.ops = mode, world, ops
         if mode == "col":
             parts = []
             for out_f, seed in zip(out_fs, seeds):
@@ -69,21 +69,33 @@ class Int8Linear(nn.Module):
             w = seeded_weight(out_fs[0], in_f, seeds[0], dev, cols=(lo, hi))
             self.bounds = (lo, hi)
             self.widths = [w.shape[0]]
+        if ops is not None:
+            # stand-in functional ops (the host-side sharding logic can then run on CPU ranks): same two calls as
+            # BlockInt8Linear.infer on the int8 weights
+            self.lin = None
+            self.W_int8, self.state_W = ops.quantize_block_rowwise(w)
+            return
         self.lin = BlockInt8Linear(w.shape[1], w.shape[0], bias=False, device=dev, dtype=torch.bfloat16)
         self.lin.weight.data = w
         self.lin.eval()
-        self.lin.prepare_for_eval()
-        self.lin.weight.data = torch.empty(0, device=dev, dtype=torch.bfloat16)      # keep only the int8 copy resident
+        self.lin.prepare_for_eval(drop_weight=True)                                  # keep only the int8 copy resident
+
+    def _infer(self, x):
+        if self.lin is not None:
+            return self.lin.infer(x)
+        X = x.reshape(-1, x.size(-1))
+        xq, sx = self.ops.quantize_block_rowwise(X)
+        return self.ops.int8_matmul_block64_rowwise_dequantize(xq, self.W_int8.t(), sx, self.state_W, None).view(*x.size()[:-1], -1)
 
     def partial(self, x):
         """This rank's contribution: the finished result for a column-parallel layer (or one rank), an fp32 partial sum for
         a row-parallel one (to be summed over the group by the caller)."""
         if self.mode == "col" or self.world == 1:
-            return self.lin.infer(x)
+            return self._infer(x)
         prev = cfg.INPUT_OUTPUT_TORCH_TYPE
         cfg.INPUT_OUTPUT_TORCH_TYPE = torch.float32
         try:
-            return self.lin.infer(x)
+            return self._infer(x)
         finally:
             cfg.INPUT_OUTPUT_TORCH_TYPE = prev
 
@@ -113,10 +125,10 @@ def rope(x, cis):
 
 
 class Layer(nn.Module):
-    def __init__(self, i, a, dev, rank, world):
+    def __init__(self, i, a, dev, rank, world, ops=None):
         super().__init__()
         d, f, blk = a.hidden, a.ffn, a.block
-        mk = lambda in_f, out_fs, seeds, mode: Int8Linear(in_f, out_fs, [1000 * i + s for s in seeds], dev, mode, rank, world, blk)
+        mk = lambda in_f, out_fs, seeds, mode: Int8Linear(in_f, out_fs, [1000 * i + s for s in seeds], dev, mode, rank, world, blk, ops)
         self.qkv = mk(d, (d, d, d), (1, 2, 3), "col")
         self.o = mk(d, (d,), (4,), "row")
         self.gate_up = mk(d, (f, f), (5, 6), "col")
@@ -168,12 +180,14 @@ def group_sum(part, dtype, world):
 
 
 class Llama(nn.Module):
-    def __init__(self, a, dev, rank, world):
+    def __init__(self, a, dev, rank, world, ops=None):
+        """`ops`: optional namespace with quantize_block_rowwise / int8_matmul_block64_rowwise_dequantize that replaces the
+        CUDA-backed functions (used to exercise the sharding on CPU ranks)."""
         super().__init__()
         g = torch.Generator(device=dev).manual_seed(7)
         self.emb = (torch.randn((a.vocab, a.hidden), device=dev, generator=g) * 0.02).to(torch.bfloat16)
-        self.layers = nn.ModuleList(Layer(i, a, dev, rank, world) for i in range(a.layers))
-        self.head = Int8Linear(a.hidden, (a.vocab,), (99,), dev, "col", rank, world, a.block)
+        self.layers = nn.ModuleList(Layer(i, a, dev, rank, world, ops) for i in range(a.layers))
+        self.head = Int8Linear(a.hidden, (a.vocab,), (99,), dev, "col", rank, world, a.block, ops)
         self.world, self.vocab, self.block = world, a.vocab, a.block
         self.cis = rope_table(a.prompt + a.decode, a.head_dim, dev)
         self.positions = torch.arange(a.prompt + a.decode, device=dev)
@@ -260,26 +274,10 @@ class Llama(nn.Module):
         return pieces
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--layers", type=int, default=32)
-    ap.add_argument("--hidden", type=int, default=4096)
-    ap.add_argument("--heads", type=int, default=32)
-    ap.add_argument("--ffn", type=int, default=11008)
-    ap.add_argument("--vocab", type=int, default=32000)
-    ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--prompt", type=int, default=512)
-    ap.add_argument("--decode", type=int, default=128)
-    ap.add_argument("--block", type=int, default=64)
-    ap.add_argument("--eager", action="store_true", help="do not capture the decode step in a CUDA graph")
-    a = ap.parse_args()
-    a.head_dim = a.hidden // a.heads
-    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
-    local = int(os.environ.get("LOCAL_RANK", 0))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+def run(a, rank, world, dev, eager=False):
+    """Builds the model described by `a` (fields as the command line options below) on this rank, runs the prompt and
+    the greedy decode, and returns the measurements and the generated tokens.  The process group, if any, is the
+    caller's."""
     assert a.heads % world == 0, "heads must divide over the ranks"
     cfg.GROUP_SIZE, cfg.INPUT_OUTPUT_TORCH_TYPE = a.block, torch.bfloat16
     model = Llama(a, dev, rank, world)
@@ -307,7 +305,7 @@ def main():
         pos_dev.add_(1)
 
     graph, pieces = None, None
-    if not a.eager:
+    if not eager:
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -324,7 +322,7 @@ def main():
             # Tensor parallel: NCCL stays outside the graphs.  The step is cut at its collectives (two sums per layer, one
             # gather of the logits); every communication-free piece is captured in a graph of its own (one shared memory
             # pool, so a piece reads the tensors the piece before it wrote) and the collectives are issued between the
-            # replays.  (Capturing the whole step with the collectives inside did not complete on this system.)
+            # replays.
             pieces, pool = [], None
             for compute, bind in model.decode_pieces(tok, pos_dev, max_len):
                 g = torch.cuda.CUDAGraph()
@@ -353,15 +351,46 @@ def main():
         out.append(tok.clone())
     torch.cuda.synchronize()
     t_decode = time.perf_counter() - t0
+    toks = torch.cat(out, dim=1)
+    return {
+        "model": f"llama-arch {a.layers}x{a.hidden} ffn {a.ffn} vocab {a.vocab}, random init N(0,0.02), BlockInt8Linear block {a.block}",
+        "n_gpus": world, "batch": a.batch, "prompt": a.prompt, "decode": a.decode,
+        "prefill_tokens_per_s": a.batch * a.prompt / t_prefill, "prefill_s": t_prefill, "first_prefill_s": t_first,
+        "decode_tokens_per_s": a.batch * (a.decode - 1) / t_decode, "decode_ms_per_step": 1e3 * t_decode / max(1, a.decode - 1),
+        "decode_mode": "eager" if eager else ("cuda graph" if world == 1 else "cuda graphs between the collectives"),
+        "first_tokens": toks[0, :8].tolist(), "tokens": toks.tolist(),
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--ffn", type=int, default=11008)
+    ap.add_argument("--vocab", type=int, default=32000)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--prompt", type=int, default=512)
+    ap.add_argument("--decode", type=int, default=128)
+    ap.add_argument("--block", type=int, default=64)
+    ap.add_argument("--eager", action="store_true", help="do not capture the decode step in a CUDA graph")
+    ap.add_argument("--out", default=None, help="also append the JSON line to this file")
+    a = ap.parse_args()
+    a.head_dim = a.hidden // a.heads
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    res = run(a, rank, world, dev, eager=a.eager)
     if rank == 0:
-        toks = torch.cat(out, dim=1)
-        print(json.dumps({
-            "model": f"llama-arch {a.layers}x{a.hidden} ffn {a.ffn} vocab {a.vocab}, random init N(0,0.02), BlockInt8Linear block {a.block}",
-            "n_gpus": world, "batch": a.batch, "prompt": a.prompt, "decode": a.decode,
-            "prefill_tokens_per_s": a.batch * a.prompt / t_prefill, "prefill_s": t_prefill, "first_prefill_s": t_first,
-            "decode_tokens_per_s": a.batch * (a.decode - 1) / t_decode, "decode_ms_per_step": 1e3 * t_decode / (a.decode - 1), "decode_mode": "eager" if a.eager else ("cuda graph" if world == 1 else "cuda graphs between the collectives"),
-            "first_tokens": toks[0, :8].tolist(),
-        }))
+        res.pop("tokens")
+        line = json.dumps(res)
+        print(line)
+        if a.out:
+            with open(a.out, "a") as f:
+                f.write(line + "\n")
     if world > 1:
         dist.destroy_process_group()
 

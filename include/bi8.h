@@ -142,11 +142,21 @@ BI8_API int bi8_gemm_dequant_fused_quant(const void* x, int x_dtype, int64_t ldx
                                  const int8_t* Wq, int64_t ldw, const float* sW, const void* bias, int bias_dtype,
                                  void* C, int64_t ldc, int out_dtype, int64_t M, int64_t N, int64_t K, int block,
                                  void* workspace, size_t workspace_bytes, int flags, void* stream);
-/* The same entry point under its earlier name. */
-BI8_API int bi8_linear_forward(const void* x, int x_dtype, int64_t ldx, int8_t* xq, float* sx,
-                       const int8_t* Wq, int64_t ldw, const float* sW, const void* bias, int bias_dtype,
-                       void* C, int64_t ldc, int out_dtype, int64_t M, int64_t N, int64_t K, int block,
-                       void* workspace, size_t workspace_bytes, int flags, void* stream);
+/* Capture sequence number of `stream` if it is being captured into a CUDA graph, 0 otherwise (no counterpart in the
+ * reference).  A host layer that caches workspaces uses it to give every captured graph a scratch buffer of its own:
+ * an address baked into a graph must not be shared with another graph that may be replayed on a different stream. */
+BI8_API int bi8_stream_capture_id(void* stream, unsigned long long* id);
+
+/* Diagnostic twin of bi8_gemm_dequant (no counterpart in the reference) that exercises the bounded waits of the general
+ * tensor-core kernel without hanging anything.  The kernel's mbarrier waits give up after about wait_limit_us
+ * microseconds (0 = the default of about two seconds), and the producer warp of every CTA leaves out the operand copies
+ * of K stage skip_stage of its first tile (-1 = none), so the MMA warp's wait for that stage runs out.  Every warp then
+ * leaves its loop, the CTA frees its tensor memory and the kernel returns normally; C is unspecified.  Afterwards
+ * bi8_device_status() returns BI8_ERR_TIMEOUT with detail 2 (the wait for operand tiles) and clears the status word.
+ * Needs a shape the tensor-core kernel takes (16-byte aligned operand rows, block 32/64/128). */
+BI8_API int bi8_gemm_wait_selftest(const int8_t* A, int64_t lda, const int8_t* Bt, int64_t ldb,
+                           const float* sA, const float* sB, void* C, int64_t ldc, int out_dtype,
+                           int64_t M, int64_t N, int64_t K, int block, unsigned wait_limit_us, int skip_stage, void* stream);
 
 /* Back-to-back tcgen05.mma kind::i8 issue rate of the current device: runs `iters` 128x256x32 MMAs per SM
  * with no loads or epilogue and returns the elapsed milliseconds in *ms (synchronises).  Used by the

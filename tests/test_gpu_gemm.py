@@ -207,14 +207,18 @@ def test_llama_projection_shapes(kn, m):
     assert_clean_device()
 
 
-def test_largest_projection_shape_properties():
-    """M = 8192, K = 4096, N = 11008: the oracle is evaluated on a sample of rows; the rest is covered by a
-    size-independent property (row blocks of the same input give the same output rows)."""
+@pytest.mark.parametrize("kn", [(4096, 11008), (4096, 4096), (11008, 4096)])
+def test_largest_projection_shape_properties(kn):
+    """M = 8192 on each of the three projection shapes: the oracle is evaluated on a sample of rows; the rest is covered
+    by a size-independent property (row blocks of the same input give the same output rows).  (11008, 4096) has 172
+    blocks per row, the longest fp32 accumulation chain of the configurations: the stated bound is checked there at
+    full M."""
     from triton_functions import quantize_block_rowwise
     set_config(64, torch.bfloat16)
-    m, k, n = 8192, 4096, 11008
-    x = O.synthetic((256, k), 3333, outlier_frac=0.0)
-    w = O.synthetic((n, k), 3334, std=0.02, outlier_frac=0.0)
+    m = 8192
+    k, n = kn
+    x = O.synthetic((256, k), 3333 + k % 13, outlier_frac=0.0)
+    w = O.synthetic((n, k), 3334 + n % 13, std=0.02, outlier_frac=0.0)
     wq, ws = O.quantize(w, 64)
     xg = x.to(DEV).repeat(m // 256, 1)                     # 32 copies of the same 256 rows
     xq_g, xs_g = quantize_block_rowwise(xg)
@@ -224,6 +228,56 @@ def test_largest_projection_shape_properties():
     _check_bf16(c[:256], xq, wq, xs, ws, 64)
     assert torch.equal(c.view(m // 256, 256, n), c[:256].unsqueeze(0).expand(m // 256, 256, n))
     assert_clean_device()
+
+
+@pytest.mark.parametrize("block", [32, 128])
+@pytest.mark.parametrize("kn", [(4096, 4096), (11008, 4096)])
+def test_llama_projection_shapes_other_blocks(kn, block):
+    """Blocks of 32 and 128 elements on projection shapes (M = 2048; the oracle on the first 128 rows)."""
+    from triton_functions import quantize_block_rowwise
+    k, n = kn
+    m = 2048
+    set_config(block, torch.bfloat16)
+    x = O.synthetic((m, k), 3500 + block, outlier_frac=0.0)
+    w = O.synthetic((n, k), 3600 + block, std=0.02, outlier_frac=0.0)
+    wq, ws = O.quantize(w, block)
+    xq_g, xs_g = quantize_block_rowwise(x.to(DEV))
+    xq, xs = O.quantize(x, block)
+    assert torch.equal(xq_g.cpu(), xq) and torch.equal(xs_g.cpu(), xs)
+    c = _gemm(xq, wq, xs, ws)
+    rows = slice(0, 128)
+    _check_bf16(c[rows], xq[rows], wq, xs[:, rows], ws, block)
+    assert_clean_device()
+    set_config(64)
+
+
+def test_bounded_wait_gives_up_cleanly():
+    """The general kernel's mbarrier waits are bounded.  bi8_gemm_wait_selftest makes one of them run out (the producer
+    leaves out the copies of one K stage, the limit is set to 200 us): the kernel must return by itself, the device
+    status must say BI8_ERR_TIMEOUT with the code of the wait for operand tiles, and the next ordinary GEMM must be
+    correct (the tensor memory was freed, nothing is left hanging)."""
+    import ctypes
+    from blockwise_int8_linear_b200 import _lib
+    L = _lib.lib()
+    set_config(64, torch.float32)
+    m, k, n = 256, 1024, 320
+    xq, xs, wq, ws = quantized_pair(m, k, n, 64, seed=4242)
+    a, bt, sa, sb = xq.to(DEV), wq.to(DEV), xs.to(DEV), ws.to(DEV)
+    c = torch.empty((m, n), dtype=torch.float32, device=DEV)
+    assert _lib.device_status() == 0
+    for skip in (0, 3):
+        rc = L.bi8_gemm_wait_selftest(_lib.ptr(a), k, _lib.ptr(bt), k, _lib.ptr(sa), _lib.ptr(sb), _lib.ptr(c), n, _lib.BI8_F32,
+                                      m, n, k, 64, 200, skip, _lib.stream_ptr())
+        _lib.check(rc, "bi8_gemm_wait_selftest")
+        torch.cuda.synchronize()                       # returns: the kernel left its loops by itself
+        detail = ctypes.c_int(0)
+        assert L.bi8_device_status(ctypes.byref(detail)) == -6      # BI8_ERR_TIMEOUT
+        assert detail.value == 2                                      # wait for the operand tiles of a stage
+        assert _lib.device_status() == 0                              # reading cleared the word
+        good = _gemm(xq, wq, xs, ws, flags=TC)
+        _check_fp32(good, xq, wq, xs, ws, 64)
+    assert_clean_device()
+    set_config(64)
 
 
 def test_unaligned_long_contraction_is_repitched_onto_the_tensor_cores():

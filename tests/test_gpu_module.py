@@ -152,3 +152,88 @@ def test_fast_matmul_helpers():
     ref = O.linear_forward(a, b, None, 64)
     _assert_bf16_close(fast_matmulT(a.to(DEV), b.to(DEV)).cpu(), ref)
     _assert_bf16_close(fast_matmul(a.to(DEV), b.t().contiguous().to(DEV)).cpu(), ref)
+
+
+def test_int8_resident_weight_and_state_dict_round_trip():
+    """prepare_for_eval(drop_weight=True): inference runs from the int8 buffers alone, and the state dict written
+    afterwards (empty `weight`, `W_int8`, `state_W`) loads into a fresh module that gives the same outputs."""
+    import io
+    from block_linear import BlockInt8Linear
+    set_config(64, torch.bfloat16)
+    torch.manual_seed(3)
+    lin = BlockInt8Linear(512, 320, bias=True, device=DEV, dtype=torch.bfloat16).eval()
+    x = O.synthetic((130, 512), 44).to(DEV)
+    with torch.no_grad():
+        y = lin(x)
+    full_bytes = lin.weight.numel() * 2
+    lin.prepare_for_eval(drop_weight=True)
+    assert lin.weight.numel() == 0 and full_bytes == 512 * 320 * 2
+    with torch.no_grad():
+        assert torch.equal(lin(x), y)
+    buf = io.BytesIO()
+    torch.save(lin.state_dict(), buf)
+    buf.seek(0)
+    sd = torch.load(buf)
+    assert set(sd) == {"weight", "bias", "W_int8", "state_W"} and sd["weight"].numel() == 0
+    fresh = BlockInt8Linear(512, 320, bias=True, device=DEV, dtype=torch.bfloat16).eval()
+    fresh.load_state_dict(sd)
+    assert fresh.weight.numel() == 0
+    with torch.no_grad():
+        assert torch.equal(fresh(x), y)
+    fresh.train()
+    with pytest.raises(RuntimeError):
+        fresh(x)
+    # the knob does the same on the first eval forward
+    import block_linear_config as cfg
+    cfg.DROP_WEIGHT_IN_EVAL = True
+    try:
+        torch.manual_seed(3)
+        lazy = BlockInt8Linear(512, 320, bias=True, device=DEV, dtype=torch.bfloat16).eval()
+        with torch.no_grad():
+            assert torch.equal(lazy(x), y)
+        assert lazy.weight.numel() == 0
+    finally:
+        cfg.DROP_WEIGHT_IN_EVAL = False
+
+
+def test_cached_quantized_weights_in_training():
+    """CACHE_QUANTIZED_WEIGHTS: micro-steps between weight updates reuse both int8 copies of the weight; results are
+    bit-identical to the uncached path, and an in-place update of the weight invalidates the copies."""
+    import block_linear_config as cfg
+    from block_linear import BlockInt8Linear
+    set_config(64, torch.bfloat16)
+    torch.manual_seed(4)
+    lin = BlockInt8Linear(256, 192, bias=True, device=DEV, dtype=torch.bfloat16).train()
+    xs = [O.synthetic((96, 256), 50 + i).to(DEV) for i in range(3)]
+    gys = [O.synthetic((96, 192), 60 + i, outlier_frac=0).to(DEV) for i in range(3)]
+
+    def micro_steps():
+        outs = []
+        for x, gy in zip(xs, gys):
+            x = x.clone().requires_grad_(True)
+            lin.weight.grad = None
+            y = lin(x)
+            y.backward(gy)
+            outs.append((y.detach().clone(), x.grad.clone(), lin.weight.grad.clone()))
+        return outs
+
+    ref = micro_steps()
+    cfg.CACHE_QUANTIZED_WEIGHTS = True
+    try:
+        got = micro_steps()
+        cache = lin.weight._bi8_quantized
+        assert "row" in cache and "col" in cache
+        for a, b in zip(ref, got):
+            assert all(torch.equal(u, v) for u, v in zip(a, b))
+        with torch.no_grad():
+            lin.weight.mul_(1.5)                      # what an optimizer step does: an in-place update
+        got2 = micro_steps()
+        assert lin.weight._bi8_quantized is not cache
+        cfg.CACHE_QUANTIZED_WEIGHTS = False
+        ref2 = micro_steps()
+        for a, b in zip(ref2, got2):
+            assert all(torch.equal(u, v) for u, v in zip(a, b))
+        assert not torch.equal(ref[0][0], ref2[0][0])
+    finally:
+        cfg.CACHE_QUANTIZED_WEIGHTS = False
+    assert_clean_device()

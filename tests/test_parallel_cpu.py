@@ -97,3 +97,63 @@ def test_sharded_layers_world2():
         p.join(timeout=300)
     assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
     assert dict(results) == {0: "ok", 1: "ok"}
+
+
+def _llama_worker(rank, world, port, results):
+    """The Llama-architecture driver of examples/ at toy size on CPU ranks: its tensor-parallel result against its own
+    one-rank result, with the CPU oracle standing in for the CUDA kernels (the driver takes an `ops` namespace)."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import argparse
+        import importlib.util
+        import block_linear_config as cfg
+        root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+        spec = importlib.util.spec_from_file_location("llama_infer", os.path.join(root, "examples", "llama_infer.py"))
+        L = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(L)
+        cfg.GROUP_SIZE, cfg.INPUT_OUTPUT_TORCH_TYPE = BLOCK, torch.bfloat16
+        ops = _oracle_ops()
+        # FFN 704 = 11 blocks: the split over 2 ranks is uneven (6 + 5 blocks); vocab 520: 5 + 4 blocks, ragged tail
+        a = argparse.Namespace(layers=2, hidden=256, heads=4, head_dim=64, ffn=704, vocab=520, batch=2, prompt=12, decode=2, block=BLOCK)
+        cpu = torch.device("cpu")
+        one = L.Llama(a, cpu, 0, 1, ops=ops)
+        two = L.Llama(a, cpu, rank, world, ops=ops)
+        ids = torch.randint(0, a.vocab, (a.batch, a.prompt), generator=torch.Generator().manual_seed(4000))
+        max_len = a.prompt + a.decode
+        ref = one(ids, 0, max_len)
+        got = two(ids, 0, max_len)
+        assert tuple(got.shape) == tuple(ref.shape) == (a.batch, 1, a.vocab)
+        d = (got.float() - ref.float()).abs().max().item()
+        assert d <= 2.0 ** -6 * ref.float().abs().max().item(), d
+        assert (got == ref).float().mean().item() > 0.5
+        # column-parallel layers: this rank's columns are bit-identical to the same columns of the unsharded layer
+        x = torch.randn((3, 5, a.hidden), generator=torch.Generator().manual_seed(9)).to(torch.bfloat16)
+        full = one.layers[0].gate_up(x)
+        mine = two.layers[0].gate_up(x)
+        lo, hi = P.block_aligned_bounds(a.ffn, world, BLOCK)[rank]
+        assert torch.equal(mine, torch.cat([full[..., lo:hi], full[..., a.ffn + lo:a.ffn + hi]], dim=-1))
+        # row-parallel layer: the sum of the ranks' fp32 partial results against the unsharded layer
+        h = torch.randn((3, 5, a.ffn), generator=torch.Generator().manual_seed(10)).to(torch.bfloat16)
+        y_full = one.layers[0].down(h)
+        y_tp = two.layers[0].down(h[..., lo:hi].contiguous())
+        d = (y_tp.float() - y_full.float()).abs().max().item()
+        assert d <= 2.0 ** -7 * y_full.float().abs().max().item(), d
+        results[rank] = "ok"
+    finally:
+        dist.destroy_process_group()
+
+
+def test_llama_driver_tensor_parallel_world2_equals_one_rank():
+    world = 2
+    ctx = mp.get_context("spawn")
+    mgr = ctx.Manager()
+    results = mgr.dict()
+    port = 31500 + os.getpid() % 2000
+    procs = [ctx.Process(target=_llama_worker, args=(r, world, port, results)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=600)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    assert dict(results) == {0: "ok", 1: "ok"}

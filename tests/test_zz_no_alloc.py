@@ -69,6 +69,25 @@ def test_static_scratch_entry_point_matches_workspace_entry_point():
     assert lib.device_status() == 0
 
 
+def test_static_scratch_too_small_for_the_decode_kernel_takes_the_general_kernel():
+    """33 <= M <= 64: the decode kernel's plan does not fit the built-in array, so the dispatcher declines it and the
+    general kernel runs with the array as its split-K scratch: same result as bi8_gemm_dequant forced onto that kernel."""
+    lib, L = _lib()
+    m, k, n = 48, 4096, 4096
+    a, bt, sa, sb, bias = _operands(m, k, n, seed=11)
+    need = L.bi8_gemm_workspace_bytes(m, n, k, 64)
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    c = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    p = lib.ptr
+    rc = L.bi8_gemm_dequant(p(a), k, p(bt), k, p(sa), p(sb), p(bias), 0, p(c), n, 0, m, n, k, 64, p(ws), ws.numel(),
+                            lib.GEMM_FORCE_TC, lib.stream_ptr())
+    lib.check(rc, "bi8_gemm_dequant")
+    got = _run(L, lib, "static", a, bt, sa, sb, bias, None)
+    torch.cuda.synchronize()
+    assert torch.equal(got, c)
+    assert lib.device_status() == 0
+
+
 def test_static_scratch_rejects_oversized_plans():
     lib, L = _lib()
     m, k, n = 128, 4096, 11008         # on a 148-SM device the plan wants 2 x 128 x 11008 floats: more than 8 MiB

@@ -18,11 +18,9 @@
 //               three s32 accumulators in tensor memory, then a commit hands that accumulator to the promotion warps.
 //   warps 2-3   spare (they only take part in set-up and teardown; see the register note below)
 //   warps 4..   promotion + epilogue, PW warps per tensor-memory lane quarter.  A warp owns 32 rows x BN/PW columns of
-//               the tile.  Per block it reads its part of the finished accumulator in two halves, re-seeds what it has
-//               read, folds the values into fp32 accumulators in registers and releases the accumulator; the first half
-//               of the NEXT block is already being read while the second half of the current one is folded, so a warp
-//               always has arithmetic to issue while its tensor-memory loads are in flight.  After the last block of a
-//               tile it casts, adds bias and stores.
+//               the tile.  Per block it reads its part of the finished accumulator in two halves (the second in flight
+//               while the first is folded), re-seeds what it has read, folds the values into fp32 accumulators in
+//               registers and releases the accumulator.  After the last block of a tile it casts, adds bias and stores.
 // The fold costs two FMAs per element and block (t = P*s_row, acc += s_col*t): 2*128*BN FMAs per block on 128 FMA lanes
 // is twice the time the MMAs of a 64-deep block need, so the FMA pipes, not the tensor pipe, bound this kernel; what
 // the code around the FMAs must do is stay out of their way (few instructions, no waiting that is not overlapped).
@@ -41,6 +39,7 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <type_traits>
 
 #ifndef BI8_TC_VARIANTS
 #define BI8_TC_VARIANTS 0
@@ -74,9 +73,6 @@ struct Cfg {
     static constexpr int COLS = BN / PW;                  // columns owned by one promotion thread: 80, 48, 40
     static constexpr int H0 = PW == 2 ? 40 : 24;          // the accumulator is read as columns [0, H0) and [H0, COLS)
     static constexpr int H1 = COLS - H0;                  // 40, 24, 16
-    // the first half of the next block is requested while the second half of the current one is folded; with 112
-    // registers (PW = 4) the two halves, 40 accumulators and the seed registers leave no room for that
-    static constexpr bool PREFETCH = PW != 4;
     static constexpr int EPI_WARPS = 4 * PW;
     static constexpr int THREADS = (kRoleWarps + EPI_WARPS) * 32;
     static constexpr int LAUNCH_REGS = PW == 2 ? 168 : PW == 3 ? 128 : 96;     // 65536 / THREADS, rounded down to a multiple of 8
@@ -127,14 +123,9 @@ struct Geo {
     static constexpr int FULL_AB = 0, EMPTY_AB = kStages, ACC_FULL = 2 * kStages, ACC_EMPTY = 2 * kStages + kAccBufs,
                          NBARS = 2 * kStages + 2 * kAccBufs;
     static constexpr uint32_t misc_off = bar_off + NBARS * 8;   // tmem holder (4 B) + abort flag (4 B) + never-raised flag (4 B)
-    static constexpr uint32_t prof_off = misc_off + 16;         // diagnostic build: cycle counters [20 warps][12]
-    static constexpr uint32_t total = prof_off + 20 * 12 * 4;
+    static constexpr uint32_t total = misc_off + 16;
     static_assert((SC_FLOATS * 4) % 128 == 0 && (SB_OFF * 4) % 128 == 0 && C::scale_off % 1024 == 0, "TMA destinations of the scale boxes are 128-byte aligned");
 };
-
-#if BI8_TC_VARIANTS
-__device__ unsigned int g_prof[160 * 20 * 12];
-#endif
 
 // Work item -> tile and K-stage range.  Items of one split are consecutive, so CTAs that run together work on
 // different tiles of the same K range.
@@ -177,6 +168,18 @@ __device__ __forceinline__ void tmem_load_cols(uint32_t taddr, uint32_t (&S)[NC]
     }
 }
 
+// Blocks go round the kAccBufs = 3 accumulators and every stage has BPS blocks, so block `blk` of the stage at position
+// `rot` in a cycle of three stages is block rot*BPS + blk of that cycle: it uses accumulator (rot*BPS + blk) % 3, for the
+// ((rot*BPS + blk) / 3)-th time in the cycle.  A cycle uses every accumulator BPS times; with BPS even the barrier
+// parities therefore repeat from cycle to cycle, with BPS odd they alternate (the callers keep that bit).
+template <int BPS>
+struct RotInfo {
+    __host__ __device__ static constexpr int buf(int rot, int blk) { return (rot * BPS + blk) % kAccBufs; }
+    __host__ __device__ static constexpr uint32_t par(int rot, int blk) { return (uint32_t)(((rot * BPS + blk) / kAccBufs) & 1); }
+};
+
+__host__ __device__ constexpr int blk_next_rot(int rot) { return rot == 2 ? 0 : rot + 1; }
+
 // A value the compiler must treat as unknown from here on.  Loop-invariant addresses of the promotion loop go through
 // this: left alone, the compiler recomputes them (from the warp index, the thread index, the shared-memory base ...)
 // inside every block instead of keeping a register, which costs more instructions than the fold itself has to spare.
@@ -214,8 +217,8 @@ __device__ __forceinline__ void fold_columns(const uint32_t (&S)[NC], uint32_t s
     }
 }
 
-// VAR (development builds only): bit 0 = request the next block's first half early for every PW; bit 1 = first product
-// as scalar FMAs instead of packed ones; bit 4 = cycle counters.
+// VAR (development builds only): bit 0 = early request of the next block's first half; bit 1 = first product as scalar
+// FMAs instead of packed ones.
 template <int QB, int MODE, bool SEED, int PW, int VAR>
 __global__ void __launch_bounds__(Cfg<PW>::THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -223,7 +226,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     using C = Cfg<PW>;
     using G = Geo<QB, PW>;
     constexpr int BN = C::BN, COLS = C::COLS, H0 = C::H0, H1 = C::H1;
-    constexpr bool kPrefetch = Cfg<PW>::PREFETCH || (VAR & 1);
     constexpr bool kScales = (MODE == 0);           // the partial-sum dump uses no scales
     constexpr bool kPack1 = (VAR & 2) == 0;
     extern __shared__ __align__(1024) unsigned char smem_dyn[];
@@ -238,20 +240,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const uint32_t abort_flag = base + G::misc_off + 4;
     const uint32_t never_flag = base + G::misc_off + 8;
     auto bar = [&](int slot) -> uint32_t { return bars + 8u * (uint32_t)slot; };
-
-    // diagnostic (VAR bit 4): cycles between consecutive tick() calls of a warp, summed per call site in shared memory
-    uint32_t* prof = reinterpret_cast<uint32_t*>(base_ptr + G::prof_off);
-    uint32_t tprev = 0;
-    auto tick = [&](int slot) {
-        if (VAR & 16) {
-            const uint32_t now = (uint32_t)clock64();
-            if ((threadIdx.x & 31) == 0) atomicAdd(&prof[(threadIdx.x >> 5) * 12 + slot], now - tprev);
-            tprev = now;
-        }
-    };
-    if (VAR & 16) {
-        for (int i = threadIdx.x; i < 20 * 12; i += blockDim.x) prof[i] = 0;
-    }
 
     // the warp index through a shuffle: known to be the same in all lanes, so what is derived from it lives in uniform registers
     const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
@@ -287,7 +275,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
-    if (VAR & 16) tprev = (uint32_t)clock64();
 
     if (warp < kRoleWarps) {
         setmaxnreg_dec<C::ROLE_REGS>();
@@ -362,50 +349,57 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
         } else if (warp == 1) {
             // ---------------- MMA issuer ----------------
+            // Every stage has BPS blocks (blocks past the end of K multiply zero-filled operands) and the blocks go
+            // round the three accumulators, so which accumulator a block of a stage uses, and the parity of its barriers,
+            // depend only on the stage's position in a cycle of three stages: the stage body exists in three copies
+            // with those values as constants (RotInfo).
             constexpr uint32_t idesc = umma_idesc_i8(kBM, BN);
-            int stage = 0, accbuf = 0;
-            uint32_t phase = 0, accphase = 0;
+            int stage = 0, rot = 0;
+            uint32_t phase = 0, qpar = 0;
             bool ok = true;
+            auto issue_stage = [&](auto rot_tag, uint64_t adesc, uint64_t bdesc) {
+                constexpr int ROT = decltype(rot_tag)::value;
+#pragma unroll
+                for (int blk = 0; blk < G::BPS; ++blk) {
+                    using R = RotInfo<G::BPS>;
+                    const int buf = R::buf(ROT, blk);
+                    ok = warp_wait(bar(G::ACC_EMPTY + buf), qpar ^ R::par(ROT, blk), abort_flag, wait_limit_mma);
+                    if (!ok) {
+                        if (lane == 0) report_timeout(p.status, abort_flag, W_ACC_EMPTY);
+                        return;
+                    }
+                    tc_fence_after();
+                    if (lane == 0) {
+#pragma unroll
+                        for (int i = 0; i < G::MMAS; ++i) {
+                            const uint64_t koff = (uint64_t)((blk * G::MMAS + i) * 32 / 16);
+                            mma_i8(tmem_base + (uint32_t)(buf * BN), adesc + koff, bdesc + koff, idesc, (SEED || i > 0) ? 1u : 0u);
+                        }
+                        tc_commit(bar(G::ACC_FULL + buf));
+                    }
+                    __syncwarp();
+                }
+            };
             for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
                 int tile, split, ks0, ks1;
                 item_range(item, num_tiles, nks, p.stages_per_split, tile, split, ks0, ks1);
                 for (int ks = ks0; ks < ks1 && ok; ++ks) {
-                    tick(3);
                     ok = warp_wait(bar(G::FULL_AB + stage), phase, abort_flag, wait_limit_mma);
                     if (!ok) {
                         if (lane == 0) report_timeout(p.status, abort_flag, W_FULL_AB);
                         break;
                     }
-                    tick(0);
                     tc_fence_after();
                     const uint64_t adesc = umma_desc_k_sw128(base + C::a_off(stage));
                     const uint64_t bdesc = umma_desc_k_sw128(base + C::b_off(stage));
-#pragma unroll
-                    for (int blk = 0; blk < G::BPS; ++blk) {
-                        if (ks * G::BPS + blk >= p.nb) break;
-                        ok = warp_wait(bar(G::ACC_EMPTY + accbuf), accphase, abort_flag, wait_limit_mma);
-                        if (!ok) {
-                            if (lane == 0) report_timeout(p.status, abort_flag, W_ACC_EMPTY);
-                            break;
-                        }
-                        tick(1);
-                        tc_fence_after();
-                        if (lane == 0) {
-#pragma unroll
-                            for (int i = 0; i < G::MMAS; ++i) {
-                                const uint64_t koff = (uint64_t)((blk * G::MMAS + i) * 32 / 16);
-                                mma_i8(tmem_base + (uint32_t)(accbuf * BN), adesc + koff, bdesc + koff, idesc, (SEED || i > 0) ? 1u : 0u);
-                            }
-                            tc_commit(bar(G::ACC_FULL + accbuf));
-                        }
-                        __syncwarp();
-                        tick(2);
-                        if (++accbuf == kAccBufs) { accbuf = 0; accphase ^= 1u; }
-                    }
+                    if (rot == 0) issue_stage(std::integral_constant<int, 0>{}, adesc, bdesc);
+                    else if (rot == 1) issue_stage(std::integral_constant<int, 1>{}, adesc, bdesc);
+                    else issue_stage(std::integral_constant<int, 2>{}, adesc, bdesc);
                     if (!ok) break;
                     if (lane == 0) tc_commit(bar(G::EMPTY_AB + stage));
                     __syncwarp();
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                    if (++rot == 3) { rot = 0; qpar ^= (uint32_t)(G::BPS & 1); }
                 }
             }
         }
@@ -451,128 +445,132 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
         };
 
-        // blocks this CTA's promotion warps will see: the read of a block's first half is issued during the block before it
-        int blocks_left = 0;
+        int sstage = 0, rot = 0;
+        uint32_t qpar = 0;
+        uint32_t sc_off = 0;                      // byte offset of scale stage `sstage`
+        bool ok = true;
+        int fail_code = 0;
+
+        // the tile's COLS fp32 accumulators of this thread, kept as packed pairs for fma.rn.f32x2
+        uint64_t acc2[COLS / 2];
+        int m = 0, nbase = 0, ks = 0;
+
+        // stages this CTA's promotion warps will see (the read of a block's first half is requested during the block
+        // before it, so the last block must be known)
+        int stages_left = 0;
         for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
             int tile, split, ks0, ks1;
             item_range(item, num_tiles, nks, p.stages_per_split, tile, split, ks0, ks1);
-            const int jend = ks1 * G::BPS < p.nb ? ks1 * G::BPS : p.nb;
-            blocks_left += jend - ks0 * G::BPS;
+            stages_left += ks1 - ks0;
         }
-
-        int accbuf = 0, sstage = 0;
-        uint32_t accphase = 0;
-        uint32_t t_acc = t_lane;                  // this thread's part of accumulator `accbuf`
-        uint32_t sc_off = 0;                      // byte offset of scale stage `sstage`
-        bool ok = true;
+        // development variant (measured slower): request the next block's first half before releasing this one
+        constexpr bool kEarly = (MODE == 0) && (VAR & 1);
         uint32_t S0[H0], S1[H1];
-        if (MODE == 0 && kPrefetch && blocks_left > 0) {
+        if (kEarly && stages_left > 0) {
             ok = warp_wait(bar0 + 8u * (uint32_t)(G::ACC_FULL + 0), 0u, abort_flag, wait_limit);
-            if (!ok) {
-                if (lane == 0) report_timeout(p.status, abort_flag, W_ACC_FULL);
-            } else {
+            if (!ok) fail_code = W_ACC_FULL;
+            else {
                 tc_fence_after();
                 tmem_load_cols<H0>(t_lane, S0);
             }
         }
+
+        // One stage of the promotion: BPS blocks.  `rot_tag` is the stage's position in a cycle of three stages, which
+        // fixes the accumulator and the barrier parity of each of its blocks (RotInfo).
+        auto promote_stage = [&](auto rot_tag) {
+            constexpr int ROT = decltype(rot_tag)::value;
+            using R = RotInfo<G::BPS>;
+#pragma unroll
+            for (int blk = 0; blk < G::BPS; ++blk) {
+                const int buf = R::buf(ROT, blk);
+                const uint32_t t_acc = t_lane + (uint32_t)(buf * BN);
+                if (!kEarly) {
+                    ok = warp_wait(bar0 + 8u * (uint32_t)(G::ACC_FULL + buf), qpar ^ R::par(ROT, blk), abort_flag, wait_limit);
+                    if (!ok) {
+                        fail_code = W_ACC_FULL;
+                        return;
+                    }
+                    tc_fence_after();
+                }
+                if (MODE == 1) {
+                    const int j = ks * G::BPS + blk;
+#pragma unroll
+                    for (int c = 0; c < COLS / 8; ++c) {
+                        uint32_t pv[8];
+                        tmem_ld8(t_acc + (uint32_t)(c * 8), pv);
+                        tmem_wait_ld();
+                        reseed(t_acc, c * 8, 8);
+                        if (m < p.M && j < p.nb) {
+                            int32_t* dst = p.partials + ((int64_t)j * p.M + m) * p.N + nbase + c * 8;
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                if (nbase + c * 8 + i < p.N)
+                                    dst[i] = SEED ? (int32_t)(pv[i] - kSeedBits) : (int32_t)pv[i];
+                        }
+                    }
+                } else {
+                    if (!kEarly) tmem_load_cols<H0>(t_acc, S0);
+                    // the row's scale, while the read of the first half is in flight
+                    float sxd = __fmul_rn(lds_f32(sa_addr + sc_off + (uint32_t)(blk * kBM * 4)), div);
+                    float negc = 0.0f;
+                    if (SEED) {
+                        sxd = __uint_as_float((__float_as_uint(sxd) + 2u) & 0xFFFFFFFCu);   // 22 significant bits
+                        negc = -__fmul_rn(kSeedF, sxd);                                      // exact
+                    }
+                    const uint32_t sw = sw_addr + sc_off + (uint32_t)(blk * BN * 4);
+                    tmem_wait_ld();
+                    tmem_load_cols<H1>(t_acc + (uint32_t)H0, S1);    // second half, in flight during the fold of the first
+                    reseed(t_acc, 0, H0);
+                    fold_columns<SEED, kPack1, 0, H0, COLS>(S0, sw, sxd, negc, acc2);
+                    tmem_wait_ld();
+                    reseed(t_acc, H0, H1);
+                    fold_columns<SEED, kPack1, H0, H1, COLS>(S1, sw, sxd, negc, acc2);
+                    if (kEarly) {
+                        // The next block's accumulator (which block that is, of which tile, does not matter here) is
+                        // waited for and its first half requested now, so that the read is in flight during this
+                        // block's release sequence and the next block's set-up.
+                        constexpr int NROT = blk_next_rot(ROT);
+                        const bool last_of_stage = blk == G::BPS - 1;
+                        const int nbuf = last_of_stage ? R::buf(NROT, 0) : R::buf(ROT, blk + 1);
+                        const uint32_t npar = last_of_stage ? ((ROT == 2 ? (qpar ^ (uint32_t)(G::BPS & 1)) : qpar) ^ R::par(NROT, 0))
+                                                            : (qpar ^ R::par(ROT, blk + 1));
+                        if (!(last_of_stage && stages_left == 1)) {
+                            ok = warp_wait(bar0 + 8u * (uint32_t)(G::ACC_FULL + nbuf), npar, abort_flag, wait_limit);
+                            if (!ok) {
+                                fail_code = W_ACC_FULL;
+                                return;
+                            }
+                            tc_fence_after();
+                            tmem_load_cols<H0>(t_lane + (uint32_t)(nbuf * BN), S0);
+                        }
+                    }
+                }
+                if (SEED) tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (leader) mbar_arrive(bar0 + 8u * (uint32_t)(G::ACC_EMPTY + buf));
+            }
+            --stages_left;
+        };
+
         for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
             int tile, split, ks0, ks1, m0, n0;
             item_range(item, num_tiles, nks, p.stages_per_split, tile, split, ks0, ks1);
             tile_coords<BN>(tile, p.tiles_m, m0, n0);
-            tick(10);
-            const int m = m0 + row;
-            const int nbase = n0 + slice * COLS;
-            // COLS fp32 accumulators per thread, kept as packed pairs for fma.rn.f32x2
-            uint64_t acc2[COLS / 2];
+            m = m0 + row;
+            nbase = n0 + slice * COLS;
 #pragma unroll
             for (int i = 0; i < COLS / 2; ++i) acc2[i] = 0ull;
 
-            for (int ks = ks0; ks < ks1 && ok; ++ks) {
-                tick(0);
-#pragma unroll
-                for (int blk = 0; blk < G::BPS; ++blk) {
-                    const int j = ks * G::BPS + blk;
-                    if (j >= p.nb) break;
-                    if (MODE == 1) {
-                        ok = warp_wait(bar0 + 8u * (uint32_t)(G::ACC_FULL + accbuf), accphase, abort_flag, wait_limit);
-                        if (!ok) {
-                            if (lane == 0) report_timeout(p.status, abort_flag, W_ACC_FULL);
-                            break;
-                        }
-                        tc_fence_after();
-#pragma unroll
-                        for (int c = 0; c < COLS / 8; ++c) {
-                            uint32_t pv[8];
-                            tmem_ld8(t_acc + (uint32_t)(c * 8), pv);
-                            tmem_wait_ld();
-                            reseed(t_acc, c * 8, 8);
-                            if (m < p.M) {
-                                int32_t* dst = p.partials + ((int64_t)j * p.M + m) * p.N + nbase + c * 8;
-#pragma unroll
-                                for (int i = 0; i < 8; ++i)
-                                    if (nbase + c * 8 + i < p.N)
-                                        dst[i] = SEED ? (int32_t)(pv[i] - kSeedBits) : (int32_t)pv[i];
-                            }
-                        }
-                        if (SEED) tmem_wait_st();
-                    } else {
-                        if (!kPrefetch) {
-                            ok = warp_wait(bar0 + 8u * (uint32_t)(G::ACC_FULL + accbuf), accphase, abort_flag, wait_limit);
-                            if (!ok) {
-                                if (lane == 0) report_timeout(p.status, abort_flag, W_ACC_FULL);
-                                break;
-                            }
-                            tc_fence_after();
-                            tmem_load_cols<H0>(t_acc, S0);
-                        }
-                        // the row's scale, while the read of the first half is in flight
-                        float sxd = __fmul_rn(lds_f32(sa_addr + sc_off + (uint32_t)(blk * kBM * 4)), div);
-                        float negc = 0.0f;
-                        if (SEED) {
-                            sxd = __uint_as_float((__float_as_uint(sxd) + 2u) & 0xFFFFFFFCu);   // 22 significant bits
-                            negc = -__fmul_rn(kSeedF, sxd);                                      // exact
-                        }
-                        const uint32_t sw = sw_addr + sc_off + (uint32_t)(blk * BN * 4);
-                        tmem_wait_ld();                                  // first half of this block
-                        tick(1);
-                        tmem_load_cols<H1>(t_acc + (uint32_t)H0, S1);    // second half, in flight during the fold
-                        reseed(t_acc, 0, H0);
-                        fold_columns<SEED, kPack1, 0, H0, COLS>(S0, sw, sxd, negc, acc2);
-                        tmem_wait_ld();
-                        tick(2);
-                        reseed(t_acc, H0, H1);
-                        // the next block's first half (the next accumulator, whichever tile it belongs to) is requested before
-                        // this block's second half is folded
-                        const int nbuf = accbuf + 1 == kAccBufs ? 0 : accbuf + 1;
-                        const uint32_t nphase = accbuf + 1 == kAccBufs ? accphase ^ 1u : accphase;
-                        --blocks_left;
-                        if (kPrefetch && blocks_left > 0) {
-                            ok = warp_wait(bar0 + 8u * (uint32_t)(G::ACC_FULL + nbuf), nphase, abort_flag, wait_limit);
-                            if (!ok) {
-                                if (lane == 0) report_timeout(p.status, abort_flag, W_ACC_FULL);
-                                break;
-                            }
-                            tc_fence_after();
-                            tick(3);
-                            tmem_load_cols<H0>(t_lane + (uint32_t)(nbuf * BN), S0);
-                        }
-                        fold_columns<SEED, kPack1, H0, H1, COLS>(S1, sw, sxd, negc, acc2);
-                        tick(4);
-                        if (SEED) tmem_wait_st();
-                        tick(5);
-                    }
-                    tc_fence_before();
-                    __syncwarp();
-                    if (leader) mbar_arrive(bar0 + 8u * (uint32_t)(G::ACC_EMPTY + accbuf));
-                    tick(6);
-                    t_acc += (uint32_t)BN;
-                    if (++accbuf == kAccBufs) { accbuf = 0; accphase ^= 1u; t_acc = t_lane; }
-                }
+            for (ks = ks0; ks < ks1 && ok; ++ks) {
+                if (rot == 0) promote_stage(std::integral_constant<int, 0>{});
+                else if (rot == 1) promote_stage(std::integral_constant<int, 1>{});
+                else promote_stage(std::integral_constant<int, 2>{});
+                if (++rot == 3) { rot = 0; qpar ^= (uint32_t)(G::BPS & 1); }
                 if (kScales) {
                     sc_off += (uint32_t)(G::SC_FLOATS * 4);
                     if (++sstage == kScaleStages) { sstage = 0; sc_off = 0; }
                 }
-                tick(7);
             }
             if (!ok) break;
 
@@ -659,19 +657,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 }
             }
         }
-        // a read that was requested for a block this warp never reached (only after a wait gave up)
-        if (MODE == 0) tmem_wait_ld();
+        if (!ok) {
+            if (kEarly) tmem_wait_ld();      // a read that was requested for a block this warp never reached
+            if (lane == 0) report_timeout(p.status, abort_flag, fail_code);
+        }
     }
 
     // ---------------- teardown ----------------
-    tick(9);
     tc_fence_before();
     __syncthreads();
-#if BI8_TC_VARIANTS
-    if (VAR & 16) {
-        for (int i = threadIdx.x; i < 20 * 12; i += blockDim.x) g_prof[blockIdx.x * 240 + i] = prof[i];
-    }
-#endif
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
@@ -797,10 +791,8 @@ int launch_pw(const TcMaps& tm, const TcParams& p, int grid, bool partials, bool
     if (partials) return seed ? launch_one<QB, 1, true, PW, 0>(tm, p, grid, st) : launch_one<QB, 1, false, PW, 0>(tm, p, grid, st);
     if (!seed) return launch_one<QB, 0, false, PW, 0>(tm, p, grid, st);
 #if BI8_TC_VARIANTS
-    if (QB == 64 && var == 16) return launch_one<64, 0, true, PW, 16>(tm, p, grid, st);
-    if (QB == 64 && var == 1) return launch_one<64, 0, true, PW, 1>(tm, p, grid, st);
-    if (QB == 64 && var == 17) return launch_one<64, 0, true, PW, 17>(tm, p, grid, st);
     if (QB == 64 && var == 2) return launch_one<64, 0, true, PW, 2>(tm, p, grid, st);
+    if (QB == 64 && var == 1) return launch_one<64, 0, true, PW, 1>(tm, p, grid, st);
 #endif
     (void)var;
     return launch_one<QB, 0, true, PW, 0>(tm, p, grid, st);
@@ -946,12 +938,6 @@ int launch_gemm_tc(const GemmArgs& g, cudaStream_t st) {
     BI8_CUDA_TRY(cudaGetLastError());
     return BI8_OK;
 }
-
-#if BI8_TC_VARIANTS
-extern "C" __attribute__((visibility("default"))) int bi8_debug_read_prof(unsigned int* host, int n) {
-    return cudaMemcpyFromSymbol(host, g_prof, (size_t)n * 4) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 int run_mma_peak_probe(int iters, float* ms, int* sm_count) {
     const DeviceInfo di = device_info();

@@ -625,12 +625,25 @@ def run_ours(args):
     e2e_value = world * ops_step / (e2e_ms * 1e-3) / 1e12
     del lin, x_host, y_host, x_dev2, y_dev2
 
+    # ---- the partitionings that communicate, at this GPU count (all ranks take part) ----
+    del xs_dev
+    torch.cuda.empty_cache()
+    tp = models = None
+    if not args.no_tp:
+        tp = tp_bench(dev, rank, world, hbm_gbs)
+    if not args.no_models:
+        try:
+            models = models_bench(dev, rank, world, local)
+        except Exception as e:            # a model driver must not take the headline down with it
+            models = {"error": f"{type(e).__name__}: {e}"}
+    _lib.device_status()
+
     if rank != 0:
         if world > 1:
             torch.distributed.destroy_process_group()
         return
 
-    # ---- rank 0: roofline, probe, extras, CPU baseline ----
+    # ---- rank 0: roofline, probe, sweeps, CPU baseline ----
     achieved = ops_step / (gemm_ms * 1e-3) / 1e12
     probe = None
     try:
@@ -652,6 +665,17 @@ def run_ours(args):
         "gemm_ms": gemm_ms, "algorithmic_ops_per_launch": ops_step,
         "traffic": ncu_traffic(f"gemm_tc:{args.workload}"),
     }
+    # comparator only: the same (M, K, N) as one bf16 GEMM in cuBLAS, what the layer costs without quantization
+    xb = torch.randn((M, K), device=dev, dtype=torch.bfloat16)
+    for _ in range(3):
+        torch.matmul(xb, w.t())
+    roofline["cublas_bf16_ms"] = time_kernel(lambda: torch.matmul(xb, w.t()), 7, flush)
+    roofline["int8_gemm_over_cublas_bf16"] = gemm_ms / roofline["cublas_bf16_ms"]
+    del xb
+    # the GEMM back to back for two seconds (pre-quantized activations, rotating outputs)
+    xq_s, sx_s = quantize_block_rowwise(torch.randn((M, K), device=dev, generator=torch.Generator(device=dev).manual_seed(1)).to(torch.bfloat16))
+    roofline["sustained"] = sustained_gemm(lambda i: int8_matmul_block64_rowwise_dequantize(xq_s, wq.t(), sx_s, ws), ops_step, local)
+    del xq_s, sx_s
     extra = None
     if world == 1 and not args.no_extras:
         extra = extras(dev, hbm_gbs, flush)
@@ -659,6 +683,13 @@ def run_ours(args):
         extra["hbm_peak_source"] = peak_src
         extra["timing"] = ("us: CUDA-graph replays over rotating inputs larger than L2, median of 5 replays; us_flushed and the "
                            "GEMM rows marked so: CUDA events around one launch behind a 256 MB fill, median of 7")
+        roofline["kernels"] = kernel_rows(extra, hbm_gbs)
+        roofline["kernels_note"] = (f"frac = fraction of the {peak_src} HBM copy bandwidth ({hbm_gbs} GB/s) for bound hbm, of the nominal "
+                                    "4500 TOP/s for bound tensor; M <= 128 rows and the quantizers are CUDA-graph replays over rotating inputs")
+    if tp is not None:
+        roofline["tp"] = tp
+    if models is not None:
+        roofline["models"] = models
     cpu = None
     if world == 1 and not args.no_cpu:
         cpu, _ = cpu_baseline(args.workload)
@@ -666,10 +697,7 @@ def run_ours(args):
         "metric": "int8_block_gemm_tops", "value": value, "unit": "TOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8", "data": "synthetic",
-        "config": {"workload": args.workload, "M_per_gpu": M, "K": K, "N": N, "block": BLOCK, "in": "bf16", "out": "bf16",
-                   "step": "block-quantize x + int8 block GEMM with fused dequantize (weights pre-quantized)",
-                   "l2": f"{NSETS} rotating input/output sets of {(M * K * 2 + M * N * 2) >> 20} MiB each (larger than L2)",
-                   "parallelism": f"dp{world} over tokens, no collective"},
+        "config": bench_config(args.workload, world),
         "roofline": roofline,
         "e2e": {"value": e2e_value, "unit": "TOP/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": M * K * 2,
                 "d2h_bytes_per_step": M * N * 2, "api": "BlockInt8Linear.forward (eval) on pinned host buffers; H2D, kernels and D2H of neighbouring steps overlap on three streams"},
@@ -678,7 +706,7 @@ def run_ours(args):
     }
     if cpu is not None:
         line["cpu_baseline"] = cpu
-    if extra is not None:
+    if extra is not None and args.full_extra:
         line["extra"] = extra
     print(json.dumps(line), flush=True)
     if world > 1:
@@ -694,6 +722,9 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default=DEFAULT_WORKLOAD)
     ap.add_argument("--no-extras", action="store_true", help="skip the quantize/dequantize/GEMM-shape sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
+    ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel MLP pair")
+    ap.add_argument("--no-models", action="store_true", help="skip the Llama inference / GPT-2 training drivers")
+    ap.add_argument("--full-extra", action="store_true", help="also print the full sweep tables (the compact rows are in roofline.kernels)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

@@ -91,7 +91,7 @@ def run(a, rank, world, local, dev):
         opt.zero_grad(set_to_none=True)
         loss.backward()
         opt.step()
-        return loss
+        return loss.detach()
 
     for _ in range(a.warmup):
         step()

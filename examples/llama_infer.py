@@ -288,10 +288,12 @@ def run(a, rank, world, dev, eager=False):
     model(ids, 0, max_len)                                        # first call: lazy initialisation, allocator growth
     torch.cuda.synchronize()
     t_first = time.perf_counter() - t0
-    t0 = time.perf_counter()
-    logits = model(ids, 0, max_len)                               # steady state (rewrites the same cache positions)
-    torch.cuda.synchronize()
-    t_prefill = time.perf_counter() - t0
+    t_prefill = float("inf")
+    for _ in range(2):                                            # steady state (rewrites the same cache positions)
+        t0 = time.perf_counter()
+        logits = model(ids, 0, max_len)
+        torch.cuda.synchronize()
+        t_prefill = min(t_prefill, time.perf_counter() - t0)
     nxt = logits.argmax(-1)
     out = [nxt]
     # Decode: one step = ~450 small launches (quantize + GEMM per linear, attention, norms); eager launch latency would

@@ -71,7 +71,11 @@ struct Cfg {
     static_assert(PW == 2 || PW == 3 || PW == 4, "2, 3 or 4 promotion warps per lane quarter");
     static constexpr int BN = PW == 3 ? 144 : 160;        // tile columns: kAccBufs * BN <= 512 tensor-memory columns
     static constexpr int COLS = BN / PW;                  // columns owned by one promotion thread: 80, 48, 40
+#ifdef BI8_TC_H0
+    static constexpr int H0 = BI8_TC_H0;
+#else
     static constexpr int H0 = PW == 2 ? 40 : 24;          // the accumulator is read as columns [0, H0) and [H0, COLS)
+#endif
     static constexpr int H1 = COLS - H0;                  // 40, 24, 16
     static constexpr int EPI_WARPS = 4 * PW;
     static constexpr int THREADS = (kRoleWarps + EPI_WARPS) * 32;
@@ -156,8 +160,12 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, uint32_
 // NC (a multiple of 8, at most 40) consecutive accumulator columns of this thread's lane -> registers.
 template <int NC>
 __device__ __forceinline__ void tmem_load_cols(uint32_t taddr, uint32_t (&S)[NC]) {
-    static_assert(NC == 40 || NC == 24 || NC == 16, "supported part widths");
-    if constexpr (NC == 40) {
+    static_assert(NC == 40 || NC == 32 || NC == 24 || NC == 16 || NC == 8, "supported part widths");
+    if constexpr (NC == 32) {
+        tmem_ld32(taddr, S);
+    } else if constexpr (NC == 8) {
+        tmem_ld8(taddr, S);
+    } else if constexpr (NC == 40) {
         tmem_ld32(taddr, reinterpret_cast<uint32_t(&)[32]>(S[0]));
         tmem_ld8(taddr + 32u, reinterpret_cast<uint32_t(&)[8]>(S[32]));
     } else if constexpr (NC == 24) {

@@ -20,10 +20,15 @@
 //   warps 4..   promotion + epilogue, PW warps per tensor-memory lane quarter.  A warp owns 32 rows x BN/PW columns of
 //               the tile.  Per block it reads its part of the finished accumulator in two halves (the second in flight
 //               while the first is folded), re-seeds what it has read, folds the values into fp32 accumulators in
-//               registers and releases the accumulator.  After the last block of a tile it casts, adds bias and stores.
-// The fold costs two FMAs per element and block (t = P*s_row, acc += s_col*t): 2*128*BN FMAs per block on 128 FMA lanes
-// is twice the time the MMAs of a 64-deep block need, so the FMA pipes, not the tensor pipe, bound this kernel; what
-// the code around the FMAs must do is stay out of their way (few instructions, no waiting that is not overlapped).
+//               registers and releases the accumulator.  After the last block of a tile it casts, adds bias and writes
+//               its 32 x BN/PW part into a staging area in shared memory, from where one TMA store (or, for
+//               destinations a tensor map cannot describe, a loop of coalesced stores) moves it out.
+// What bounds the kernel: the fold costs two FMAs per element and block (t = P*s_row, acc += s_col*t), 2*128*BN FMAs per
+// block on 128 FMA lanes = 320 cycles for BN = 160, twice the 163 cycles the MMAs of a 64-deep block need.  On top of
+// that every promotion warp reads its BN/PW column scales of every block from shared memory as broadcast loads, which
+// deliver 8 bytes per wavefront: 16 warps x ~21 wavefronts, plus the 144 wavefronts in which the tensor core reads the
+// block's operands, is ~520 shared-memory wavefronts per block on a pipe that serves one per cycle.  Measured (block 64)
+// the kernel needs ~790 cycles per block with the instruction issue slots 57 % and the shared-memory pipe 65 % busy.
 //
 // Registers: a scheduler (SM sub-partition) owns a quarter of the register file and every fourth warp, and setmaxnreg can
 // only move registers between warps of the same scheduler.  Each scheduler has exactly one of warps 0-3, which shrinks,
@@ -37,13 +42,9 @@
 #include "bi8_common.cuh"
 #include "tc_common.cuh"
 
-#include <cstdlib>
 #include <cstring>
 #include <type_traits>
 
-#ifndef BI8_TC_VARIANTS
-#define BI8_TC_VARIANTS 0
-#endif
 
 namespace bi8 {
 namespace {
@@ -53,7 +54,7 @@ using namespace ptx;
 constexpr int kBM = 128;                 // tile rows
 constexpr int kAccBufs = 3;              // s32 accumulators in tensor memory
 constexpr int kProbeN = 256;             // N of the issue-rate probe's MMAs
-constexpr int kStages = 5;
+constexpr int kStages = 4;               // operand stages of 128 K-bytes in flight
 // Scale ring depth.  The producer fills the slot of stage s after the MMA warp has committed stage s - kStages, whose last
 // block was issued into an accumulator that the promotion warps had released three blocks earlier: with 2 blocks per
 // stage they are then done with every stage up to s - kStages - 2, with 1 block per stage up to s - kStages - 3, with 4
@@ -71,11 +72,7 @@ struct Cfg {
     static_assert(PW == 2 || PW == 3 || PW == 4, "2, 3 or 4 promotion warps per lane quarter");
     static constexpr int BN = PW == 3 ? 144 : 160;        // tile columns: kAccBufs * BN <= 512 tensor-memory columns
     static constexpr int COLS = BN / PW;                  // columns owned by one promotion thread: 80, 48, 40
-#ifdef BI8_TC_H0
-    static constexpr int H0 = BI8_TC_H0;
-#else
     static constexpr int H0 = PW == 2 ? 40 : 24;          // the accumulator is read as columns [0, H0) and [H0, COLS)
-#endif
     static constexpr int H1 = COLS - H0;                  // 40, 24, 16
     static constexpr int EPI_WARPS = 4 * PW;
     static constexpr int THREADS = (kRoleWarps + EPI_WARPS) * 32;
@@ -107,7 +104,8 @@ struct TcParams {
     int tiles_m, tiles_n;
     int out_dtype, bias_dtype;
     int vec_store;      // C base and row pitch allow 16-byte stores
-    int tma_scales;     // sA and sB are described by the tensor maps tmSA / tmSB
+    int tma_store;      // the output is described by the tensor map tmC: staged tiles leave by TMA stores
+    int tma_scales;     // bit 0: sA is described by the tensor map tmSA, bit 1: sB by tmSB
     int ksplit;         // > 1: the K stages are divided over ksplit work items per tile (split-K)
     int stages_per_split;
     float* ws;          // split-K: fp32 partial results [ksplit, M, N]
@@ -127,7 +125,11 @@ struct Geo {
     static constexpr int FULL_AB = 0, EMPTY_AB = kStages, ACC_FULL = 2 * kStages, ACC_EMPTY = 2 * kStages + kAccBufs,
                          NBARS = 2 * kStages + 2 * kAccBufs;
     static constexpr uint32_t misc_off = bar_off + NBARS * 8;   // tmem holder (4 B) + abort flag (4 B) + never-raised flag (4 B)
-    static constexpr uint32_t total = misc_off + 16;
+    // outputs leave through shared memory: every promotion warp stages 32 rows x COLS*2 bytes per pass
+    static constexpr uint32_t OUT_WARP_BYTES = 32 * C::COLS * 2;
+    static constexpr uint32_t out_off = (misc_off + 16 + 127) & ~127u;
+    static constexpr uint32_t total = out_off + C::EPI_WARPS * OUT_WARP_BYTES;
+    static_assert(OUT_WARP_BYTES % 128 == 0, "TMA store sources are 128-byte aligned");
     static_assert((SC_FLOATS * 4) % 128 == 0 && (SB_OFF * 4) % 128 == 0 && C::scale_off % 1024 == 0, "TMA destinations of the scale boxes are 128-byte aligned");
 };
 
@@ -177,16 +179,12 @@ __device__ __forceinline__ void tmem_load_cols(uint32_t taddr, uint32_t (&S)[NC]
 }
 
 // Blocks go round the kAccBufs = 3 accumulators and every stage has BPS blocks, so block `blk` of the stage at position
-// `rot` in a cycle of three stages is block rot*BPS + blk of that cycle: it uses accumulator (rot*BPS + blk) % 3, for the
-// ((rot*BPS + blk) / 3)-th time in the cycle.  A cycle uses every accumulator BPS times; with BPS even the barrier
-// parities therefore repeat from cycle to cycle, with BPS odd they alternate (the callers keep that bit).
+// `rot` in a cycle of three stages is block rot*BPS + blk of that cycle and uses accumulator (rot*BPS + blk) % 3.  A
+// cycle of three stages ends where it began, on accumulator 0.
 template <int BPS>
 struct RotInfo {
     __host__ __device__ static constexpr int buf(int rot, int blk) { return (rot * BPS + blk) % kAccBufs; }
-    __host__ __device__ static constexpr uint32_t par(int rot, int blk) { return (uint32_t)(((rot * BPS + blk) / kAccBufs) & 1); }
 };
-
-__host__ __device__ constexpr int blk_next_rot(int rot) { return rot == 2 ? 0 : rot + 1; }
 
 // A value the compiler must treat as unknown from here on.  Loop-invariant addresses of the promotion loop go through
 // this: left alone, the compiler recomputes them (from the warp index, the thread index, the shared-memory base ...)
@@ -225,17 +223,15 @@ __device__ __forceinline__ void fold_columns(const uint32_t (&S)[NC], uint32_t s
     }
 }
 
-// VAR (development builds only): bit 0 = early request of the next block's first half; bit 1 = first product as scalar
-// FMAs instead of packed ones.
-template <int QB, int MODE, bool SEED, int PW, int VAR>
+template <int QB, int MODE, bool SEED, int PW>
 __global__ void __launch_bounds__(Cfg<PW>::THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const __grid_constant__ CUtensorMap tmSA, const __grid_constant__ CUtensorMap tmSB, const TcParams p) {
+               const __grid_constant__ CUtensorMap tmSA, const __grid_constant__ CUtensorMap tmSB,
+               const __grid_constant__ CUtensorMap tmC, const TcParams p) {
     using C = Cfg<PW>;
     using G = Geo<QB, PW>;
     constexpr int BN = C::BN, COLS = C::COLS, H0 = C::H0, H1 = C::H1;
     constexpr bool kScales = (MODE == 0);           // the partial-sum dump uses no scales
-    constexpr bool kPack1 = (VAR & 2) == 0;
     extern __shared__ __align__(1024) unsigned char smem_dyn[];
     // dynamic shared memory is only guaranteed 16-byte aligned: round up to the swizzle atom
     const uint32_t raw = smem_u32(smem_dyn);
@@ -263,7 +259,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             // the lane that issues the TMA copies; with scales copied by cp.async, every lane of the producer warp as well
-            mbar_init(bar(G::FULL_AB + s), (kScales && !p.tma_scales) ? 33 : 1);
+            mbar_init(bar(G::FULL_AB + s), (kScales && p.tma_scales != 3) ? 33 : 1);
             mbar_init(bar(G::EMPTY_AB + s), 1);
         }
         for (int b = 0; b < kAccBufs; ++b) {
@@ -297,7 +293,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             for (int s = 0; s < kStages; ++s) last_parity[s] = -1;
             bool ok = true;
             bool first_item = true;
-            constexpr uint32_t kScaleBytes = (uint32_t)(G::BPS * (kBM + BN) * 4);
+            constexpr uint32_t kSaBytes = (uint32_t)(G::BPS * kBM * 4), kSbBytes = (uint32_t)(G::BPS * BN * 4);
+            const bool tma_sa = kScales && (p.tma_scales & 1), tma_sb = kScales && (p.tma_scales & 2);
             for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
                 int tile, split, ks0, ks1, m0, n0;
                 item_range(item, num_tiles, nks, p.stages_per_split, tile, split, ks0, ks1);
@@ -312,29 +309,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const uint32_t fb = bar(G::FULL_AB + stage);
                     const uint32_t sdst = sc_ring_u32 + (uint32_t)(sslot * G::SC_FLOATS * 4);
                     if (lane == 0 && !skip) {
-                        mbar_expect_tx(fb, C::STAGE_BYTES + ((kScales && p.tma_scales) ? kScaleBytes : 0u));
+                        mbar_expect_tx(fb, C::STAGE_BYTES + (tma_sa ? kSaBytes : 0u) + (tma_sb ? kSbBytes : 0u));
                         tma_load_2d(base + C::a_off(stage), &tmA, fb, ks * kBK, m0);
                         tma_load_2d(base + C::b_off(stage), &tmB, fb, ks * kBK, n0);
-                        if (kScales && p.tma_scales) {
-                            // boxes [BPS, 128] of sA and [BPS, BN] of sB; rows and blocks outside the tensors read as zero
-                            tma_load_2d(sdst, &tmSA, fb, m0, ks * G::BPS);
-                            tma_load_2d(sdst + (uint32_t)(G::SB_OFF * 4), &tmSB, fb, n0, ks * G::BPS);
-                        }
+                        // boxes [BPS, 128] of sA and [BPS, BN] of sB; rows and blocks outside the tensors read as zero
+                        if (tma_sa) tma_load_2d(sdst, &tmSA, fb, m0, ks * G::BPS);
+                        if (tma_sb) tma_load_2d(sdst + (uint32_t)(G::SB_OFF * 4), &tmSB, fb, n0, ks * G::BPS);
                     }
-                    if (kScales && !p.tma_scales && !skip) {
-                        // asynchronous 4-byte copies: the warp does not wait for the data; each lane's arrival on the
-                        // stage's barrier fires when its copies have landed
-                        for (int idx = lane; idx < G::BPS * (kBM + BN); idx += 32) {
-                            const bool is_a = idx < G::SB_OFF;
-                            const int rel = is_a ? idx : idx - G::SB_OFF;
-                            const int width = is_a ? kBM : BN;
-                            const int blk = rel / width, c = rel % width;
+                    if (kScales && !(tma_sa && tma_sb) && !skip) {
+                        // A scale tensor whose rows are not 16-byte aligned: asynchronous 4-byte copies by the 32 lanes (the
+                        // warp does not wait for the data; each lane's arrival on the stage's barrier fires when its
+                        // copies have landed)
+#pragma unroll
+                        for (int blk = 0; blk < G::BPS; ++blk) {
                             const int j = ks * G::BPS + blk;
-                            const int x = (is_a ? m0 : n0) + c, extent = is_a ? p.M : p.N;
-                            const float* src = is_a ? p.sA : p.sB;
-                            const bool live = j < p.nb && x < extent;
-                            const float* g = live ? src + (int64_t)j * extent + x : src;
-                            cp_async_4(sdst + (uint32_t)(idx * 4), g, live ? 4u : 0u);
+                            if (!tma_sa) {
+                                const float* row = p.sA + (int64_t)j * p.M + m0;
+#pragma unroll
+                                for (int c = lane; c < kBM; c += 32) {
+                                    const bool live = j < p.nb && m0 + c < p.M;
+                                    cp_async_4(sdst + (uint32_t)((blk * kBM + c) * 4), live ? row + c : p.sA, live ? 4u : 0u);
+                                }
+                            }
+                            if (!tma_sb) {
+                                const float* row = p.sB + (int64_t)j * p.N + n0;
+#pragma unroll
+                                for (int c = lane; c < BN; c += 32) {
+                                    const bool live = j < p.nb && n0 + c < p.N;
+                                    cp_async_4(sdst + (uint32_t)((G::SB_OFF + blk * BN + c) * 4), live ? row + c : p.sB, live ? 4u : 0u);
+                                }
+                            }
                         }
                         cp_async_arrive(fb);
                     }
@@ -358,24 +362,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         } else if (warp == 1) {
             // ---------------- MMA issuer ----------------
             // Every stage has BPS blocks (blocks past the end of K multiply zero-filled operands) and the blocks go
-            // round the three accumulators, so which accumulator a block of a stage uses, and the parity of its barriers,
-            // depend only on the stage's position in a cycle of three stages: the stage body exists in three copies
-            // with those values as constants (RotInfo).
+            // round the three accumulators.  Every tile starts on accumulator 0, so which accumulator a block uses
+            // depends only on the stage's position in a cycle of three stages: the K loop runs in such cycles, with the
+            // stage body in three copies that have the accumulator as a constant (RotInfo) and no dispatch between
+            // them.  The barrier parity of each accumulator flips with every use.
             constexpr uint32_t idesc = umma_idesc_i8(kBM, BN);
-            int stage = 0, rot = 0;
-            uint32_t phase = 0, qpar = 0;
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t accpar[kAccBufs] = {0u, 0u, 0u};
             bool ok = true;
-            auto issue_stage = [&](auto rot_tag, uint64_t adesc, uint64_t bdesc) {
+            auto issue_stage = [&](auto rot_tag) {
                 constexpr int ROT = decltype(rot_tag)::value;
+                ok = warp_wait(bar(G::FULL_AB + stage), phase, abort_flag, wait_limit_mma);
+                if (!ok) {
+                    if (lane == 0) report_timeout(p.status, abort_flag, W_FULL_AB);
+                    return;
+                }
+                tc_fence_after();
+                const uint64_t adesc = umma_desc_k_sw128(base + C::a_off(stage));
+                const uint64_t bdesc = umma_desc_k_sw128(base + C::b_off(stage));
 #pragma unroll
                 for (int blk = 0; blk < G::BPS; ++blk) {
-                    using R = RotInfo<G::BPS>;
-                    const int buf = R::buf(ROT, blk);
-                    ok = warp_wait(bar(G::ACC_EMPTY + buf), qpar ^ R::par(ROT, blk), abort_flag, wait_limit_mma);
+                    const int buf = RotInfo<G::BPS>::buf(ROT, blk);
+                    ok = warp_wait(bar(G::ACC_EMPTY + buf), accpar[buf], abort_flag, wait_limit_mma);
                     if (!ok) {
                         if (lane == 0) report_timeout(p.status, abort_flag, W_ACC_EMPTY);
                         return;
                     }
+                    accpar[buf] ^= 1u;
                     tc_fence_after();
                     if (lane == 0) {
 #pragma unroll
@@ -387,27 +401,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     }
                     __syncwarp();
                 }
+                if (lane == 0) tc_commit(bar(G::EMPTY_AB + stage));
+                __syncwarp();
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
             };
             for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
                 int tile, split, ks0, ks1;
                 item_range(item, num_tiles, nks, p.stages_per_split, tile, split, ks0, ks1);
-                for (int ks = ks0; ks < ks1 && ok; ++ks) {
-                    ok = warp_wait(bar(G::FULL_AB + stage), phase, abort_flag, wait_limit_mma);
-                    if (!ok) {
-                        if (lane == 0) report_timeout(p.status, abort_flag, W_FULL_AB);
-                        break;
-                    }
-                    tc_fence_after();
-                    const uint64_t adesc = umma_desc_k_sw128(base + C::a_off(stage));
-                    const uint64_t bdesc = umma_desc_k_sw128(base + C::b_off(stage));
-                    if (rot == 0) issue_stage(std::integral_constant<int, 0>{}, adesc, bdesc);
-                    else if (rot == 1) issue_stage(std::integral_constant<int, 1>{}, adesc, bdesc);
-                    else issue_stage(std::integral_constant<int, 2>{}, adesc, bdesc);
-                    if (!ok) break;
-                    if (lane == 0) tc_commit(bar(G::EMPTY_AB + stage));
-                    __syncwarp();
-                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
-                    if (++rot == 3) { rot = 0; qpar ^= (uint32_t)(G::BPS & 1); }
+                for (int ks = ks0; ks < ks1 && ok; ks += 3) {
+                    issue_stage(std::integral_constant<int, 0>{});
+                    if (ks + 1 < ks1 && ok) issue_stage(std::integral_constant<int, 1>{});
+                    if (ks + 2 < ks1 && ok) issue_stage(std::integral_constant<int, 2>{});
                 }
             }
         }
@@ -418,6 +422,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int slice = (warp - kRoleWarps) >> 2;       // columns COLS*slice .. of the tile
         const int row = quarter * 32 + lane;
         const uint32_t t_lane = keep(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(slice * COLS));
+        // eight spare tensor-memory columns of this warp's lanes keep the seed pattern
+        static_assert(kAccBufs * BN + 8 * PW <= 512, "no spare tensor-memory columns for the seed pattern");
+        const uint32_t t_seed = keep(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(kAccBufs * BN + 8 * slice));
         // shared addresses of this thread's row scale and of its first column scale in scale stage 0, block 0
         const uint32_t sa_addr = keep(sc_ring_u32 + (uint32_t)(row * 4));
         const uint32_t sw_addr = keep(sc_ring_u32 + (uint32_t)((G::SB_OFF + slice * COLS) * 4));
@@ -434,11 +441,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
                 for (int c = 0; c < COLS / 8; ++c) tmem_st8(t_lane + (uint32_t)(b * BN + c * 8), seedv);
             tmem_wait_st();
-            // The seed registers are re-read from tensor memory: as the result of one load they are a tuple of consecutive
-            // registers that stays resident.  Left as eight constants the compiler rebuilds the tuple with eight moves
-            // in front of every store.
-            tmem_ld8(t_lane, seedv);
-            tmem_wait_ld();
+            // The promotion loop re-reads the seed pattern from the spare columns in every block: the result of a load is
+            // a tuple of consecutive registers, which is what the stores want, and it is live for half a block only.
+            // Eight constants would be rebuilt with eight moves in front of every store; a tuple kept across the loop
+            // costs eight registers that the loop does not have, and the compiler then copies it around.
+            tmem_st8(t_seed, seedv);
+            tmem_wait_st();
         }
         tc_fence_before();
         __syncwarp();
@@ -453,53 +461,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
         };
 
-        int sstage = 0, rot = 0;
-        uint32_t qpar = 0;
+        int sstage = 0;
+        uint32_t accpar[kAccBufs] = {0u, 0u, 0u};   // barrier parities of the three accumulators, flipped with every use
         uint32_t sc_off = 0;                      // byte offset of scale stage `sstage`
         bool ok = true;
         int fail_code = 0;
 
         // the tile's COLS fp32 accumulators of this thread, kept as packed pairs for fma.rn.f32x2
         uint64_t acc2[COLS / 2];
-        int m = 0, nbase = 0, ks = 0;
-
-        // stages this CTA's promotion warps will see (the read of a block's first half is requested during the block
-        // before it, so the last block must be known)
-        int stages_left = 0;
-        for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
-            int tile, split, ks0, ks1;
-            item_range(item, num_tiles, nks, p.stages_per_split, tile, split, ks0, ks1);
-            stages_left += ks1 - ks0;
-        }
-        // development variant (measured slower): request the next block's first half before releasing this one
-        constexpr bool kEarly = (MODE == 0) && (VAR & 1);
+        int m = 0, nbase = 0;
         uint32_t S0[H0], S1[H1];
-        if (kEarly && stages_left > 0) {
-            ok = warp_wait(bar0 + 8u * (uint32_t)(G::ACC_FULL + 0), 0u, abort_flag, wait_limit);
-            if (!ok) fail_code = W_ACC_FULL;
-            else {
-                tc_fence_after();
-                tmem_load_cols<H0>(t_lane, S0);
-            }
-        }
 
         // One stage of the promotion: BPS blocks.  `rot_tag` is the stage's position in a cycle of three stages, which
-        // fixes the accumulator and the barrier parity of each of its blocks (RotInfo).
-        auto promote_stage = [&](auto rot_tag) {
+        // fixes the accumulator of each of its blocks (RotInfo); `ks` is the stage's index along K.
+        auto promote_stage = [&](auto rot_tag, int ks) {
             constexpr int ROT = decltype(rot_tag)::value;
             using R = RotInfo<G::BPS>;
 #pragma unroll
             for (int blk = 0; blk < G::BPS; ++blk) {
                 const int buf = R::buf(ROT, blk);
                 const uint32_t t_acc = t_lane + (uint32_t)(buf * BN);
-                if (!kEarly) {
-                    ok = warp_wait(bar0 + 8u * (uint32_t)(G::ACC_FULL + buf), qpar ^ R::par(ROT, blk), abort_flag, wait_limit);
-                    if (!ok) {
-                        fail_code = W_ACC_FULL;
-                        return;
-                    }
-                    tc_fence_after();
+                ok = warp_wait(bar0 + 8u * (uint32_t)(G::ACC_FULL + buf), accpar[buf], abort_flag, wait_limit);
+                if (!ok) {
+                    fail_code = W_ACC_FULL;
+                    return;
                 }
+                accpar[buf] ^= 1u;
+                tc_fence_after();
                 if (MODE == 1) {
                     const int j = ks * G::BPS + blk;
 #pragma unroll
@@ -517,7 +505,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         }
                     }
                 } else {
-                    if (!kEarly) tmem_load_cols<H0>(t_acc, S0);
+                    tmem_load_cols<H0>(t_acc, S0);
+                    if (SEED) tmem_ld8(t_seed, seedv);      // the seed tuple for this block's stores
                     // the row's scale, while the read of the first half is in flight
                     float sxd = __fmul_rn(lds_f32(sa_addr + sc_off + (uint32_t)(blk * kBM * 4)), div);
                     float negc = 0.0f;
@@ -529,36 +518,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     tmem_wait_ld();
                     tmem_load_cols<H1>(t_acc + (uint32_t)H0, S1);    // second half, in flight during the fold of the first
                     reseed(t_acc, 0, H0);
-                    fold_columns<SEED, kPack1, 0, H0, COLS>(S0, sw, sxd, negc, acc2);
+                    fold_columns<SEED, true, 0, H0, COLS>(S0, sw, sxd, negc, acc2);
                     tmem_wait_ld();
                     reseed(t_acc, H0, H1);
-                    fold_columns<SEED, kPack1, H0, H1, COLS>(S1, sw, sxd, negc, acc2);
-                    if (kEarly) {
-                        // The next block's accumulator (which block that is, of which tile, does not matter here) is
-                        // waited for and its first half requested now, so that the read is in flight during this
-                        // block's release sequence and the next block's set-up.
-                        constexpr int NROT = blk_next_rot(ROT);
-                        const bool last_of_stage = blk == G::BPS - 1;
-                        const int nbuf = last_of_stage ? R::buf(NROT, 0) : R::buf(ROT, blk + 1);
-                        const uint32_t npar = last_of_stage ? ((ROT == 2 ? (qpar ^ (uint32_t)(G::BPS & 1)) : qpar) ^ R::par(NROT, 0))
-                                                            : (qpar ^ R::par(ROT, blk + 1));
-                        if (!(last_of_stage && stages_left == 1)) {
-                            ok = warp_wait(bar0 + 8u * (uint32_t)(G::ACC_FULL + nbuf), npar, abort_flag, wait_limit);
-                            if (!ok) {
-                                fail_code = W_ACC_FULL;
-                                return;
-                            }
-                            tc_fence_after();
-                            tmem_load_cols<H0>(t_lane + (uint32_t)(nbuf * BN), S0);
-                        }
-                    }
+                    fold_columns<SEED, true, H0, H1, COLS>(S1, sw, sxd, negc, acc2);
                 }
                 if (SEED) tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
                 if (leader) mbar_arrive(bar0 + 8u * (uint32_t)(G::ACC_EMPTY + buf));
             }
-            --stages_left;
+            if (kScales) {
+                sc_off += (uint32_t)(G::SC_FLOATS * 4);
+                if (++sstage == kScaleStages) { sstage = 0; sc_off = 0; }
+            }
         };
 
         for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
@@ -570,103 +543,145 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
             for (int i = 0; i < COLS / 2; ++i) acc2[i] = 0ull;
 
-            for (ks = ks0; ks < ks1 && ok; ++ks) {
-                if (rot == 0) promote_stage(std::integral_constant<int, 0>{});
-                else if (rot == 1) promote_stage(std::integral_constant<int, 1>{});
-                else promote_stage(std::integral_constant<int, 2>{});
-                if (++rot == 3) { rot = 0; qpar ^= (uint32_t)(G::BPS & 1); }
-                if (kScales) {
-                    sc_off += (uint32_t)(G::SC_FLOATS * 4);
-                    if (++sstage == kScaleStages) { sstage = 0; sc_off = 0; }
-                }
+            // cycles of three stages; every tile starts on accumulator 0, like the MMA issuer
+            for (int ks = ks0; ks < ks1 && ok; ks += 3) {
+                promote_stage(std::integral_constant<int, 0>{}, ks);
+                if (ks + 1 < ks1 && ok) promote_stage(std::integral_constant<int, 1>{}, ks + 1);
+                if (ks + 2 < ks1 && ok) promote_stage(std::integral_constant<int, 2>{}, ks + 2);
             }
             if (!ok) break;
 
-            if (MODE == 0 && m < p.M) {
-                float acc[COLS];
-#pragma unroll
-                for (int i = 0; i < COLS / 2; ++i) unpack_f32x2(acc2[i], acc[2 * i], acc[2 * i + 1]);
-                if (p.ksplit > 1) {
-                    // split-K: raw fp32 partial result of this K range; cast and bias happen in the reduction
-                    float* wrow = p.ws + ((int64_t)split * p.M + m) * p.N;
-#pragma unroll
-                    for (int g = 0; g < COLS / 4; ++g) {
-                        const int n = nbase + g * 4;
-                        if ((p.N & 3) == 0 && n + 4 <= p.N) {
-                            *reinterpret_cast<float4*>(wrow + n) = make_float4(acc[g * 4], acc[g * 4 + 1], acc[g * 4 + 2], acc[g * 4 + 3]);
-                        } else {
-#pragma unroll
-                            for (int u = 0; u < 4; ++u)
-                                if (n + u < p.N) wrow[n + u] = acc[g * 4 + u];
-                        }
-                    }
-                    continue;
-                }
-                const bool has_bias = p.bias != nullptr;
+            if (MODE == 0) {
+                // The tile leaves through the warp's staging area in shared memory: every lane writes its row's share
+                // (ROWB bytes), then either one TMA store or a loop of coalesced stores moves the 32 x ROWB bytes out.
+                // 2-byte outputs take one pass of COLS columns, 4-byte outputs (fp32, split-K partial sums) two passes of
+                // COLS / 2.  Addresses are derived here from the thread index rather than kept in registers through the
+                // K loop, whose register budget is full.
+                constexpr uint32_t ROWB = (uint32_t)(COLS * 2);
+                uint32_t tid_now;
+                asm volatile("mov.u32 %0, %%tid.x;" : "=r"(tid_now));
+                const uint32_t ln = tid_now & 31u;
+                const uint32_t out_stage = base + G::out_off + ((tid_now >> 5) - (uint32_t)kRoleWarps) * G::OUT_WARP_BYTES;
+                const uint32_t my_row = out_stage + ln * ROWB;
+                const bool partial = p.ksplit > 1;
+                const bool wide = partial || p.out_dtype == BI8_F32;
+                const bool bf = p.out_dtype == BI8_BF16;
+                const bool has_bias = p.bias != nullptr && !partial;   // split-K: cast and bias happen in the reduction
+                const int row0 = m - (int)ln;                         // first row of the warp's part
                 auto bias_at = [&](int n) -> float {
+                    if (n >= p.N) return 0.0f;
                     if (p.bias_dtype == BI8_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n]);
                     if (p.bias_dtype == BI8_F16) return __half2float(static_cast<const __half*>(p.bias)[n]);
                     return static_cast<const float*>(p.bias)[n];
                 };
-                if (p.out_dtype == BI8_F32) {
-                    float* crow = static_cast<float*>(p.C) + (int64_t)m * p.ldc;
+                const int passes = wide ? 2 : 1;
+#pragma unroll 1
+                for (int ps = 0; ps < passes; ++ps) {
+                    const int col0 = nbase + ps * (COLS / 2);
+                    // the previous TMA store must have read the staging area before it is written again
+                    if (p.tma_store && ln == 0) tma_store_wait_read();
+                    __syncwarp();
+                    if (wide) {
 #pragma unroll
-                    for (int g = 0; g < COLS / 4; ++g) {
-                        const int n = nbase + g * 4;
-                        float v[4];
+                        for (int g = 0; g < COLS / 8; ++g) {
+                            float v[4];
+                            unpack_f32x2(acc2[2 * g], v[0], v[1]);
+                            unpack_f32x2(acc2[2 * g + 1], v[2], v[3]);
+                            if (has_bias) {
 #pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            v[u] = acc[g * 4 + u];
-                            if (has_bias && n + u < p.N) v[u] = __fadd_rn(v[u], bias_at(n + u));
+                                for (int u = 0; u < 4; ++u) v[u] = __fadd_rn(v[u], bias_at(col0 + g * 4 + u));
+                            }
+                            sts_v4(my_row + (uint32_t)(g * 16), __float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]),
+                                   __float_as_uint(v[3]));
                         }
-                        if (p.vec_store && n + 4 <= p.N) {
-                            *reinterpret_cast<float4*>(crow + n) = make_float4(v[0], v[1], v[2], v[3]);
-                        } else {
+                        // the second pass finds its columns where the first found its own
 #pragma unroll
-                            for (int u = 0; u < 4; ++u)
-                                if (n + u < p.N) crow[n + u] = v[u];
+                        for (int i = 0; i < COLS / 4; ++i) acc2[i] = acc2[i + COLS / 4];
+                    } else {
+#pragma unroll
+                        for (int g = 0; g < COLS / 8; ++g) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                float lo, hi;
+                                unpack_f32x2(acc2[g * 4 + u], lo, hi);
+                                uint32_t pk = bf ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
+                                if (has_bias) {
+                                    // the reference adds the bias after the cast, in the output type (lines 127-131)
+                                    const int n = col0 + g * 8 + 2 * u;
+                                    const float blo = bias_at(n), bhi = bias_at(n + 1);
+                                    if (bf) {
+                                        uint32_t bb = pack_bf16x2(blo, bhi);
+                                        pk = pack_bf16x2(__fadd_rn(bf16lo(pk), bf16lo(bb)), __fadd_rn(bf16hi(pk), bf16hi(bb)));
+                                    } else {
+                                        __half2 a2 = *reinterpret_cast<__half2*>(&pk);
+                                        __half2 b2 = __floats2half2_rn(blo, bhi);
+                                        float2 af = __half22float2(a2), bfv = __half22float2(b2);
+                                        pk = pack_f16x2(__fadd_rn(af.x, bfv.x), __fadd_rn(af.y, bfv.y));
+                                    }
+                                }
+                                w[u] = pk;
+                            }
+                            sts_v4(my_row + (uint32_t)(g * 16), w[0], w[1], w[2], w[3]);
                         }
                     }
-                } else {
-                    const bool bf = p.out_dtype == BI8_BF16;
-                    uint16_t* crow = static_cast<uint16_t*>(p.C) + (int64_t)m * p.ldc;
-#pragma unroll
-                    for (int g = 0; g < COLS / 8; ++g) {
-                        const int n = nbase + g * 8;
-                        uint32_t w[4];
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            float lo = acc[g * 8 + 2 * u], hi = acc[g * 8 + 2 * u + 1];
-                            uint32_t pk = bf ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
-                            if (has_bias) {
-                                // the reference adds the bias after the cast, in the output type (lines 127-131)
-                                float blo = (n + 2 * u < p.N) ? bias_at(n + 2 * u) : 0.0f;
-                                float bhi = (n + 2 * u + 1 < p.N) ? bias_at(n + 2 * u + 1) : 0.0f;
-                                if (bf) {
-                                    uint32_t bb = pack_bf16x2(blo, bhi);
-                                    pk = pack_bf16x2(__fadd_rn(bf16lo(pk), bf16lo(bb)), __fadd_rn(bf16hi(pk), bf16hi(bb)));
-                                } else {
-                                    __half2 a2 = *reinterpret_cast<__half2*>(&pk);
-                                    __half2 b2 = __floats2half2_rn(blo, bhi);
-                                    float2 af = __half22float2(a2), bfv = __half22float2(b2);
-                                    pk = pack_f16x2(__fadd_rn(af.x, bfv.x), __fadd_rn(af.y, bfv.y));
+                    if (p.tma_store) {
+                        // rows and columns of the box that lie outside the tensor are not written
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (ln == 0 && col0 < p.N && row0 < p.M) {
+                            tma_store_2d(&tmC, out_stage, col0, row0);
+                            tma_store_commit();
+                        }
+                    } else {
+                        // Destinations that a tensor map cannot describe (base or row pitch not 16-byte aligned) and
+                        // split-K partial sums: consecutive lanes store consecutive 4-byte words of a row, or 2-byte
+                        // elements where the rows of a 16-bit output are not all 4-byte aligned.
+                        __syncwarp();
+                        const int esz = wide ? 4 : 2;
+                        unsigned char* dst;
+                        int64_t pitch;
+                        if (partial) {
+                            pitch = (int64_t)p.N * 4;
+                            dst = reinterpret_cast<unsigned char*>(p.ws) + ((int64_t)split * p.M + row0) * pitch + (int64_t)col0 * 4;
+                        } else {
+                            pitch = p.ldc * esz;
+                            dst = static_cast<unsigned char*>(p.C) + (int64_t)row0 * pitch + (int64_t)col0 * esz;
+                        }
+                        const int rows_valid = p.M - row0;                         // may exceed 32 or be negative
+                        const int cols_left = p.N - col0;
+                        const int cols_pass = wide ? COLS / 2 : COLS;
+                        const int cols_valid = cols_left < cols_pass ? cols_left : cols_pass;
+                        if (wide || (((reinterpret_cast<uintptr_t>(dst) | (uintptr_t)pitch) & 3u) == 0)) {
+                            constexpr int WPR = (int)ROWB / 4;                     // words per staged row
+                            const int words = wide ? cols_valid : (cols_valid >> 1);
+                            const bool odd_tail = !wide && (cols_valid & 1) && cols_valid > 0;
+#pragma unroll 4
+                            for (int idx = (int)ln; idx < 32 * WPR; idx += 32) {
+                                const int r = idx / WPR, w = idx - r * WPR;
+                                if (r < rows_valid) {
+                                    const uint32_t v = lds_u32(out_stage + (uint32_t)(idx * 4));
+                                    unsigned char* d = dst + (int64_t)r * pitch + w * 4;
+                                    if (w < words) *reinterpret_cast<uint32_t*>(d) = v;
+                                    else if (odd_tail && w == words) *reinterpret_cast<uint16_t*>(d) = (uint16_t)(v & 0xffffu);
                                 }
                             }
-                            w[u] = pk;
-                        }
-                        if (p.vec_store && n + 8 <= p.N) {
-                            *reinterpret_cast<uint4*>(crow + n) = make_uint4(w[0], w[1], w[2], w[3]);
                         } else {
-#pragma unroll
-                            for (int u = 0; u < 8; ++u)
-                                if (n + u < p.N) crow[n + u] = (uint16_t)((w[u / 2] >> (16 * (u % 2))) & 0xffffu);
+                            constexpr int EPR = (int)ROWB / 2;                     // elements per staged row
+#pragma unroll 4
+                            for (int idx = (int)ln; idx < 32 * EPR; idx += 32) {
+                                const int r = idx / EPR, c = idx - r * EPR;
+                                if (r < rows_valid && c < cols_valid)
+                                    *reinterpret_cast<uint16_t*>(dst + (int64_t)r * pitch + c * 2) = lds_u16(out_stage + (uint32_t)(idx * 2));
+                            }
                         }
                     }
                 }
             }
         }
+        // shared memory stays valid until the last store has read it
+        if (lane == 0) tma_store_wait_read();
         if (!ok) {
-            if (kEarly) tmem_wait_ld();      // a read that was requested for a block this warp never reached
             if (lane == 0) report_timeout(p.status, abort_flag, fail_code);
         }
     }
@@ -755,65 +770,38 @@ __global__ void __launch_bounds__(128, 1) mma_peak_probe_kernel(int iters, int* 
 }
 
 struct TcMaps {
-    CUtensorMap a, b, sa, sb;
+    CUtensorMap a, b, sa, sb, c;
 };
 
-template <int QB, int MODE, bool SEED, int PW, int VAR>
+template <int QB, int MODE, bool SEED, int PW>
 int launch_one(const TcMaps& tm, const TcParams& p, int grid, cudaStream_t st) {
     using C = Cfg<PW>;
     constexpr size_t smem = Geo<QB, PW>::total + 1024;
     static SmemOptIn opt_in;
-    const int rc = opt_in.ensure(gemm_tc_kernel<QB, MODE, SEED, PW, VAR>, smem);
+    const int rc = opt_in.ensure(gemm_tc_kernel<QB, MODE, SEED, PW>, smem);
     if (rc != BI8_OK) return rc;
     // setmaxnreg.inc waits for registers that the role warps of the same scheduler give up: if the compiler gave the
     // kernel fewer registers per thread than the budget was written for, the wait would never end.  Checked once.
     static int regs_ok = 0;       // 0 unknown, 1 fine, -1 refused
     if (regs_ok == 0) {
         cudaFuncAttributes fa;
-        BI8_CUDA_TRY(cudaFuncGetAttributes(&fa, gemm_tc_kernel<QB, MODE, SEED, PW, VAR>));
+        BI8_CUDA_TRY(cudaFuncGetAttributes(&fa, gemm_tc_kernel<QB, MODE, SEED, PW>));
         regs_ok = ((1 + PW) * fa.numRegs >= C::ROLE_REGS + PW * C::EPI_REGS && (1 + PW) * 32 * fa.numRegs <= 16384) ? 1 : -1;
     }
     if (regs_ok < 0) return fail(BI8_ERR_CUDA, "tensor-core GEMM: the kernel was compiled with a register count its register moves do not fit");
-    gemm_tc_kernel<QB, MODE, SEED, PW, VAR><<<grid, C::THREADS, smem, st>>>(tm.a, tm.b, tm.sa, tm.sb, p);
+    gemm_tc_kernel<QB, MODE, SEED, PW><<<grid, C::THREADS, smem, st>>>(tm.a, tm.b, tm.sa, tm.sb, tm.c, p);
     BI8_CUDA_TRY(cudaGetLastError());
     return BI8_OK;
 }
 
 // Promotion warps per lane quarter (and with it the tile width) of the kernel that runs.
-int tc_pw() {
-#if BI8_TC_VARIANTS
-    if (const char* e = std::getenv("BI8_TC_PW")) {
-        const int v = std::atoi(e);
-        if (v >= 2 && v <= 4) return v;
-    }
-#endif
-    return 4;
-}
-int tc_bn() {
-    const int pw = tc_pw();
-    return pw == 3 ? Cfg<3>::BN : Cfg<4>::BN;
-}
-
-template <int QB, int PW>
-int launch_pw(const TcMaps& tm, const TcParams& p, int grid, bool partials, bool seed, int var, cudaStream_t st) {
-    if (partials) return seed ? launch_one<QB, 1, true, PW, 0>(tm, p, grid, st) : launch_one<QB, 1, false, PW, 0>(tm, p, grid, st);
-    if (!seed) return launch_one<QB, 0, false, PW, 0>(tm, p, grid, st);
-#if BI8_TC_VARIANTS
-    if (QB == 64 && var == 2) return launch_one<64, 0, true, PW, 2>(tm, p, grid, st);
-    if (QB == 64 && var == 1) return launch_one<64, 0, true, PW, 1>(tm, p, grid, st);
-#endif
-    (void)var;
-    return launch_one<QB, 0, true, PW, 0>(tm, p, grid, st);
-}
+constexpr int kPW = 4;
+int tc_bn() { return Cfg<kPW>::BN; }
 
 template <int QB>
-int launch_qb(const TcMaps& tm, const TcParams& p, int grid, bool partials, bool seed, int var, cudaStream_t st) {
-#if BI8_TC_VARIANTS
-    const int pw = tc_pw();
-    if (pw == 2) return launch_pw<QB, 2>(tm, p, grid, partials, seed, var, st);
-    if (pw == 3) return launch_pw<QB, 3>(tm, p, grid, partials, seed, var, st);
-#endif
-    return launch_pw<QB, 4>(tm, p, grid, partials, seed, var, st);
+int launch_qb(const TcMaps& tm, const TcParams& p, int grid, bool partials, bool seed, cudaStream_t st) {
+    if (partials) return seed ? launch_one<QB, 1, true, kPW>(tm, p, grid, st) : launch_one<QB, 1, false, kPW>(tm, p, grid, st);
+    return seed ? launch_one<QB, 0, true, kPW>(tm, p, grid, st) : launch_one<QB, 0, false, kPW>(tm, p, grid, st);
 }
 
 }  // namespace
@@ -883,16 +871,18 @@ int launch_gemm_tc(const GemmArgs& g, cudaStream_t st) {
     TcParams p;
     std::memset(&p, 0, sizeof(p));
     const bool partials = g.partials != nullptr;
-    // the scale tensors go through TMA when a tensor map can describe them: 16-byte aligned base and row length
-    p.tma_scales = (!partials && aligned(g.sA, 16) && aligned(g.sB, 16) && g.M % 4 == 0 && g.N % 4 == 0) ? 1 : 0;
-    if (p.tma_scales) {
+    // a scale tensor goes through TMA when a tensor map can describe it: 16-byte aligned base and row length
+    const bool tma_sa = !partials && aligned(g.sA, 16) && g.M % 4 == 0, tma_sb = !partials && aligned(g.sB, 16) && g.N % 4 == 0;
+    p.tma_scales = (tma_sa ? 1 : 0) | (tma_sb ? 2 : 0);
+    tm.sa = tm.a;          // stand-ins that are never dereferenced
+    tm.sb = tm.b;
+    if (tma_sa) {
         rc = cached_scale_map(&tm.sa, dev, g.sA, nb, g.M, kBM, bps);
         if (rc != BI8_OK) return rc;
+    }
+    if (tma_sb) {
         rc = cached_scale_map(&tm.sb, dev, g.sB, nb, g.N, bn, bps);
         if (rc != BI8_OK) return rc;
-    } else {
-        tm.sa = tm.a;      // never dereferenced
-        tm.sb = tm.b;
     }
     p.sA = g.sA;
     p.sB = g.sB;
@@ -914,6 +904,7 @@ int launch_gemm_tc(const GemmArgs& g, cudaStream_t st) {
     p.vec_store = (g.C != nullptr && aligned(g.C, 16) && (g.ldc * esz) % 16 == 0) ? 1 : 0;
     p.wait_limit_us = g.wait_limit_us;
     p.skip_stage = g.skip_stage;
+    tm.c = tm.a;           // stand-in, never dereferenced without tma_store
     const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
     if (tiles >= (1ll << 31) / 32) return fail(BI8_ERR_SHAPE, "too many output tiles");
     SplitPlan pl;
@@ -925,18 +916,21 @@ int launch_gemm_tc(const GemmArgs& g, cudaStream_t st) {
     }
     p.ksplit = pl.ksplit;
     p.stages_per_split = pl.stages_per_split;
+    if (!partials && pl.ksplit == 1 && p.vec_store) {
+        // one box = what a promotion warp stages per pass: 32 rows x (its columns, or half of them for 4-byte elements)
+        const int cols = bn / kPW;
+        rc = cached_output_map(&tm.c, dev, g.C, esz, g.M, g.N, g.ldc, 32, esz == 2 ? cols : cols / 2);
+        if (rc != BI8_OK) return rc;
+        p.tma_store = 1;
+    }
     p.ws = static_cast<float*>(g.workspace);
     const int64_t items = tiles * pl.ksplit;
     const int grid = (int)(items < di.sms ? items : di.sms);
     const bool seed = (g.flags & BI8_GEMM_NO_SEED) == 0;
-    int var = 0;
-#if BI8_TC_VARIANTS
-    if (const char* e = std::getenv("BI8_TC_VAR")) var = std::atoi(e);
-#endif
     switch (g.block) {
-        case 32: rc = launch_qb<32>(tm, p, grid, partials, seed, var, st); break;
-        case 64: rc = launch_qb<64>(tm, p, grid, partials, seed, var, st); break;
-        case 128: rc = launch_qb<128>(tm, p, grid, partials, seed, var, st); break;
+        case 32: rc = launch_qb<32>(tm, p, grid, partials, seed, st); break;
+        case 64: rc = launch_qb<64>(tm, p, grid, partials, seed, st); break;
+        case 128: rc = launch_qb<128>(tm, p, grid, partials, seed, st); break;
         default: return fail(BI8_ERR_BLOCK, "tensor-core GEMM supports block 32, 64, 128 (got %d)", g.block);
     }
     if (rc != BI8_OK || pl.ksplit == 1) return rc;

@@ -72,13 +72,28 @@ inline int make_scale_map(CUtensorMap* map, const float* ptr, int64_t nb, int64_
     return BI8_OK;
 }
 
+// Output [rows, cols] row-major of 2- or 4-byte elements with row pitch ld elements (16-byte aligned base and pitch) ->
+// boxes of box_cols columns x box_rows rows, no swizzle; a store writes only the part of a box that lies inside the tensor.
+inline int make_output_map(CUtensorMap* map, void* ptr, int esz, int64_t rows, int64_t cols, int64_t ld, int box_rows, int box_cols) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(BI8_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t gstride[1] = {(cuuint64_t)ld * (cuuint64_t)esz};
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, esz == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, ptr, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(BI8_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with CUresult %d", (int)r);
+    return BI8_OK;
+}
+
 // ---- tensor-map cache ---------------------------------------------------------------------------------
 // Encoding a tensor map is a driver call of a few microseconds; a layer calls the GEMM with the same weight and scale
 // tensors every step.  A map depends only on (device, base address, extents, pitch, box), so encoded maps are kept in
 // a small table guarded by a mutex and looked up by those values (a stale entry for a freed and re-used address is
 // still a correct description of that address).
 struct MapKey {
-    int dev, kind;            // kind 0: int8 operand, 1: fp32 scales
+    int dev, kind;            // kind 0: int8 operand, 1: fp32 scales, 2 / 4: output of 2- / 4-byte elements
     const void* ptr;
     int64_t rows, cols, ld;
     int box_rows, box_cols;
@@ -143,6 +158,15 @@ inline int cached_scale_map(CUtensorMap* map, int dev, const float* ptr, int64_t
     const MapKey key{dev, 1, ptr, nb, cols, cols, box_blocks, box_cols};
     if (map_cache().find(key, map)) return BI8_OK;
     const int rc = make_scale_map(map, ptr, nb, cols, box_cols, box_blocks);
+    if (rc == BI8_OK) map_cache().put(key, *map);
+    return rc;
+}
+
+inline int cached_output_map(CUtensorMap* map, int dev, void* ptr, int esz, int64_t rows, int64_t cols, int64_t ld, int box_rows,
+                             int box_cols) {
+    const MapKey key{dev, esz, ptr, rows, cols, ld, box_rows, box_cols};
+    if (map_cache().find(key, map)) return BI8_OK;
+    const int rc = make_output_map(map, ptr, esz, rows, cols, ld, box_rows, box_cols);
     if (rc == BI8_OK) map_cache().put(key, *map);
     return rc;
 }

@@ -259,9 +259,10 @@ def extras(dev, hbm_gbs, flush):
     the fill's dirty lines to a kernel of a few tens of microseconds."""
     import block_linear_config as cfg
     from triton_functions import (dequantize_block_rowwise, int8_matmul_block64_rowwise_dequantize,
-                                  quantize_block_colwise, quantize_block_rowwise, quantize_matmul_block_rowwise_dequantize)
+                                  quantize_block_colwise, quantize_block_dual, quantize_block_rowwise,
+                                  quantize_matmul_block_rowwise_dequantize)
     cfg.GROUP_SIZE, cfg.INPUT_OUTPUT_TORCH_TYPE = BLOCK, torch.bfloat16
-    out = {"quantize": [], "dequantize": [], "quantize_colwise": [], "gemm": []}
+    out = {"quantize": [], "dequantize": [], "quantize_colwise": [], "quantize_dual": [], "gemm": []}
     for n in (4096, 8192, 16384):
         copies = max(2, -(-(300 << 20) // (n * n * 2)) + 1)
         xs, qs, ss = [], [], []
@@ -275,13 +276,16 @@ def extras(dev, hbm_gbs, flush):
             ss.append(s)
         nbytes = n * n * (2 + 1 + 4 / BLOCK)
         reps = 2 * copies
-        for key, fn in (("quantize", lambda i: quantize_block_rowwise(xs[i % copies])),
-                        ("dequantize", lambda i: dequantize_block_rowwise(qs[i % copies], ss[i % copies])),
-                        ("quantize_colwise", lambda i: quantize_block_colwise(xs[i % copies]))):
+        # the dual quantizer reads the input once and writes both int8 results: 2 + 2 * (1 + 4/block) bytes per element
+        dual_bytes = n * n * (2 + 2 * (1 + 4 / BLOCK))
+        for key, fn, nb_ in (("quantize", lambda i: quantize_block_rowwise(xs[i % copies]), nbytes),
+                             ("dequantize", lambda i: dequantize_block_rowwise(qs[i % copies], ss[i % copies]), nbytes),
+                             ("quantize_colwise", lambda i: quantize_block_colwise(xs[i % copies]), nbytes),
+                             ("quantize_dual", lambda i: quantize_block_dual(xs[i % copies]), dual_bytes)):
             ms = time_graph(fn, reps)
             ms_flushed = time_kernel(lambda: fn(0), 7, flush)
-            out[key].append({"shape": [n, n], "us": ms * 1e3, "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / hbm_gbs,
-                             "us_flushed": ms_flushed * 1e3, "frac_hbm_flushed": nbytes / ms_flushed / 1e6 / hbm_gbs})
+            out[key].append({"shape": [n, n], "us": ms * 1e3, "gbs": nb_ / ms / 1e6, "frac_hbm": nb_ / ms / 1e6 / hbm_gbs,
+                             "us_flushed": ms_flushed * 1e3, "frac_hbm_flushed": nb_ / ms_flushed / 1e6 / hbm_gbs})
         del xs, qs, ss
     # Llama-7B projection shapes.  "us" times the GEMM on pre-quantized activations, "us_linear" the layer's forward from
     # bf16 activations (quantize + GEMM: for M <= 64 one library call whose kernels overlap).  Launches of a few

@@ -14,6 +14,7 @@ from .triton_functions import (
     dequantize_block_rowwise,
     int8_matmul_block64_rowwise_dequantize,
     quantize_block_colwise,
+    quantize_block_dual,
     quantize_block_rowwise,
     quantize_matmul_block_rowwise_dequantize,
 )
@@ -76,15 +77,25 @@ class blockwise_int8_linear(torch.autograd.Function):
     (``block_linear.py:69-112``).  X and W are re-quantized on every call, as in the reference (unless
     ``CACHE_QUANTIZED_WEIGHTS`` is set); the transposed operands of the backward GEMMs are quantized straight from
     the row-major tensors by the fused column-wise quantizer, which is bit-identical to ``t().contiguous()`` +
-    row-wise quantize."""
+    row-wise quantize.  With ``FUSE_DUAL_QUANTIZE`` (default) X and G are each read once for both of their
+    quantizations, and the backward pass keeps X as its transposed int8 copy; every result is unchanged."""
 
     @staticmethod
     def forward(ctx, X_3D, W, bias):
         X = X_3D.reshape(-1, X_3D.size(-1))
-        ctx.save_for_backward(X, W)
         ctx.has_bias = bias is not None
         ctx.wcache = cache = _weight_cache(W)
-        X_int8, state_X = quantize_block_rowwise(X)
+        if ctx.needs_input_grad[1] and getattr(block_linear_config, "FUSE_DUAL_QUANTIZE", True):
+            # the weight gradient needs X blocked along the tokens (block_linear.py:100-101): both quantizations come
+            # from one read of X, and the backward pass keeps the int8 transposed copy instead of X itself
+            X_int8, state_X, Xt_int8, state_Xt = quantize_block_dual(X)
+            ctx.save_for_backward(Xt_int8, state_Xt, W)
+            ctx.x_quantized = True
+            ctx.block = block_linear_config.GROUP_SIZE
+        else:
+            X_int8, state_X = quantize_block_rowwise(X)
+            ctx.save_for_backward(X, W)
+            ctx.x_quantized = False
         if cache is not None and "row" in cache:
             W_int8, state_W = cache["row"]
         else:
@@ -97,11 +108,21 @@ class blockwise_int8_linear(torch.autograd.Function):
     @staticmethod
     def backward(ctx, G_3D):
         G = G_3D.reshape(-1, G_3D.size(-1))
-        X, W = ctx.saved_tensors
+        if ctx.x_quantized:
+            if ctx.block != block_linear_config.GROUP_SIZE:
+                raise RuntimeError("GROUP_SIZE changed between the forward and the backward pass of a BlockInt8Linear")
+            x_int8, x_state, W = ctx.saved_tensors
+        else:
+            X, W = ctx.saved_tensors
         grad_X = grad_W = grad_bias = None
+        gt_int8 = None
+        if ctx.needs_input_grad[0] and ctx.needs_input_grad[1] and getattr(block_linear_config, "FUSE_DUAL_QUANTIZE", True):
+            # G is needed blocked along N (for dX) and along the tokens (for dW): one read
+            g_int8, g_state, gt_int8, gt_state = quantize_block_dual(G)
+        elif ctx.needs_input_grad[0]:
+            g_int8, g_state = quantize_block_rowwise(G)
         if ctx.needs_input_grad[0]:
             # contraction over N: both operands blocked along N (block_linear.py:92-95)
-            g_int8, g_state = quantize_block_rowwise(G)
             cache = ctx.wcache         # still valid: autograd refuses to run backward on a weight modified since forward
             if cache is not None and "col" in cache:
                 Wt_int8, w_state = cache["col"]
@@ -113,8 +134,10 @@ class blockwise_int8_linear(torch.autograd.Function):
             grad_X = grad_X.view(*G_3D.size()[:-1], -1)
         if ctx.needs_input_grad[1]:
             # contraction over the tokens: both operands blocked along M (block_linear.py:100-104)
-            x_int8, x_state = quantize_block_colwise(X)                      # [K, M], state [M/B, K]
-            gt_int8, gt_state = quantize_block_colwise(G)                    # [N, M], state [M/B, N]
+            if not ctx.x_quantized:
+                x_int8, x_state = quantize_block_colwise(X)                  # [K, M], state [M/B, K]
+            if gt_int8 is None:
+                gt_int8, gt_state = quantize_block_colwise(G)                # [N, M], state [M/B, N]
             grad_W = int8_matmul_block64_rowwise_dequantize(gt_int8, x_int8.t(), gt_state, x_state)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             grad_bias = G.sum(dim=0)

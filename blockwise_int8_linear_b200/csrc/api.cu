@@ -143,6 +143,23 @@ int bi8_quantize_colwise(const void* x, int x_dtype, int64_t ldx, int8_t* q, flo
     return launch_quantize_colwise(x, x_dtype, ldx, q, s, R, C, block, static_cast<cudaStream_t>(stream));
 }
 
+int bi8_quantize_dual(const void* x, int x_dtype, int64_t ldx, int8_t* q_row, float* s_row, int8_t* q_col, float* s_col, int64_t R,
+                      int64_t C, int block, void* stream) {
+    if (!dtype_ok(x_dtype)) return fail(BI8_ERR_DTYPE, "quantize_dual: unknown dtype code %d", x_dtype);
+    if (block < 1) return fail(BI8_ERR_BLOCK, "quantize_dual: block size %d", block);
+    if (R < 0 || C < 0 || ldx < C) return fail(BI8_ERR_SHAPE, "quantize_dual: bad shape R=%lld C=%lld ldx=%lld", (long long)R, (long long)C, (long long)ldx);
+    if (R == 0 || C == 0) return BI8_OK;
+    if (!x || !q_row || !s_row || !q_col || !s_col) return fail(BI8_ERR_NULL, "quantize_dual: null pointer");
+    if (!aligned(x, dtype_size(x_dtype)) || !aligned(s_row, 4) || !aligned(s_col, 4)) return fail(BI8_ERR_ALIGN, "quantize_dual: pointer not element aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (quantize_tile_applicable(x, x_dtype, ldx, q_col, q_row, R, C, block))
+        return launch_quantize_tile(x, x_dtype, ldx, q_col, s_col, q_row, s_row, R, C, block, st);
+    // shapes the one-pass kernel does not take: the two single-purpose quantizers, same results
+    const int rc = launch_quantize_rowwise(x, x_dtype, ldx, q_row, s_row, R, C, block, st);
+    if (rc != BI8_OK) return rc;
+    return launch_quantize_colwise(x, x_dtype, ldx, q_col, s_col, R, C, block, st);
+}
+
 int bi8_dequantize_rowwise(const int8_t* q, const float* s, void* out, int out_dtype, int64_t M, int64_t K, int block,
                            void* stream) {
     if (!dtype_ok(out_dtype)) return fail(BI8_ERR_DTYPE, "dequantize: unknown dtype code %d", out_dtype);

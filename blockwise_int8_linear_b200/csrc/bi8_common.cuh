@@ -50,6 +50,10 @@ int launch_quantize_rowwise(const void* x, int dt, int64_t ldx, int8_t* q, float
                             int block, cudaStream_t st);
 int launch_quantize_colwise(const void* x, int dt, int64_t ldx, int8_t* q, float* s, int64_t R, int64_t C,
                             int block, cudaStream_t st);
+// tile quantizer (quantize_tile.cu): column-wise result, and with q_row != nullptr the row-wise result of the same input
+bool quantize_tile_applicable(const void* x, int dt, int64_t ldx, const void* q_col, const void* q_row, int64_t R, int64_t C, int block);
+int launch_quantize_tile(const void* x, int dt, int64_t ldx, int8_t* q_col, float* s_col, int8_t* q_row, float* s_row, int64_t R,
+                         int64_t C, int block, cudaStream_t st);
 int launch_dequantize_rowwise(const int8_t* q, const float* s, void* out, int dt, int64_t M, int64_t K,
                               int block, cudaStream_t st);
 

@@ -729,6 +729,8 @@ int launch_quantize_rowwise(const void* x, int dt, int64_t ldx, int8_t* q, float
 
 int launch_quantize_colwise(const void* x, int dt, int64_t ldx, int8_t* q, float* s, int64_t R, int64_t C, int block,
                             cudaStream_t st) {
+    if (quantize_tile_applicable(x, dt, ldx, q, nullptr, R, C, block))
+        return launch_quantize_tile(x, dt, ldx, q, s, nullptr, nullptr, R, C, block, st);
     switch (dt) {
         case BI8_BF16: return quantize_colwise_t(static_cast<const __nv_bfloat16*>(x), ldx, q, s, R, C, block, st);
         case BI8_F16: return quantize_colwise_t(static_cast<const __half*>(x), ldx, q, s, R, C, block, st);

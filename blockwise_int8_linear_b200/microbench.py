@@ -23,7 +23,7 @@ if ROOT not in sys.path:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["quantize", "dequantize", "colwise", "gemm"])
+    ap.add_argument("op", choices=["quantize", "dequantize", "colwise", "dual", "gemm"])
     ap.add_argument("dims", type=int, nargs="+")
     ap.add_argument("--block", type=int, default=64)
     ap.add_argument("--reps", type=int, default=7)
@@ -52,9 +52,9 @@ def main():
         x = torch.randn((m, k), device=dev, generator=g).to(torch.bfloat16)
         q, s = F.quantize_block_rowwise(x)
         fn = {"quantize": lambda: F.quantize_block_rowwise(x), "dequantize": lambda: F.dequantize_block_rowwise(q, s),
-              "colwise": lambda: F.quantize_block_colwise(x)}[a.op]
+              "colwise": lambda: F.quantize_block_colwise(x), "dual": lambda: F.quantize_block_dual(x)}[a.op]
         work = 0.0
-        nbytes = m * k * (2 + 1 + 4.0 / a.block)
+        nbytes = m * k * (2 + (2 if a.op == "dual" else 1) * (1 + 4.0 / a.block))
     flush = None if a.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     for _ in range(a.warmup):
         fn()

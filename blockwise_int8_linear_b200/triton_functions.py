@@ -19,7 +19,7 @@ from . import _lib
 from . import block_linear_config
 
 __all__ = [
-    "ceil_div", "quantize_block_rowwise", "quantize_block_colwise", "dequantize_block_rowwise",
+    "ceil_div", "quantize_block_rowwise", "quantize_block_colwise", "quantize_block_dual", "dequantize_block_rowwise",
     "int8_matmul_block64_rowwise_dequantize", "quantize_matmul_block_rowwise_dequantize", "int8_matmul_block_partials",
     "fast_matmulT",
 ]
@@ -110,6 +110,27 @@ def quantize_block_colwise(x: torch.Tensor, fblock_size=None):
                                              block, _lib.stream_ptr())
     _lib.check(rc, "bi8_quantize_colwise")
     return output, output_maxs
+
+
+def quantize_block_dual(x: torch.Tensor, fblock_size=None):
+    """``quantize_block_rowwise(x)`` and ``quantize_block_colwise(x)`` from one read of ``x`` ``[R, C]``: returns
+    ``(q_row [R, C], state_row [ceil(C/block), R], q_col [C, R], state_col [ceil(R/block), C])``, each bit-identical to its
+    single-purpose function.  The layer needs both for its input (forward GEMM and weight gradient,
+    ``block_linear.py:78, 100-101``) and for the output gradient (``block_linear.py:92, 102-103``)."""
+    block = _block(fblock_size)
+    r, c = x.shape
+    assert x.is_cuda
+    x = _rows_contiguous(x)
+    code = _lib.dtype_code(x.dtype)
+    q_row = torch.empty((r, c), device=x.device, dtype=torch.int8)
+    s_row = torch.empty((ceil_div(c, block), r), device=x.device, dtype=_scale_dtype())
+    q_col = torch.empty((c, r), device=x.device, dtype=torch.int8)
+    s_col = torch.empty((ceil_div(r, block), c), device=x.device, dtype=_scale_dtype())
+    with _on_device(x):
+        rc = _lib.lib().bi8_quantize_dual(_lib.ptr(x), code, _pitch(x), _lib.ptr(q_row), _lib.ptr(s_row), _lib.ptr(q_col),
+                                          _lib.ptr(s_col), r, c, block, _lib.stream_ptr())
+    _lib.check(rc, "bi8_quantize_dual")
+    return q_row, s_row, q_col, s_col
 
 
 def dequantize_block_rowwise(x: torch.Tensor, state_x: torch.Tensor, fblock_size=None):

@@ -84,6 +84,12 @@ BI8_API int bi8_quantize_rowwise(const void* x, int x_dtype, int64_t ldx, int8_t
 BI8_API int bi8_quantize_colwise(const void* x, int x_dtype, int64_t ldx, int8_t* q, float* s,
                          int64_t R, int64_t C, int block, void* stream);
 
+/* Both quantizations of one tensor from a single read: q_row [R,C] / s_row [ceil(C/block), R] as bi8_quantize_rowwise
+ * gives them and q_col [C,R] / s_col [ceil(R/block), C] as bi8_quantize_colwise gives them, bit for bit.  Replaces the pairs
+ * of calls at block_linear.py:78 + 100-101 (X: forward and weight gradient) and 92 + 102-103 (the output gradient). */
+BI8_API int bi8_quantize_dual(const void* x, int x_dtype, int64_t ldx, int8_t* q_row, float* s_row, int8_t* q_col, float* s_col,
+                      int64_t R, int64_t C, int block, void* stream);
+
 /* Replaces dequantize_block_rowwise (triton_functions.py:492-500, kernel 467-490).
  * out[m,k] = cast((s[k/block, m] * float(q[m,k])) * fl32(1/127)), out [M,K] contiguous of out_dtype. */
 BI8_API int bi8_dequantize_rowwise(const int8_t* q, const float* s, void* out, int out_dtype,

@@ -237,3 +237,40 @@ def test_cached_quantized_weights_in_training():
     finally:
         cfg.CACHE_QUANTIZED_WEIGHTS = False
     assert_clean_device()
+
+
+@pytest.mark.parametrize("shape", [(4, 96, 256, 384), (1, 130, 200, 72)])
+def test_fused_dual_quantize_changes_no_result(shape):
+    """X and G read once for both of their quantizations (the default) against the separate quantizers: y, dX, dW and db
+    must be bit-identical, with a frozen weight and with a frozen input as well, for shapes the one-pass kernel takes and
+    for shapes that fall back to the two single kernels."""
+    import block_linear_config as cfg
+    from block_linear import BlockInt8Linear
+    b, t, k, n = shape
+    set_config(64, torch.bfloat16)
+    lin = BlockInt8Linear(k, n, bias=True, device=DEV, dtype=torch.bfloat16)
+    g = torch.Generator(device=DEV).manual_seed(3)
+    go = torch.randn((b, t, n), device=DEV, generator=g).to(torch.bfloat16)
+    results = {}
+    try:
+        for fused in (True, False):
+            cfg.FUSE_DUAL_QUANTIZE = fused
+            for x_grad, w_grad in ((True, True), (False, True), (True, False)):
+                x = torch.randn((b, t, k), device=DEV, generator=torch.Generator(device=DEV).manual_seed(5)).to(torch.bfloat16)
+                x.requires_grad_(x_grad)
+                lin.weight.requires_grad_(w_grad)
+                lin.weight.grad = lin.bias.grad = None
+                y = lin(x)
+                y.backward(go)
+                results[(fused, x_grad, w_grad)] = (y.detach().clone(), None if x.grad is None else x.grad.clone(),
+                                                    None if lin.weight.grad is None else lin.weight.grad.clone(),
+                                                    lin.bias.grad.clone())
+    finally:
+        cfg.FUSE_DUAL_QUANTIZE = True
+        lin.weight.requires_grad_(True)
+    for x_grad, w_grad in ((True, True), (False, True), (True, False)):
+        for a, c in zip(results[(True, x_grad, w_grad)], results[(False, x_grad, w_grad)]):
+            assert (a is None) == (c is None)
+            if a is not None:
+                assert torch.equal(a, c)
+    assert_clean_device()

@@ -132,6 +132,50 @@ def test_colwise_equals_transpose_then_rowwise(shape, block):
     assert torch.equal(q.cpu(), q_ref)
 
 
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("block", [32, 64, 128, 48])
+@pytest.mark.parametrize("shape", [(128, 128), (256, 384), (208, 144), (48, 1008), (1008, 48), (8192, 768), (4096, 4096),
+                                   (70, 33), (200, 136), (130, 50257)])
+def test_dual_equals_both_single_quantizers(shape, block, dt):
+    """One read, both quantizations: each output must be bit-identical to its single-purpose function and to the
+    oracle (zero columns, NaN-free outliers and ragged tile edges included; shapes the one-pass kernel does not take go
+    through the two single kernels)."""
+    from triton_functions import quantize_block_colwise, quantize_block_dual, quantize_block_rowwise
+    x = randn_bf16(shape, 3 * shape[0] + shape[1], outliers=0.01).to(dt)
+    x[:, 1] = 0                                     # a column of zeros: scale 0, result 0
+    x[0, :] = 0
+    xd = x.to(DEV)
+    q_row, s_row, q_col, s_col = quantize_block_dual(xd, block)
+    q1, s1 = quantize_block_rowwise(xd, block)
+    q2, s2 = quantize_block_colwise(xd, block)
+    assert torch.equal(q_row, q1) and torch.equal(s_row, s1)
+    assert torch.equal(q_col, q2) and torch.equal(s_col, s2)
+    if shape[0] * shape[1] <= 1 << 22:
+        qr, sr = O.quantize(x.float() if dt == torch.float16 else x, block)
+        qc, sc = O.quantize((x.float() if dt == torch.float16 else x).t().contiguous(), block)
+        assert torch.equal(q_row.cpu(), qr) and torch.equal(s_row.cpu(), sr)
+        assert torch.equal(q_col.cpu(), qc) and torch.equal(s_col.cpu(), sc)
+    assert_clean_device()
+
+
+def test_dual_strided_rows_and_extremes():
+    """Row pitch larger than the row, values at the ends of the bf16 range, and a block whose only nonzero is subnormal in
+    fp32 terms (the exact-division shortcut must hand over to the IEEE division there)."""
+    from triton_functions import quantize_block_colwise, quantize_block_dual, quantize_block_rowwise
+    base = randn_bf16((256, 512), 5).to(DEV)
+    base[3, 130] = 3.0e38
+    base[64:128, 200] = 1e-38
+    base[64:128, 201] = 0
+    base[70, 201] = 1e-39
+    view = base[:, 128:384]
+    q_row, s_row, q_col, s_col = quantize_block_dual(view, 64)
+    q1, s1 = quantize_block_rowwise(view, 64)
+    q2, s2 = quantize_block_colwise(view, 64)
+    assert torch.equal(q_row, q1) and torch.equal(s_row, s1) and torch.equal(q_col, q2) and torch.equal(s_col, s2)
+    qc, sc = O.quantize(view.cpu().t().contiguous(), 64)
+    assert torch.equal(q_col.cpu(), qc) and torch.equal(s_col.cpu(), sc)
+
+
 def test_colwise_fp32():
     from triton_functions import quantize_block_colwise
     x = torch.randn((130, 72), generator=torch.Generator().manual_seed(3))

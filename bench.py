@@ -404,7 +404,12 @@ def tp_bench(dev, rank, world, hbm_gbs):
         x = torch.randn((M, d), device=dev, generator=torch.Generator(device=dev).manual_seed(7000)).to(torch.bfloat16)
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
 
-        def pair(i, timed=False):
+        peer = None
+        if world > 1 and M <= 64:
+            from blockwise_int8_linear_b200.peer import PeerAllReduce
+            peer = PeerAllReduce(M * d, dev)
+
+        def pair(i, timed=False, use_peer=False):
             wq_gu, s_gu = gus[i % copies]
             wq_dn, s_dn = dns[i % copies]
             if timed:
@@ -427,7 +432,9 @@ def tp_bench(dev, rank, world, hbm_gbs):
                 cfg.INPUT_OUTPUT_TORCH_TYPE = torch.bfloat16
             if timed:
                 ev[1].record()
-            if world > 1:
+            if world > 1 and use_peer:
+                y = peer(part)
+            elif world > 1:
                 dist.all_reduce(part)
                 y = part.to(torch.bfloat16)
             else:
@@ -463,6 +470,27 @@ def tp_bench(dev, rank, world, hbm_gbs):
                     "tokens_per_s": M / (ms_pair * 1e-3), "rank_roofline_ms": roof_ms, "frac_of_rank_roofline": roof_ms / ms_pair,
                     "timing": "CUDA events, median of 15 eager steps, max over ranks; " +
                               ("weights rotate over copies larger than L2" if M <= 64 else "operands larger than L2")}
+        if peer is not None:
+            # the same pair with the library's peer-memory reduction (one kernel, plain stores over NVLink) instead of NCCL
+            for i in range(5):
+                pair(i, use_peer=True)
+            torch.cuda.synchronize()
+            dist.barrier()
+            tot, comp = [], []
+            for i in range(15):
+                dist.barrier()
+                pair(i, timed=True, use_peer=True)
+                ev[2].synchronize()
+                comp.append(ev[0].elapsed_time(ev[1]))
+                tot.append(ev[0].elapsed_time(ev[2]))
+            tot.sort()
+            comp.sort()
+            t = torch.tensor([tot[len(tot) // 2], comp[len(comp) // 2]], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            out[tag]["peer_reduce"] = {"kernel": "bi8_peer_allreduce (st.global to every rank's slots, flag per chunk, sum in rank order)",
+                                       "ms_per_pair": t[0].item(), "ms_reduce": (t[0] - t[1]).item()}
+            from blockwise_int8_linear_b200 import _lib
+            _lib.device_status()
         del gus, dns
     return out
 

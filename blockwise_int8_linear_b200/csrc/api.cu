@@ -160,6 +160,19 @@ int bi8_quantize_dual(const void* x, int x_dtype, int64_t ldx, int8_t* q_row, fl
     return launch_quantize_colwise(x, x_dtype, ldx, q_col, s_col, R, C, block, st);
 }
 
+size_t bi8_peer_allreduce_buffer_bytes(int world, int64_t capacity) {
+    if (world < 1 || world > 8 || capacity <= 0 || capacity % 1024 != 0) return 0;
+    return peer_allreduce_buffer_bytes(world, capacity);
+}
+
+int bi8_peer_allreduce(void* const* peer_bufs, int rank, int world, int64_t capacity, const float* partial, int64_t M, int64_t N,
+                       const void* bias, int bias_dtype, void* out, int out_dtype, unsigned wait_limit_us, void* stream) {
+    if (!peer_bufs || !partial || !out) return fail(BI8_ERR_NULL, "peer all-reduce: null pointer");
+    if (!dtype_ok(out_dtype) || (bias && !dtype_ok(bias_dtype))) return fail(BI8_ERR_DTYPE, "peer all-reduce: unknown dtype code");
+    return launch_peer_allreduce(peer_bufs, rank, world, capacity, partial, M, N, bias, bias_dtype, out, out_dtype, wait_limit_us,
+                                 static_cast<cudaStream_t>(stream));
+}
+
 int bi8_dequantize_rowwise(const int8_t* q, const float* s, void* out, int out_dtype, int64_t M, int64_t K, int block,
                            void* stream) {
     if (!dtype_ok(out_dtype)) return fail(BI8_ERR_DTYPE, "dequantize: unknown dtype code %d", out_dtype);

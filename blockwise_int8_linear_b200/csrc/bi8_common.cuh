@@ -54,6 +54,10 @@ int launch_quantize_colwise(const void* x, int dt, int64_t ldx, int8_t* q, float
 bool quantize_tile_applicable(const void* x, int dt, int64_t ldx, const void* q_col, const void* q_row, int64_t R, int64_t C, int block);
 int launch_quantize_tile(const void* x, int dt, int64_t ldx, int8_t* q_col, float* s_col, int8_t* q_row, float* s_row, int64_t R,
                          int64_t C, int block, cudaStream_t st);
+// sum of the ranks' fp32 partial results over peer memory (peer_reduce.cu)
+size_t peer_allreduce_buffer_bytes(int world, int64_t capacity);
+int launch_peer_allreduce(void* const* peer_bufs, int rank, int world, int64_t capacity, const float* partial, int64_t M, int64_t N,
+                          const void* bias, int bias_dtype, void* out, int out_dtype, unsigned wait_limit_us, cudaStream_t st);
 int launch_dequantize_rowwise(const int8_t* q, const float* s, void* out, int dt, int64_t M, int64_t K,
                               int block, cudaStream_t st);
 

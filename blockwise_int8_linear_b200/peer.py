@@ -1,0 +1,88 @@
+"""Sum of the fp32 partial results of a row-parallel ``BlockInt8Linear`` over NVLink peer memory.
+
+The reference has no multi-GPU path; a Llama MLP sharded the usual way (``gate_up`` by columns, ``down`` by input
+features, ``block_linear.py:141-143`` per shard) ends every layer half with a sum of ``[M, hidden]`` fp32 partial results
+over the ranks.  ``PeerAllReduce`` does that sum with the library's own kernel (``bi8_peer_allreduce``: plain stores into
+every rank's exchange buffer, a flag per chunk and rank, a bounded wait, the sum in rank order) instead of an NCCL call,
+so that a decode step can be captured in one CUDA graph per rank with no host work between its kernels.
+
+The exchange buffers come from ``torch.distributed._symmetric_memory`` (one allocation per rank, mapped by all ranks of
+the group); only this library's kernel ever reads or writes them.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+import torch.distributed as dist
+
+from . import _lib, block_linear_config
+
+__all__ = ["PeerAllReduce"]
+
+_CHUNK = 1024
+
+
+class PeerAllReduce:
+    """``PeerAllReduce(capacity, device, group)(partial, bias)`` -> ``cast(sum over ranks of partial) + bias``.
+
+    ``capacity``: largest ``M * N`` (fp32 values) one call will carry.  With a group of one rank (or no process group)
+    the buffer is ordinary device memory and the call is a cast + bias."""
+
+    def __init__(self, capacity: int, device, group=None, _local_world: int = 0):
+        self.device = torch.device(device)
+        self.capacity = -(-int(capacity) // _CHUNK) * _CHUNK
+        if _local_world:
+            # test hook: `_local_world` exchange buffers on this one device, this object acting as rank 0 of them
+            self.rank, self.world = 0, _local_world
+        elif dist.is_initialized() and dist.get_world_size(group) > 1:
+            self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        else:
+            self.rank, self.world = 0, 1
+        if self.world > 8:
+            raise ValueError("PeerAllReduce supports at most 8 ranks")
+        L = _lib.lib()
+        nbytes = L.bi8_peer_allreduce_buffer_bytes(self.world, self.capacity)
+        if nbytes == 0:
+            raise ValueError(f"bad exchange buffer geometry: world {self.world}, capacity {self.capacity}")
+        if self.world == 1 or _local_world:
+            self._bufs = [torch.zeros(nbytes, dtype=torch.uint8, device=self.device) for _ in range(self.world)]
+            ptrs = [b.data_ptr() for b in self._bufs]
+        else:
+            # plain peer mappings are all this needs: keep the allocation off NVLink multicast objects
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed._symmetric_memory as symm
+            pg = group if group is not None else dist.group.WORLD
+            name = pg.group_name
+            enable = getattr(symm, "enable_symm_mem_for_group", None)
+            if enable is not None:
+                try:
+                    enable(name)
+                except Exception:       # newer torch versions need no registration
+                    pass
+            buf = symm.empty(nbytes, dtype=torch.uint8, device=self.device)
+            buf.zero_()
+            self._handle = symm.rendezvous(buf, name)
+            self._bufs = [buf]
+            ptrs = [int(p) for p in self._handle.buffer_ptrs]
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group)         # every rank's buffer is zeroed before anybody's first kernel writes into it
+        self._ptrs = (ctypes.c_void_p * 8)(*(ptrs + [ptrs[0]] * (8 - len(ptrs))))
+
+    def __call__(self, partial: torch.Tensor, bias: torch.Tensor = None, out: torch.Tensor = None, wait_limit_us: int = 0):
+        if partial.dtype != torch.float32 or not partial.is_contiguous():
+            raise ValueError("partial must be a contiguous float32 tensor")
+        n = partial.shape[-1]
+        m = partial.numel() // n
+        out_dtype = block_linear_config.INPUT_OUTPUT_TORCH_TYPE
+        if out is None:
+            out = torch.empty(partial.shape, dtype=out_dtype, device=partial.device)
+        if bias is not None:
+            bias = bias.contiguous()
+        with torch.cuda.device(partial.device):
+            rc = _lib.lib().bi8_peer_allreduce(self._ptrs, self.rank, self.world, self.capacity, _lib.ptr(partial), m, n,
+                                               _lib.ptr(bias), _lib.dtype_code(bias.dtype) if bias is not None else 0,
+                                               _lib.ptr(out), _lib.dtype_code(out.dtype), int(wait_limit_us), _lib.stream_ptr())
+        _lib.check(rc, "bi8_peer_allreduce")
+        return out

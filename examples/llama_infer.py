@@ -171,10 +171,16 @@ class Layer(nn.Module):
         return x + group_sum(self.mlp_partial(x), x.dtype, self.down.world)
 
 
+PEER = None      # a blockwise_int8_linear_b200.peer.PeerAllReduce while the decode step uses the library's own reduction
+
+
 def group_sum(part, dtype, world):
-    """Sum of the ranks' row-parallel partial results (fp32 over NCCL), cast to the activation type."""
+    """Sum of the ranks' row-parallel partial results, cast to the activation type: the library's peer-memory kernel
+    when one is installed and the tensor fits its buffers (decode), else fp32 over NCCL (prefill)."""
     if world == 1:
         return part
+    if PEER is not None and part.numel() <= PEER.capacity:
+        return PEER(part.contiguous())
     dist.all_reduce(part)
     return part.to(dtype)
 
@@ -219,8 +225,17 @@ class Llama(nn.Module):
             x = layer(x, pos0, max_len, cis, mask, pos_dev)
         logits = self.local_logits(x)                              # [B, 1, V_local]
         if self.world > 1:
-            bufs = [torch.empty_like(logits) for _ in range(self.world)]
-            dist.all_gather(bufs, logits)
+            width = logits.shape[-1]
+            if PEER is not None and logits.shape[0] * width * self.world <= PEER.capacity:
+                # gather as a sum: every rank contributes its shard in place and zeros elsewhere
+                full = torch.zeros((logits.shape[0], 1, width * self.world), device=logits.device, dtype=torch.float32)
+                rank = dist.get_rank()
+                full[..., rank * width:(rank + 1) * width] = torch.nan_to_num(logits.float(), neginf=-3.0e38)
+                summed = PEER(full, out=torch.empty_like(full))
+                bufs = list(summed.split(width, dim=-1))
+            else:
+                bufs = [torch.empty_like(logits) for _ in range(self.world)]
+                dist.all_gather(bufs, logits)
             logits = self.join_logits(bufs)
         return logits
 
@@ -306,6 +321,12 @@ def run(a, rank, world, dev, eager=False):
         tok.copy_(lg.argmax(-1))
         pos_dev.add_(1)
 
+    global PEER
+    PEER = None
+    if world > 1 and not eager and getattr(a, "reduce", "peer") == "peer":
+        from blockwise_int8_linear_b200.peer import PeerAllReduce
+        widest = max(hi - lo for lo, hi in block_aligned_bounds(a.vocab, world, a.block))
+        PEER = PeerAllReduce(max(a.batch * a.hidden, a.batch * widest * world), dev)
     graph, pieces = None, None
     if not eager:
         side = torch.cuda.Stream()
@@ -316,7 +337,8 @@ def run(a, rank, world, dev, eager=False):
         torch.cuda.current_stream().wait_stream(side)
         tok.copy_(nxt)
         pos_dev.fill_(a.prompt)
-        if world == 1:
+        if world == 1 or PEER is not None:
+            # one graph for the whole step: with the peer-memory reduction there is no host work between its kernels
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 decode_step()
@@ -354,12 +376,18 @@ def run(a, rank, world, dev, eager=False):
     torch.cuda.synchronize()
     t_decode = time.perf_counter() - t0
     toks = torch.cat(out, dim=1)
+    if PEER is not None:
+        from blockwise_int8_linear_b200 import _lib
+        _lib.device_status()                                      # raises if a bounded flag wait gave up
+        PEER = None
     return {
         "model": f"llama-arch {a.layers}x{a.hidden} ffn {a.ffn} vocab {a.vocab}, random init N(0,0.02), BlockInt8Linear block {a.block}",
         "n_gpus": world, "batch": a.batch, "prompt": a.prompt, "decode": a.decode,
         "prefill_tokens_per_s": a.batch * a.prompt / t_prefill, "prefill_s": t_prefill, "first_prefill_s": t_first,
         "decode_tokens_per_s": a.batch * (a.decode - 1) / t_decode, "decode_ms_per_step": 1e3 * t_decode / max(1, a.decode - 1),
-        "decode_mode": "eager" if eager else ("cuda graph" if world == 1 else "cuda graphs between the collectives"),
+        "decode_mode": "eager" if eager else ("cuda graph" if world == 1 else
+                                              "one cuda graph, peer-memory reductions" if graph is not None else
+                                              "cuda graphs between the NCCL collectives"),
         "first_tokens": toks[0, :8].tolist(), "tokens": toks.tolist(),
     }
 
@@ -376,6 +404,8 @@ def main():
     ap.add_argument("--decode", type=int, default=128)
     ap.add_argument("--block", type=int, default=64)
     ap.add_argument("--eager", action="store_true", help="do not capture the decode step in a CUDA graph")
+    ap.add_argument("--reduce", choices=["peer", "nccl"], default="peer",
+                    help="tensor-parallel decode: the library's peer-memory reduction inside one CUDA graph, or NCCL between graphs")
     ap.add_argument("--out", default=None, help="also append the JSON line to this file")
     a = ap.parse_args()
     a.head_dim = a.hidden // a.heads

@@ -104,8 +104,11 @@ BI8_API int bi8_dequantize_rowwise(const int8_t* q, const float* s, void* out, i
  * workspace: bi8_gemm_workspace_bytes(M,N,K,block) bytes of 16-byte aligned device memory (may be NULL when that
  * is 0; without it small-M shapes run on slower kernels).  It is plain scratch: nothing has to be cleared, every
  * call overwrites what it later reads; calls that may run concurrently need separate workspaces.
- * The int32 partial sums are exact; the fp32 accumulation multiplies the three factors in a different
- * order than the reference (a few fp32 ulps per term). */
+ * The int32 partial sums are exact.  The fp32 accumulation of the tensor-core kernel for M > 64 evaluates a term as
+ * sB * fl(P * s) with s = sA/127^2 rounded to fp32 and then to 22 significant bits (relative error of s at most
+ * 2^-24 + 2^-22), one rounding for P*s and one for the fused multiply-add into the sum, where the reference rounds
+ * three times per term; the result stays within 12 * 2^-24 * sum_j |term_j| of the reference's.  The kernels for
+ * M <= 64 and the CUDA-core kernel evaluate every term in the reference's order. */
 BI8_API int bi8_gemm_dequant(const int8_t* A, int64_t lda, const int8_t* Bt, int64_t ldb,
                      const float* sA, const float* sB, const void* bias, int bias_dtype,
                      void* C, int64_t ldc, int out_dtype, int64_t M, int64_t N, int64_t K, int block,
@@ -163,6 +166,25 @@ BI8_API int bi8_stream_capture_id(void* stream, unsigned long long* id);
 BI8_API int bi8_gemm_wait_selftest(const int8_t* A, int64_t lda, const int8_t* Bt, int64_t ldb,
                            const float* sA, const float* sB, void* C, int64_t ldc, int out_dtype,
                            int64_t M, int64_t N, int64_t K, int block, unsigned wait_limit_us, int skip_stage, void* stream);
+
+/* Row-parallel layers (the contraction dimension of block_linear.py:141-143 divided over ranks on block boundaries)
+ * leave an fp32 partial result [M,N] on every rank; the layer's output is their sum in rank order, cast, plus bias.
+ * bi8_peer_allreduce does that sum with one kernel per rank over peer-mapped memory (plain loads and stores over
+ * NVLink, bounded flag waits), so that it can sit in a CUDA graph between the layer's GEMM and the next layer.
+ *   peer_bufs[r]  device address, valid on THIS device, of rank r's exchange buffer: bi8_peer_allreduce_buffer_bytes(world,
+ *                 capacity) bytes, 16-byte aligned, zero-filled once before the first call, mapped by every rank (for
+ *                 example a torch.distributed._symmetric_memory allocation, or CUDA IPC handles).  peer_bufs[rank] is
+ *                 this rank's own buffer.  capacity = fp32 values per rank and reduction, a multiple of 1024, >= M*N.
+ *   partial       this rank's [M,N] fp32 partial result (contiguous, 16-byte aligned), N a multiple of 4.
+ *   out           [M,N] contiguous of out_dtype = cast(sum over ranks in ascending order) (+ cast(bias) in the output type):
+ *                 bit-identical on all ranks.
+ *   wait_limit_us how long a CTA waits for the other ranks' flags (0 = one second); when it runs out the kernel records
+ *                 BI8_ERR_TIMEOUT (bi8_device_status) and returns without writing its part of `out`.
+ * Every rank must call it the same number of times with the same M and N.  world <= 8. */
+BI8_API size_t bi8_peer_allreduce_buffer_bytes(int world, int64_t capacity);
+BI8_API int bi8_peer_allreduce(void* const* peer_bufs, int rank, int world, int64_t capacity, const float* partial,
+                       int64_t M, int64_t N, const void* bias, int bias_dtype, void* out, int out_dtype,
+                       unsigned wait_limit_us, void* stream);
 
 /* Back-to-back tcgen05.mma kind::i8 issue rate of the current device: runs `iters` 128x256x32 MMAs per SM
  * with no loads or epilogue and returns the elapsed milliseconds in *ms (synchronises).  Used by the

@@ -223,3 +223,20 @@ def test_errors():
         dequantize_block_rowwise(torch.zeros((4, 64), dtype=torch.int8, device=DEV),
                                  torch.zeros((4, 1), dtype=torch.float32, device=DEV), 64)
     assert_clean_device()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs a second GPU")
+@pytest.mark.parametrize("shape", [(256, 384), (200, 136)])
+def test_colwise_block128_on_second_device(shape):
+    """Per-device kernel attributes: block 128 needs more than the default 48 KiB of dynamic shared memory in both
+    column-wise kernels (the TMA tile kernel takes the first shape, the shared-memory tile kernel the second), and the
+    opt-in must have been made on the device the call runs on, not only on the first device the process used."""
+    from triton_functions import quantize_block_colwise, quantize_block_dual
+    x = randn_bf16(shape, 77, outliers=0.01)
+    q0, s0 = quantize_block_colwise(x.to("cuda:0"), 128)
+    q1, s1 = quantize_block_colwise(x.to("cuda:1"), 128)
+    q_ref, s_ref = O.quantize(x.t().contiguous(), 128)
+    assert torch.equal(q0.cpu(), q_ref) and torch.equal(s0.cpu(), s_ref)
+    assert torch.equal(q1.cpu(), q_ref) and torch.equal(s1.cpu(), s_ref)
+    d = quantize_block_dual(x.to("cuda:1"), 128)
+    assert d[2].device.index == 1 and torch.equal(d[2].cpu(), q_ref) and torch.equal(d[3].cpu(), s_ref)

@@ -55,6 +55,28 @@ def _pitch(t: torch.Tensor) -> int:
     return t.stride(0) if t.shape[0] > 1 else max(t.shape[1], 1)
 
 
+def _pad16(x: torch.Tensor, block: int, rows: bool, cols: bool):
+    """Zero-padded copy of a large 16-bit ``x [R, C]`` whose row or column count is not a multiple of 16 (GPT-2's 50257-wide
+    logits and their gradient), or None when no padding is called for.
+
+    The fast quantizers and the tensor-core GEMM want 16-byte aligned rows; the kernels for unaligned rows move two bytes
+    per lane and run 5-8 x slower than one extra copy plus the fast kernel.  Padding with zeros changes no result: the
+    pad stays inside the last block (block sizes here are multiples of 16), and zeros change neither a block's absmax nor
+    the quantized values of its other elements."""
+    r, c = x.shape
+    if x.dtype not in (torch.bfloat16, torch.float16) or block % 16 != 0 or r * c < (1 << 22):
+        return None
+    rp = -(-r // 16) * 16 if rows else r
+    cp = -(-c // 16) * 16 if cols else c
+    if (rp, cp) == (r, c) or min(r, c) < 256:
+        return None
+    buf = torch.zeros((rp, cp), device=x.device, dtype=x.dtype) if rp != r else torch.empty((rp, cp), device=x.device, dtype=x.dtype)
+    if rp == r:
+        buf[:, c:].zero_()
+    buf[:r, :c].copy_(x)
+    return buf
+
+
 class _on_device:
     """Makes the tensor's device current for the duration of a library call (no-op when it already is)."""
 
@@ -83,6 +105,11 @@ def quantize_block_rowwise(x: torch.Tensor, fblock_size=None):
     block = _block(fblock_size)
     m, k = x.shape
     assert x.is_cuda
+    padded = _pad16(x, block, rows=False, cols=True) if x.dim() == 2 else None
+    if padded is not None:
+        # the result is a view with a 16-byte aligned row pitch, which the GEMM takes as it is
+        q, state = quantize_block_rowwise(padded, block)
+        return q[:, :k], state
     x = _rows_contiguous(x)
     code = _lib.dtype_code(x.dtype)
     output = torch.empty((m, k), device=x.device, dtype=torch.int8)
@@ -101,6 +128,10 @@ def quantize_block_colwise(x: torch.Tensor, fblock_size=None):
     block = _block(fblock_size)
     r, c = x.shape
     assert x.is_cuda
+    padded = _pad16(x, block, rows=True, cols=True) if x.dim() == 2 else None
+    if padded is not None:
+        q, state = quantize_block_colwise(padded, block)
+        return q[:c, :r], state[:, :c]
     x = _rows_contiguous(x)
     code = _lib.dtype_code(x.dtype)
     output = torch.empty((c, r), device=x.device, dtype=torch.int8)
@@ -120,6 +151,10 @@ def quantize_block_dual(x: torch.Tensor, fblock_size=None):
     block = _block(fblock_size)
     r, c = x.shape
     assert x.is_cuda
+    padded = _pad16(x, block, rows=True, cols=True) if x.dim() == 2 else None
+    if padded is not None:
+        q_row, s_row, q_col, s_col = quantize_block_dual(padded, block)
+        return q_row[:r, :c], s_row[:, :r], q_col[:c, :r], s_col[:, :c]
     x = _rows_contiguous(x)
     code = _lib.dtype_code(x.dtype)
     q_row = torch.empty((r, c), device=x.device, dtype=torch.int8)

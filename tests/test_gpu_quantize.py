@@ -240,3 +240,22 @@ def test_colwise_block128_on_second_device(shape):
     assert torch.equal(q1.cpu(), q_ref) and torch.equal(s1.cpu(), s_ref)
     d = quantize_block_dual(x.to("cuda:1"), 128)
     assert d[2].device.index == 1 and torch.equal(d[2].cpu(), q_ref) and torch.equal(d[3].cpu(), s_ref)
+
+
+@pytest.mark.parametrize("shape", [(4099, 1031), (1031, 4099), (4112, 1031)])
+def test_large_unaligned_tensors_are_padded_not_slowed(shape):
+    """Large 16-bit tensors whose row or column count is not a multiple of 16 (GPT-2's 50257-wide logits) are copied once
+    into a zero-padded buffer and go through the fast kernels; the results (returned as views of the padded outputs)
+    must equal the oracle's on the unpadded tensor, bit for bit."""
+    from triton_functions import quantize_block_colwise, quantize_block_dual, quantize_block_rowwise
+    x = randn_bf16(shape, 11 * shape[0] + shape[1], outliers=0.01)
+    xd = x.to(DEV)
+    qr_ref, sr_ref = O.quantize(x, 64)
+    qc_ref, sc_ref = O.quantize(x.t().contiguous(), 64)
+    q, s = quantize_block_rowwise(xd, 64)
+    assert tuple(q.shape) == shape and torch.equal(q.cpu(), qr_ref) and torch.equal(s.cpu(), sr_ref)
+    q, s = quantize_block_colwise(xd, 64)
+    assert tuple(q.shape) == shape[::-1] and torch.equal(q.cpu(), qc_ref) and torch.equal(s.cpu(), sc_ref)
+    a, b, c, d = quantize_block_dual(xd, 64)
+    assert torch.equal(a.cpu(), qr_ref) and torch.equal(b.cpu(), sr_ref) and torch.equal(c.cpu(), qc_ref) and torch.equal(d.cpu(), sc_ref)
+    assert_clean_device()

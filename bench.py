@@ -407,7 +407,15 @@ def tp_bench(dev, rank, world, hbm_gbs):
         peer = None
         if world > 1 and M <= 64:
             from blockwise_int8_linear_b200.peer import PeerAllReduce
-            peer = PeerAllReduce(M * d, dev)
+            try:
+                peer = PeerAllReduce(M * d, dev)
+            except Exception as e:       # no peer mapping on this machine: the NCCL figures stand alone
+                print(f"peer-memory reduction unavailable ({type(e).__name__}: {e})", file=sys.stderr)
+                peer = None
+            flag = torch.tensor([1 if peer is not None else 0], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if flag.item() == 0:
+                peer = None
 
         def pair(i, timed=False, use_peer=False):
             wq_gu, s_gu = gus[i % copies]
@@ -662,13 +670,19 @@ def run_ours(args):
     torch.cuda.empty_cache()
     tp = models = None
     if not args.no_tp:
-        tp = tp_bench(dev, rank, world, hbm_gbs)
+        try:
+            tp = tp_bench(dev, rank, world, hbm_gbs)
+        except Exception as e:            # the tensor-parallel pair must not take the headline down with it
+            tp = {"error": f"{type(e).__name__}: {e}"}
     if not args.no_models:
         try:
             models = models_bench(dev, rank, world, local)
         except Exception as e:            # a model driver must not take the headline down with it
             models = {"error": f"{type(e).__name__}: {e}"}
-    _lib.device_status()
+    try:
+        _lib.device_status()
+    except Exception as e:                # a bounded wait that gave up in one of the extras: reported, not fatal
+        (models if isinstance(models, dict) else {}).setdefault("device_status", str(e))
 
     if rank != 0:
         if world > 1:

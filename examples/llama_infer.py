@@ -326,7 +326,16 @@ def run(a, rank, world, dev, eager=False):
     if world > 1 and not eager and getattr(a, "reduce", "peer") == "peer":
         from blockwise_int8_linear_b200.peer import PeerAllReduce
         widest = max(hi - lo for lo, hi in block_aligned_bounds(a.vocab, world, a.block))
-        PEER = PeerAllReduce(max(a.batch * a.hidden, a.batch * widest * world), dev)
+        try:
+            PEER = PeerAllReduce(max(a.batch * a.hidden, a.batch * widest * world), dev)
+        except Exception as e:                                  # no peer mapping on this machine: NCCL between graphs
+            print(f"peer-memory reduction unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
+            PEER = None
+        # all ranks take the same path
+        flag = torch.tensor([1 if PEER is not None else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if flag.item() == 0:
+            PEER = None
     graph, pieces = None, None
     if not eager:
         side = torch.cuda.Stream()

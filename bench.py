@@ -348,6 +348,37 @@ def kernel_rows(extra, hbm_gbs):
     return rows
 
 
+def k512_sweep(dev, flush):
+    """The reference's own benchmark protocol (triton_functions.py:521-567): square M = N in 2048 .. 14336, K = 512,
+    providers cuBLAS bf16 (torch.matmul), blockwise_int8 (the GEMM on pre-quantized operands) and blockwise_int8_quantise
+    (both quantizers + the GEMM), in TFLOP/s = 2*M*N*K / t.  Events around one launch behind an L2 flush, median of 7."""
+    import block_linear_config as cfg
+    from triton_functions import int8_matmul_block64_rowwise_dequantize as mm, quantize_block_rowwise as qr
+    cfg.GROUP_SIZE, cfg.INPUT_OUTPUT_TORCH_TYPE = BLOCK, torch.bfloat16
+    rows = []
+    K = 512
+    for n in range(2048, 16 * 1024, 2048):
+        g = torch.Generator(device=dev).manual_seed(n)
+        a = torch.randn((n, K), device=dev, generator=g).to(torch.bfloat16)
+        bt = torch.randn((n, K), device=dev, generator=g).to(torch.bfloat16)      # the reference's b.t().contiguous()
+        aq, sa = qr(a)
+        bq, sb = qr(bt)
+
+        def quantise_and_multiply():
+            x, sx = qr(a)
+            w, sw = qr(bt)
+            return mm(x, w.t(), sx, sw)
+
+        ops = 2.0 * n * n * K
+        t_cublas = time_kernel(lambda: torch.matmul(a, bt.t()), 7, flush)
+        t_gemm = time_kernel(lambda: mm(aq, bq.t(), sa, sb), 7, flush)
+        t_all = time_kernel(quantise_and_multiply, 7, flush)
+        rows.append({"M": n, "N": n, "K": K, "cublas_bf16_tflops": round(ops / t_cublas / 1e9, 1),
+                     "blockwise_int8_tops": round(ops / t_gemm / 1e9, 1), "blockwise_int8_quantise_tops": round(ops / t_all / 1e9, 1)})
+        del a, bt, aq, bq
+    return rows
+
+
 def sustained_gemm(step_gemm, ops, local, seconds=2.0):
     """The GEMM back to back for `seconds` with the SM clock sampled: the number a long training or prefill run sees."""
     sampler = ClockSampler(local)
@@ -730,6 +761,10 @@ def run_ours(args):
         extra["timing"] = ("us: CUDA-graph replays over rotating inputs larger than L2, median of 5 replays; us_flushed and the "
                            "GEMM rows marked so: CUDA events around one launch behind a 256 MB fill, median of 7")
         roofline["kernels"] = kernel_rows(extra, hbm_gbs)
+        try:
+            roofline["k512_sweep"] = k512_sweep(dev, flush)
+        except Exception as e:            # comparator table only
+            roofline["k512_sweep"] = {"error": f"{type(e).__name__}: {e}"}
         roofline["kernels_note"] = (f"frac = fraction of the {peak_src} HBM copy bandwidth ({hbm_gbs} GB/s) for bound hbm, of the nominal "
                                     "4500 TOP/s for bound tensor; M <= 128 rows and the quantizers are CUDA-graph replays over rotating inputs")
     if tp is not None:

@@ -439,7 +439,7 @@ def tp_bench(dev, rank, world, hbm_gbs):
         if world > 1 and M <= 64:
             from blockwise_int8_linear_b200.peer import PeerAllReduce
             try:
-                peer = PeerAllReduce(M * d, dev)
+                peer = PeerAllReduce(M * d, dev, wait_limit_us=20_000_000)
             except Exception as e:       # no peer mapping on this machine: the NCCL figures stand alone
                 print(f"peer-memory reduction unavailable ({type(e).__name__}: {e})", file=sys.stderr)
                 peer = None

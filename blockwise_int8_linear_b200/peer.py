@@ -27,11 +27,14 @@ _CHUNK = 1024
 class PeerAllReduce:
     """``PeerAllReduce(capacity, device, group)(partial, bias)`` -> ``cast(sum over ranks of partial) + bias``.
 
-    ``capacity``: largest ``M * N`` (fp32 values) one call will carry.  With a group of one rank (or no process group)
-    the buffer is ordinary device memory and the call is a cast + bias."""
+    ``capacity``: largest ``M * N`` (fp32 values) one call will carry.  ``wait_limit_us``: how long a call waits for the
+    other ranks before it gives up with ``BI8_ERR_TIMEOUT`` in the device status (ranks that reach the call seconds apart,
+    e.g. right after capturing their graphs, need more than the default second).  With a group of one rank (or no
+    process group) the buffer is ordinary device memory and the call is a cast + bias."""
 
-    def __init__(self, capacity: int, device, group=None, _local_world: int = 0):
+    def __init__(self, capacity: int, device, group=None, wait_limit_us: int = 0, _local_world: int = 0):
         self.device = torch.device(device)
+        self.wait_limit_us = int(wait_limit_us)          # default limit of the flag waits (0 = the library's one second)
         self.capacity = -(-int(capacity) // _CHUNK) * _CHUNK
         if _local_world:
             # test hook: `_local_world` exchange buffers on this one device, this object acting as rank 0 of them
@@ -70,7 +73,7 @@ class PeerAllReduce:
             dist.barrier(group)         # every rank's buffer is zeroed before anybody's first kernel writes into it
         self._ptrs = (ctypes.c_void_p * 8)(*(ptrs + [ptrs[0]] * (8 - len(ptrs))))
 
-    def __call__(self, partial: torch.Tensor, bias: torch.Tensor = None, out: torch.Tensor = None, wait_limit_us: int = 0):
+    def __call__(self, partial: torch.Tensor, bias: torch.Tensor = None, out: torch.Tensor = None, wait_limit_us: int = None):
         if partial.dtype != torch.float32 or not partial.is_contiguous():
             raise ValueError("partial must be a contiguous float32 tensor")
         n = partial.shape[-1]
@@ -80,6 +83,8 @@ class PeerAllReduce:
             out = torch.empty(partial.shape, dtype=out_dtype, device=partial.device)
         if bias is not None:
             bias = bias.contiguous()
+        if wait_limit_us is None:
+            wait_limit_us = self.wait_limit_us
         with torch.cuda.device(partial.device):
             rc = _lib.lib().bi8_peer_allreduce(self._ptrs, self.rank, self.world, self.capacity, _lib.ptr(partial), m, n,
                                                _lib.ptr(bias), _lib.dtype_code(bias.dtype) if bias is not None else 0,

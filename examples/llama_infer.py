@@ -327,7 +327,7 @@ def run(a, rank, world, dev, eager=False):
         from blockwise_int8_linear_b200.peer import PeerAllReduce
         widest = max(hi - lo for lo, hi in block_aligned_bounds(a.vocab, world, a.block))
         try:
-            PEER = PeerAllReduce(max(a.batch * a.hidden, a.batch * widest * world), dev)
+            PEER = PeerAllReduce(max(a.batch * a.hidden, a.batch * widest * world), dev, wait_limit_us=20_000_000)
         except Exception as e:                                  # no peer mapping on this machine: NCCL between graphs
             print(f"peer-memory reduction unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
             PEER = None
@@ -370,6 +370,8 @@ def run(a, rank, world, dev, eager=False):
         tok.copy_(nxt)
         pos_dev.fill_(a.prompt)
     torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()                                            # the ranks start the decode loop together
     t0 = time.perf_counter()
     for step in range(a.decode - 1):
         if graph is not None:

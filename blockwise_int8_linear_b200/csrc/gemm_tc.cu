@@ -696,32 +696,62 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 }
 
 // Split-K reduction: C[m,n] = cast(sum_s ws[s,m,n]) (+ cast(bias[n]) in the output type).  The splits are added in
-// ascending order, so the result does not depend on scheduling.
+// ascending order, so the result does not depend on scheduling.  VEC = 4: a thread takes four consecutive columns of a row
+// (16-byte loads of every split, all in flight before the first addition); VEC = 1 for N not a multiple of 4.
+template <int VEC>
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ ws, int ksplit, const void* __restrict__ bias,
                                                             int bias_dtype, void* __restrict__ C, int64_t ldc, int out_dtype,
                                                             int M, int N) {
-    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
-    if (i >= (int64_t)M * N) return;
+    const int64_t i = ((int64_t)blockIdx.x * 256 + threadIdx.x) * VEC;
+    const int64_t total = (int64_t)M * N;
+    if (i >= total) return;
     const int m = (int)(i / N), n = (int)(i % N);
-    float acc = 0.0f;
-    for (int s = 0; s < ksplit; ++s) acc = __fadd_rn(acc, ws[((int64_t)s * M + m) * N + n]);
-    float bv = 0.0f;
-    const bool hb = bias != nullptr;
-    if (hb) {
-        if (bias_dtype == BI8_BF16) bv = __bfloat162float(static_cast<const __nv_bfloat16*>(bias)[n]);
-        else if (bias_dtype == BI8_F16) bv = __half2float(static_cast<const __half*>(bias)[n]);
-        else bv = static_cast<const float*>(bias)[n];
+    float acc[VEC];
+#pragma unroll
+    for (int u = 0; u < VEC; ++u) acc[u] = 0.0f;
+    for (int s0 = 0; s0 < ksplit; s0 += 4) {
+        float v[4][VEC];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            if (s0 + q < ksplit) {
+                const float* src = ws + (int64_t)(s0 + q) * total + i;
+                if (VEC == 4) {
+                    const float4 f = __ldcg(reinterpret_cast<const float4*>(src));
+                    v[q][0] = f.x;
+                    if (VEC > 1) { v[q][1 % VEC] = f.y; v[q][2 % VEC] = f.z; v[q][3 % VEC] = f.w; }
+                } else {
+                    v[q][0] = __ldcg(src);
+                }
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            if (s0 + q < ksplit) {
+#pragma unroll
+                for (int u = 0; u < VEC; ++u) acc[u] = __fadd_rn(acc[u], v[q][u]);
+            }
     }
-    if (out_dtype == BI8_F32) {
-        static_cast<float*>(C)[(int64_t)m * ldc + n] = hb ? __fadd_rn(acc, bv) : acc;
-    } else if (out_dtype == BI8_BF16) {
-        __nv_bfloat16 c = __float2bfloat16_rn(acc);
-        if (hb) c = __float2bfloat16_rn(__fadd_rn(__bfloat162float(c), __bfloat162float(__float2bfloat16_rn(bv))));
-        static_cast<__nv_bfloat16*>(C)[(int64_t)m * ldc + n] = c;
-    } else {
-        __half c = __float2half_rn(acc);
-        if (hb) c = __float2half_rn(__fadd_rn(__half2float(c), __half2float(__float2half_rn(bv))));
-        static_cast<__half*>(C)[(int64_t)m * ldc + n] = c;
+    const bool hb = bias != nullptr;
+#pragma unroll
+    for (int u = 0; u < VEC; ++u) {
+        float bv = 0.0f;
+        if (hb) {
+            if (bias_dtype == BI8_BF16) bv = __bfloat162float(static_cast<const __nv_bfloat16*>(bias)[n + u]);
+            else if (bias_dtype == BI8_F16) bv = __half2float(static_cast<const __half*>(bias)[n + u]);
+            else bv = static_cast<const float*>(bias)[n + u];
+        }
+        const int64_t o = (int64_t)m * ldc + n + u;
+        if (out_dtype == BI8_F32) {
+            static_cast<float*>(C)[o] = hb ? __fadd_rn(acc[u], bv) : acc[u];
+        } else if (out_dtype == BI8_BF16) {
+            __nv_bfloat16 c = __float2bfloat16_rn(acc[u]);
+            if (hb) c = __float2bfloat16_rn(__fadd_rn(__bfloat162float(c), __bfloat162float(__float2bfloat16_rn(bv))));
+            static_cast<__nv_bfloat16*>(C)[o] = c;
+        } else {
+            __half c = __float2half_rn(acc[u]);
+            if (hb) c = __float2half_rn(__fadd_rn(__half2float(c), __half2float(__float2half_rn(bv))));
+            static_cast<__half*>(C)[o] = c;
+        }
     }
 }
 
@@ -935,8 +965,12 @@ int launch_gemm_tc(const GemmArgs& g, cudaStream_t st) {
     }
     if (rc != BI8_OK || pl.ksplit == 1) return rc;
     const int64_t total = g.M * g.N;
-    splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(p.ws, pl.ksplit, g.bias, g.bias_dtype, g.C, g.ldc,
-                                                                          g.out_dtype, (int)g.M, (int)g.N);
+    if (g.N % 4 == 0)
+        splitk_reduce_kernel<4><<<(unsigned)((total / 4 + 255) / 256), 256, 0, st>>>(p.ws, pl.ksplit, g.bias, g.bias_dtype, g.C, g.ldc,
+                                                                                 g.out_dtype, (int)g.M, (int)g.N);
+    else
+        splitk_reduce_kernel<1><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(p.ws, pl.ksplit, g.bias, g.bias_dtype, g.C, g.ldc,
+                                                                             g.out_dtype, (int)g.M, (int)g.N);
     BI8_CUDA_TRY(cudaGetLastError());
     return BI8_OK;
 }

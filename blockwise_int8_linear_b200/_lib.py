@@ -21,7 +21,7 @@ GEMM_QUANT_IN_KERNEL = 32
 _DTYPE_CODE = {torch.bfloat16: BI8_BF16, torch.float32: BI8_F32, torch.float16: BI8_F16}
 
 EXPORTS = [
-    "bi8_version", "bi8_last_error_string", "bi8_device_status", "bi8_quantize_rowwise", "bi8_quantize_colwise", "bi8_quantize_dual", "bi8_peer_allreduce", "bi8_peer_allreduce_buffer_bytes",
+    "bi8_version", "bi8_last_error_string", "bi8_device_status", "bi8_quantize_rowwise", "bi8_quantize_colwise", "bi8_quantize_dual", "bi8_peer_allreduce", "bi8_peer_allreduce_buffer_bytes", "bi8_row_parallel_linear",
     "bi8_dequantize_rowwise", "bi8_gemm_dequant", "bi8_gemm_workspace_bytes", "bi8_gemm_block_partials",
     "bi8_gemm_dequant_fused_quant", "bi8_mma_peak_probe", "bi8_gemm_dequant_static", "bi8_gemm_static_scratch_bytes",
     "bi8_gemm_wait_selftest", "bi8_stream_capture_id",
@@ -53,6 +53,8 @@ def lib() -> ctypes.CDLL:
         L.bi8_dequantize_rowwise.argtypes = [vp, vp, vp, i32, i64, i64, i32, vp]
         L.bi8_peer_allreduce_buffer_bytes.argtypes = [i32, i64]
         L.bi8_peer_allreduce_buffer_bytes.restype = sz
+        L.bi8_row_parallel_linear.argtypes = [vp, i32, i64, vp, vp, vp, i64, vp, vp, i64, i64, i64, i32, vp, sz, c.POINTER(vp), i32, i32,
+                                              i64, vp, i32, vp, i32, c.c_uint, i32, vp]
         L.bi8_peer_allreduce.argtypes = [c.POINTER(vp), i32, i32, i64, vp, i64, i64, vp, i32, vp, i32, c.c_uint, vp]
         L.bi8_gemm_dequant.argtypes = [vp, i64, vp, i64, vp, vp, vp, i32, vp, i64, i32, i64, i64, i64, i32, vp, sz, i32, vp]
         L.bi8_gemm_workspace_bytes.argtypes = [i64, i64, i64, i32]

@@ -1,5 +1,6 @@
 // extern "C" surface of libbi8.so: argument validation, dispatch, error text.  See include/bi8.h.
 #include "bi8_common.cuh"
+#include "peer_common.cuh"
 
 #include <cstdarg>
 #include <cstdio>
@@ -254,6 +255,38 @@ int bi8_gemm_dequant_fused_quant(const void* x, int x_dtype, int64_t ldx, int8_t
     if (rc != BI8_OK) return rc;
     return bi8_gemm_dequant(xq, K, Wq, ldw, sx, sW, bias, bias_dtype, C, ldc, out_dtype, M, N, K, block, workspace,
                             workspace_bytes, flags & ~BI8_GEMM_FORCE_SKINNY, stream);
+}
+
+int bi8_row_parallel_linear(const void* x, int x_dtype, int64_t ldx, int8_t* xq, float* sx, const int8_t* Wq, int64_t ldw,
+                            const float* sW, float* partial, int64_t M, int64_t N, int64_t K, int block, void* workspace,
+                            size_t workspace_bytes, void* const* peer_bufs, int rank, int world, int64_t capacity, const void* bias,
+                            int bias_dtype, void* out, int out_dtype, unsigned wait_limit_us, int flags, void* stream) {
+    if (!x || !xq || !sx || !Wq || !sW || !partial || !peer_bufs || !out) return fail(BI8_ERR_NULL, "row_parallel_linear: null pointer");
+    if (!dtype_ok(x_dtype) || !dtype_ok(out_dtype) || (bias && !dtype_ok(bias_dtype))) return fail(BI8_ERR_DTYPE, "row_parallel_linear: unknown dtype code");
+    if (M <= 0 || N <= 0 || K <= 0 || ldx < K || ldw < K) return fail(BI8_ERR_SHAPE, "row_parallel_linear: bad shape M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
+    if (!aligned(partial, 16) || !aligned(out, 16)) return fail(BI8_ERR_ALIGN, "row_parallel_linear: partial and out must be 16-byte aligned");
+    PeerArgs pa;
+    int rc = make_peer_args(&pa, peer_bufs, rank, world, capacity, M, N);
+    if (rc != BI8_OK) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool forced = (flags & (BI8_GEMM_FORCE_GENERIC | BI8_GEMM_FORCE_TC | BI8_GEMM_FORCE_SMALLM | BI8_GEMM_QUANT_IN_KERNEL)) != 0;
+    if (!forced && aligned(x, 16) && (ldx * dtype_size(x_dtype)) % 16 == 0 && K % 16 == 0 && aligned(xq, 16)) {
+        // decode-sized M: quantizer, weight-streaming GEMM, and a reduction kernel that sums the tile parts AND the ranks
+        GemmArgs g{xq, K, Wq, ldw, sx, sW, nullptr, 0, partial, N, BI8_F32, nullptr, M, N, K, block, flags, workspace, workspace_bytes};
+        if (gemm_skinny_applicable(g)) {
+            PeerEpilogue pe{&pa, bias, bias_dtype, out, out_dtype, peer_wait_limit_cycles(wait_limit_us)};
+            rc = launch_skinny_quantize(x, x_dtype, ldx, xq, sx, M, K, block, st);
+            if (rc != BI8_OK) return rc;
+            g.after_own_quantizer = true;
+            g.peer = &pe;
+            return launch_gemm_skinny(g, st);
+        }
+    }
+    // other shapes: the layer's two steps into `partial`, then the stand-alone reduction
+    rc = bi8_gemm_dequant_fused_quant(x, x_dtype, ldx, xq, sx, Wq, ldw, sW, nullptr, 0, partial, N, BI8_F32, M, N, K, block, workspace,
+                                      workspace_bytes, flags, stream);
+    if (rc != BI8_OK) return rc;
+    return launch_peer_allreduce(peer_bufs, rank, world, capacity, partial, M, N, bias, bias_dtype, out, out_dtype, wait_limit_us, st);
 }
 
 int bi8_stream_capture_id(void* stream, unsigned long long* id) {

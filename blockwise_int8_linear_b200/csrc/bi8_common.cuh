@@ -61,6 +61,17 @@ int launch_peer_allreduce(void* const* peer_bufs, int rank, int world, int64_t c
 int launch_dequantize_rowwise(const int8_t* q, const float* s, void* out, int dt, int64_t M, int64_t K,
                               int block, cudaStream_t st);
 
+// Row-parallel layers: the fp32 result in C is this rank's partial result; where the kernel that finishes the GEMM can, it
+// hands its values straight to the peer-memory reduction (peer_common.cuh) instead of leaving that to a second kernel.
+struct PeerEpilogue {
+    const void* args;         // const PeerArgs*
+    const void* bias;
+    int bias_dtype;
+    void* out;                // [M, N] of out_dtype, contiguous
+    int out_dtype;
+    long long limit_cycles;
+};
+
 struct GemmArgs {
     const int8_t* A;
     int64_t lda;
@@ -85,6 +96,7 @@ struct GemmArgs {
     bool after_own_quantizer = false;   // the kernel launched just before is this library's decode quantizer
     unsigned wait_limit_us = 0;         // diagnostic: limit of the general kernel's bounded waits (0 = default, about 2 s)
     int skip_stage = -1;                // diagnostic: the general kernel's producer leaves this stage of its first item out
+    const PeerEpilogue* peer = nullptr; // decode kernel only: reduce over the ranks inside its reduction kernel
 };
 
 bool gemm_tc_applicable(const GemmArgs& g, const char** why);

@@ -30,6 +30,7 @@
 //     order within a range, so a tile that is not divided is bit-identical to the CUDA-core kernel.
 #include "quant_math.cuh"
 #include "tc_common.cuh"
+#include "peer_common.cuh"
 
 #include <cstring>
 
@@ -612,6 +613,49 @@ __global__ void __launch_bounds__(256) skinny_reduce_kernel(const float* __restr
     finish_store(acc, m, n, bias, bias_dtype, C, ldc, out_dtype);
 }
 
+// The same reduction for a row-parallel layer: the tile sums are this rank's partial result, and instead of writing them
+// out for a second kernel the CTA exchanges them with the other ranks over peer memory right away (peer_common.cuh).  A
+// thread takes four consecutive columns of a row (they lie in one tile); `part` is the fp32 [M, N] array into which the
+// GEMM wrote the tiles that one CTA covered completely.  Launched for every shape, divided tiles or not.
+__global__ void __launch_bounds__(kPeerThreads) skinny_reduce_peer_kernel(const float* __restrict__ ws, long long total_stages, int ctas,
+                                                                          int nks, int bns, const float* __restrict__ part, int M,
+                                                                          int N, const PeerArgs a, const void* __restrict__ bias,
+                                                                          int bias_dtype, void* __restrict__ out, int out_dtype,
+                                                                          long long limit_cycles, int* status) {
+    const int64_t count = (int64_t)M * N;
+    const int64_t i = (int64_t)blockIdx.x * kPeerChunk + (int64_t)threadIdx.x * 4;
+    const bool live = i < count;
+    const int m = live ? (int)(i / N) : 0, n = live ? (int)(i % N) : 0;
+    const int tile = n / kTileRows, row = n % kTileRows;
+    const long long t0 = (long long)tile * nks, t1 = t0 + nks;
+    long long c0 = t0 * ctas / total_stages;
+    while (c0 + 1 < ctas && range_start(c0 + 1, total_stages, ctas) <= t0) ++c0;
+    while (c0 > 0 && range_start(c0, total_stages, ctas) > t0) --c0;
+    const long long cs0 = range_start(c0, total_stages, ctas);
+    const bool whole = cs0 <= t0 && range_start(c0 + 1, total_stages, ctas) >= t1;   // written by the GEMM itself
+    int parts = 1;
+    while (range_start(c0 + parts, total_stages, ctas) < t1) ++parts;
+    const uint32_t seq = peer_sequence(a);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (live) {
+        if (whole) {
+            v = __ldcg(reinterpret_cast<const float4*>(part + i));
+        } else {
+            // parts in ascending K order, like skinny_reduce_kernel (0 + first part is exact)
+            v = __ldcg(reinterpret_cast<const float4*>(ws + ((2 * c0 + (cs0 < t0 ? 1 : 0)) * bns + m) * kTileRows + row));
+            for (int q = 1; q < parts; ++q) {
+                const float4 w = __ldcg(reinterpret_cast<const float4*>(ws + (2 * (c0 + q) * bns + m) * kTileRows + row));
+                v.x = __fadd_rn(v.x, w.x);
+                v.y = __fadd_rn(v.y, w.y);
+                v.z = __fadd_rn(v.z, w.z);
+                v.w = __fadd_rn(v.w, w.w);
+            }
+        }
+    }
+    peer_exchange_store(a, seq, v, count, N, bias, bias_dtype, out, out_dtype, limit_cycles, status);
+}
+
 template <int QB, int BNS, bool FUSED>
 int launch_skinny(const GemmArgs& g, const SkParams& p, int grid, cudaStream_t st) {
     using G = SkGeo<QB, BNS, FUSED>;
@@ -757,6 +801,25 @@ int launch_gemm_skinny(const GemmArgs& g, cudaStream_t st) {
     BI8_SK(128, 16) BI8_SK(128, 32) BI8_SK(128, 64)
 #undef BI8_SK
     if (rc != BI8_OK) return rc;
+    if (g.peer != nullptr) {
+        // row-parallel layer: the reduction kernel also exchanges the sums with the other ranks and writes the layer's output
+        const PeerEpilogue& pe = *g.peer;
+        const int64_t count = g.M * g.N;
+        cudaLaunchConfig_t pc;
+        std::memset(&pc, 0, sizeof(pc));
+        pc.gridDim = dim3((unsigned)((count + kPeerChunk - 1) / kPeerChunk));
+        pc.blockDim = dim3(kPeerThreads);
+        pc.stream = st;
+        cudaLaunchAttribute pa[1];
+        pa[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;     // see skinny_reduce_kernel
+        pa[0].val.programmaticStreamSerializationAllowed = 1;
+        pc.attrs = pa;
+        pc.numAttrs = 1;
+        BI8_CUDA_TRY(cudaLaunchKernelEx(&pc, skinny_reduce_peer_kernel, (const float*)p.ws, p.total_stages, grid, p.nks, bns,
+                                        (const float*)g.C, (int)g.M, (int)g.N, *static_cast<const PeerArgs*>(pe.args), pe.bias,
+                                        pe.bias_dtype, pe.out, pe.out_dtype, pe.limit_cycles, p.status));
+        return BI8_OK;
+    }
     if (p.total_stages % grid == 0 && (p.total_stages / grid) % p.nks == 0) return BI8_OK;   // no tile is divided
     const int64_t total = g.M * g.N;
     cudaLaunchConfig_t cfg;

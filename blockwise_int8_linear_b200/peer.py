@@ -91,3 +91,44 @@ class PeerAllReduce:
                                                _lib.ptr(out), _lib.dtype_code(out.dtype), int(wait_limit_us), _lib.stream_ptr())
         _lib.check(rc, "bi8_peer_allreduce")
         return out
+
+    def row_parallel_linear(self, x: torch.Tensor, w_int8: torch.Tensor, state_w: torch.Tensor, bias: torch.Tensor = None,
+                            wait_limit_us: int = None):
+        """The whole row-parallel layer in one library call: ``x [..., K_r]`` is this rank's slice of the input features,
+        ``w_int8 [N, K_r]`` / ``state_w [ceil(K_r/block), N]`` this rank's weight slice.  Returns
+        ``cast(sum over ranks of x_r @ W_r^T) + bias``.  For decode-sized batches (at most 64 rows) the kernel that finishes
+        the weight-streaming GEMM exchanges its sums with the other ranks itself; the result equals
+        ``self(partial)`` on the fp32 output of ``quantize_matmul_block_rowwise_dequantize``."""
+        from .triton_functions import _block, _pitch, _rows_contiguous, ceil_div
+        block = _block()
+        lead = x.shape[:-1]
+        x2 = _rows_contiguous(x.reshape(-1, x.shape[-1]))
+        m, k = x2.shape
+        n = w_int8.shape[0]
+        if w_int8.dtype != torch.int8 or w_int8.shape[1] != k or w_int8.stride(1) != 1:
+            raise ValueError("w_int8 must be int8 [N, K] with contiguous rows")
+        nb = ceil_div(k, block)
+        if tuple(state_w.shape) != (nb, n) or state_w.dtype != torch.float32:
+            raise ValueError(f"state_w must be float32 [{nb}, {n}] for block {block}")
+        state_w = state_w.contiguous()
+        out_dtype = block_linear_config.INPUT_OUTPUT_TORCH_TYPE
+        dev = x2.device
+        out = torch.empty((m, n), dtype=out_dtype, device=dev)
+        partial = torch.empty((m, n), dtype=torch.float32, device=dev)
+        xq = torch.empty((m, k), dtype=torch.int8, device=dev)
+        sx = torch.empty((nb, m), dtype=torch.float32, device=dev)
+        if bias is not None:
+            bias = bias.reshape(n).contiguous()
+        if wait_limit_us is None:
+            wait_limit_us = self.wait_limit_us
+        L = _lib.lib()
+        with torch.cuda.device(dev):
+            ws_bytes = L.bi8_gemm_workspace_bytes(m, n, k, block)
+            ws = _lib.workspace(dev, ws_bytes)
+            rc = L.bi8_row_parallel_linear(_lib.ptr(x2), _lib.dtype_code(x2.dtype), _pitch(x2), _lib.ptr(xq), _lib.ptr(sx),
+                                           _lib.ptr(w_int8), _pitch(w_int8), _lib.ptr(state_w), _lib.ptr(partial), m, n, k, block,
+                                           _lib.ptr(ws), ws_bytes, self._ptrs, self.rank, self.world, self.capacity,
+                                           _lib.ptr(bias), _lib.dtype_code(bias.dtype) if bias is not None else 0,
+                                           _lib.ptr(out), _lib.dtype_code(out_dtype), int(wait_limit_us), 0, _lib.stream_ptr())
+        _lib.check(rc, "bi8_row_parallel_linear")
+        return out.view(*lead, n)

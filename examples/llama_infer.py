@@ -106,6 +106,15 @@ class Int8Linear(nn.Module):
         dist.all_reduce(part)
         return part.to(cfg.INPUT_OUTPUT_TORCH_TYPE)
 
+    def summed(self, x):
+        """A row-parallel layer's output summed over the group, cast to the activation type: for decode-sized inputs with
+        the peer-memory reduction installed, one library call whose last kernel adds the GEMM's tile parts and the ranks."""
+        if self.world > 1 and self.mode == "row" and PEER is not None and self.lin is not None:
+            rows = x.numel() // x.shape[-1]
+            if rows <= 64 and rows * self.widths[0] <= PEER.capacity:
+                return PEER.row_parallel_linear(x, self.lin.W_int8, self.lin.state_W)
+        return group_sum(self.partial(x), cfg.INPUT_OUTPUT_TORCH_TYPE, self.world)
+
 
 def rms_norm(x, eps=1e-5):
     return F.rms_norm(x, (x.shape[-1],), eps=eps)
@@ -137,7 +146,7 @@ class Layer(nn.Module):
         self.head_dim = a.head_dim
         self.kcache = self.vcache = None
 
-    def attn_partial(self, x, pos0, max_len, cis, mask=None, pos_dev=None):
+    def attn_partial(self, x, pos0, max_len, cis, mask=None, pos_dev=None, summed=False):
         """Attention half of the layer up to the output projection, without the sum over ranks and the residual add.
         Prefill: pos0 is a Python int and the cache is sliced.  Decode (pos_dev given, T == 1): the position is a device
         tensor, the cache is written with index_copy_ and attended in full under a mask, so that every shape is static and
@@ -160,15 +169,16 @@ class Layer(nn.Module):
             self.vcache.index_copy_(2, pos_dev, v)
             att = F.scaled_dot_product_attention(q, self.kcache, self.vcache, attn_mask=mask)
         att = att.transpose(1, 2).reshape(B, T, hl * hd)
-        return self.o.partial(att)
+        return self.o.summed(att) if summed else self.o.partial(att)
 
-    def mlp_partial(self, x):
+    def mlp_partial(self, x, summed=False):
         gate, up = self.gate_up(rms_norm(x)).split(self.gate_up.widths, dim=-1)
-        return self.down.partial(F.silu(gate) * up)
+        h = F.silu(gate) * up
+        return self.down.summed(h) if summed else self.down.partial(h)
 
     def forward(self, x, pos0, max_len, cis, mask=None, pos_dev=None):
-        x = x + group_sum(self.attn_partial(x, pos0, max_len, cis, mask, pos_dev), x.dtype, self.o.world)
-        return x + group_sum(self.mlp_partial(x), x.dtype, self.down.world)
+        x = x + self.attn_partial(x, pos0, max_len, cis, mask, pos_dev, summed=True)
+        return x + self.mlp_partial(x, summed=True)
 
 
 PEER = None      # a blockwise_int8_linear_b200.peer.PeerAllReduce while the decode step uses the library's own reduction

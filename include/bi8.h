@@ -186,6 +186,20 @@ BI8_API int bi8_peer_allreduce(void* const* peer_bufs, int rank, int world, int6
                        int64_t M, int64_t N, const void* bias, int bias_dtype, void* out, int out_dtype,
                        unsigned wait_limit_us, void* stream);
 
+/* A whole row-parallel layer in one call: quantize x [M,K] (this rank's slice of the input features), multiply with this
+ * rank's weight slice Wq [N,K] / sW, and sum the ranks' fp32 partial results as bi8_peer_allreduce does.  For M <= 64
+ * (decode) the kernel that adds the weight-streaming GEMM's tile parts hands its sums straight to the exchange, so the layer
+ * is three launches (quantizer, GEMM, reduction over parts and ranks) with no fp32 round trip in between; other shapes run
+ * bi8_gemm_dequant_fused_quant into `partial` followed by bi8_peer_allreduce.  Same results as those two calls.
+ * xq [M,K] int8 and sx [ceil(K/block), M] fp32 are scratch as in bi8_gemm_dequant_fused_quant; partial [M,N] fp32 is scratch
+ * (16-byte aligned); workspace as in bi8_gemm_dequant; peer_bufs .. capacity, bias, out, wait_limit_us as in
+ * bi8_peer_allreduce (out [M,N] contiguous, N a multiple of 4). */
+BI8_API int bi8_row_parallel_linear(const void* x, int x_dtype, int64_t ldx, int8_t* xq, float* sx, const int8_t* Wq, int64_t ldw,
+                            const float* sW, float* partial, int64_t M, int64_t N, int64_t K, int block,
+                            void* workspace, size_t workspace_bytes, void* const* peer_bufs, int rank, int world,
+                            int64_t capacity, const void* bias, int bias_dtype, void* out, int out_dtype,
+                            unsigned wait_limit_us, int flags, void* stream);
+
 /* Back-to-back tcgen05.mma kind::i8 issue rate of the current device: runs `iters` 128x256x32 MMAs per SM
  * with no loads or epilogue and returns the elapsed milliseconds in *ms (synchronises).  Used by the
  * benchmark to state the measured dense INT8 peak next to the nominal one. */

@@ -74,7 +74,7 @@ def _peer_worker(rank, world, port, results):
         from blockwise_int8_linear_b200 import _lib
         from blockwise_int8_linear_b200.peer import PeerAllReduce
         cfg.INPUT_OUTPUT_TORCH_TYPE = torch.bfloat16
-        peer = PeerAllReduce(8 * 4096, dev)
+        peer = PeerAllReduce(70 * 4096, dev)
         g = torch.Generator(device=dev).manual_seed(100 + rank)
         bias = torch.randn(4096, device=dev, generator=torch.Generator(device=dev).manual_seed(5)).to(torch.bfloat16)
         for m, n in ((8, 4096), (3, 1000), (1, 4)):
@@ -95,6 +95,20 @@ def _peer_worker(rank, world, port, results):
                     parts = [torch.empty_like(part) for _ in range(world)]
                     dist.all_gather(parts, part)
                     assert torch.equal(got, (parts[0] + parts[1]).to(torch.bfloat16))      # rank order, fp32
+        # the whole row-parallel layer in one call (the GEMM's reduction kernel exchanges its sums itself) against the two
+        # steps: tiles divided over CTAs (N = 4096), whole tiles (N = 15360), more than 64 rows (two-step path inside)
+        from triton_functions import quantize_block_rowwise, quantize_matmul_block_rowwise_dequantize
+        cfg.GROUP_SIZE = 64
+        for m, k, n in ((8, 2048, 4096), (5, 1408, 15360), (33, 1024, 4096), (70, 1024, 4096)):
+            w = (torch.randn((n, k), device=dev, generator=g) * 0.02).to(torch.bfloat16)
+            wq, sw = quantize_block_rowwise(w)
+            x = torch.randn((m, k), device=dev, generator=g).to(torch.bfloat16)
+            cfg.INPUT_OUTPUT_TORCH_TYPE = torch.float32
+            part = quantize_matmul_block_rowwise_dequantize(x, wq.t(), sw)
+            cfg.INPUT_OUTPUT_TORCH_TYPE = torch.bfloat16
+            want = peer(part, bias[:n] if n <= 4096 else None)
+            got = peer.row_parallel_linear(x, wq, sw, bias[:n] if n <= 4096 else None)
+            assert torch.equal(got, want), (m, k, n, (got.float() - want.float()).abs().max().item())
         # replayed from a graph: the sequence number continues on the device
         part = torch.randn((8, 4096), device=dev, generator=g)
         out = torch.empty((8, 4096), device=dev, dtype=torch.bfloat16)
@@ -158,6 +172,16 @@ def test_peer_allreduce_one_rank_and_bounded_wait():
     one = PeerAllReduce(8 * 4096, DEV)
     for _ in range(3):
         assert torch.equal(one(part, bias), part.to(torch.bfloat16) + bias)
+    assert _lib.device_status() == 0
+    # one rank: the row-parallel layer call is the layer itself
+    from triton_functions import quantize_block_rowwise, quantize_matmul_block_rowwise_dequantize
+    cfg.GROUP_SIZE = 64
+    big = PeerAllReduce(70 * 4096, DEV)
+    for m in (8, 40, 70):
+        w = (torch.randn((4096, 1024), device=DEV) * 0.02).to(torch.bfloat16)
+        wq, sw = quantize_block_rowwise(w)
+        x = torch.randn((m, 1024), device=DEV).to(torch.bfloat16)
+        assert torch.equal(big.row_parallel_linear(x, wq, sw, bias), quantize_matmul_block_rowwise_dequantize(x, wq.t(), sw, bias))
     assert _lib.device_status() == 0
     lonely = PeerAllReduce(8 * 4096, DEV, _local_world=2)
     out = torch.full((8, 4096), 7.0, device=DEV, dtype=torch.bfloat16)

@@ -460,6 +460,13 @@ def tp_bench(dev, rank, world, hbm_gbs):
                 xq, sx = quantize_block_rowwise(x)
                 h = mm(xq, wq_gu.t(), sx, s_gu)
             a = F.silu(h[:, :fr]) * h[:, fr:]
+            if use_peer == 2:
+                # the whole row-parallel layer in one call: the GEMM's reduction kernel exchanges its sums itself
+                y = peer.row_parallel_linear(a, wq_dn, s_dn)
+                if timed:
+                    ev[1].record()
+                    ev[2].record()
+                return y
             cfg.INPUT_OUTPUT_TORCH_TYPE = torch.float32 if world > 1 else torch.bfloat16
             try:
                 if M <= 64:
@@ -528,6 +535,21 @@ def tp_bench(dev, rank, world, hbm_gbs):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             out[tag]["peer_reduce"] = {"kernel": "bi8_peer_allreduce (st.global to every rank's slots, flag per chunk, sum in rank order)",
                                        "ms_per_pair": t[0].item(), "ms_reduce": (t[0] - t[1]).item()}
+            for i in range(5):
+                pair(i, use_peer=2)
+            torch.cuda.synchronize()
+            dist.barrier()
+            tot = []
+            for i in range(15):
+                dist.barrier()
+                pair(i, timed=True, use_peer=2)
+                ev[2].synchronize()
+                tot.append(ev[0].elapsed_time(ev[2]))
+            tot.sort()
+            t = torch.tensor([tot[len(tot) // 2]], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            out[tag]["peer_reduce_fused"] = {"kernel": "bi8_row_parallel_linear (the decode GEMM's reduction kernel sums tile parts and ranks)",
+                                             "ms_per_pair": t[0].item()}
             from blockwise_int8_linear_b200 import _lib
             _lib.device_status()
         del gus, dns

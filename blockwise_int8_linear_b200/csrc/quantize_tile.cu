@@ -376,6 +376,7 @@ quantize_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
 int make_q_map(CUtensorMap* map, int8_t* ptr, int64_t rows, int64_t cols) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(BI8_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    ensure_current_context();
     cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     cuuint64_t gstride[1] = {(cuuint64_t)cols};
     cuuint32_t box[2] = {128, 128};
@@ -390,6 +391,7 @@ int make_q_map(CUtensorMap* map, int8_t* ptr, int64_t rows, int64_t cols) {
 int make_x_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int64_t ld) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(BI8_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    ensure_current_context();
     cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     cuuint64_t gstride[1] = {(cuuint64_t)ld * 2};
     cuuint32_t box[2] = {64, 128};

@@ -41,10 +41,30 @@ inline EncodeTiledFn encode_fn() {
     return fn;
 }
 
+// cuTensorMapEncodeTiled is a driver call and wants a context current on the calling thread.  A thread that has made no
+// runtime call yet has none (an autograd worker thread whose first CUDA work is one of this library's functions; any fresh
+// host thread), and the encode then fails with CUDA_ERROR_INVALID_CONTEXT: bind the current device's primary context first.
+inline void ensure_current_context() {
+    typedef CUresult (*GetCurrentFn)(CUcontext*);
+    static GetCurrentFn get_current = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuCtxGetCurrent", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            get_current = reinterpret_cast<GetCurrentFn>(sym);
+    });
+    CUcontext ctx = nullptr;
+    if (get_current && get_current(&ctx) == CUDA_SUCCESS && ctx != nullptr) return;
+    (void)cudaFree(nullptr);          // initialises the runtime on this thread and makes the primary context current
+}
+
 // int8 [rows, K] row-major with row pitch ld bytes -> boxes of 128 K-bytes x box_rows rows, 128-byte swizzle
 inline int make_operand_map(CUtensorMap* map, const int8_t* ptr, int64_t rows, int64_t K, int64_t ld, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(BI8_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    ensure_current_context();
     cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)rows};
     cuuint64_t gstride[1] = {(cuuint64_t)ld};
     cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
@@ -61,6 +81,7 @@ inline int make_operand_map(CUtensorMap* map, const int8_t* ptr, int64_t rows, i
 inline int make_scale_map(CUtensorMap* map, const float* ptr, int64_t nb, int64_t cols, int box_cols, int box_blocks) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(BI8_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    ensure_current_context();
     cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)nb};
     cuuint64_t gstride[1] = {(cuuint64_t)cols * 4};
     cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_blocks};
@@ -77,6 +98,7 @@ inline int make_scale_map(CUtensorMap* map, const float* ptr, int64_t nb, int64_
 inline int make_output_map(CUtensorMap* map, void* ptr, int esz, int64_t rows, int64_t cols, int64_t ld, int box_rows, int box_cols) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(BI8_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    ensure_current_context();
     cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     cuuint64_t gstride[1] = {(cuuint64_t)ld * (cuuint64_t)esz};
     cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};

@@ -259,3 +259,35 @@ def test_large_unaligned_tensors_are_padded_not_slowed(shape):
     a, b, c, d = quantize_block_dual(xd, 64)
     assert torch.equal(a.cpu(), qr_ref) and torch.equal(b.cpu(), sr_ref) and torch.equal(c.cpu(), qc_ref) and torch.equal(d.cpu(), sc_ref)
     assert_clean_device()
+
+
+def test_tensor_map_kernels_from_a_fresh_thread():
+    """A host thread that has made no CUDA call yet has no context current, and the tensor-map encode is a driver call: the
+    library binds the primary context itself (an autograd worker thread whose first CUDA work is this layer's backward
+    is such a thread)."""
+    import threading
+    from triton_functions import (int8_matmul_block64_rowwise_dequantize, quantize_block_colwise, quantize_block_dual,
+                                  quantize_block_rowwise)
+    set_config(64, torch.bfloat16)
+    x = randn_bf16((256, 512), 21).to(DEV)
+    w = randn_bf16((384, 512), 22).to(DEV)
+    xq, xs = quantize_block_rowwise(x)
+    wq, ws = quantize_block_rowwise(w)
+    want = (quantize_block_dual(x), quantize_block_colwise(x), int8_matmul_block64_rowwise_dequantize(xq, wq.t(), xs, ws))
+    torch.cuda.synchronize()
+    got, errors = [], []
+
+    def work():
+        try:
+            got.append((quantize_block_dual(x), quantize_block_colwise(x), int8_matmul_block64_rowwise_dequantize(xq, wq.t(), xs, ws)))
+            torch.cuda.synchronize()
+        except Exception as e:            # reported in the main thread
+            errors.append(e)
+
+    t = threading.Thread(target=work)
+    t.start()
+    t.join()
+    assert not errors, errors
+    for a, b in zip(want[0], got[0][0]):
+        assert torch.equal(a, b)
+    assert torch.equal(want[1][0], got[0][1][0]) and torch.equal(want[2], got[0][2])

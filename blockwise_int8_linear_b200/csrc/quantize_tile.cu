@@ -403,6 +403,23 @@ int make_x_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, in
     return BI8_OK;
 }
 
+// Encoded maps are looked up in the library's map table first (kinds 5 and 6 there): a training step quantizes tensors of
+// the same few shapes at addresses the allocator keeps handing back, and an encode is a driver call of a few microseconds.
+int cached_x_map(CUtensorMap* map, int dev, const void* ptr, int64_t rows, int64_t cols, int64_t ld) {
+    const MapKey key{dev, 5, ptr, rows, cols, ld, 128, 64};
+    if (map_cache().find(key, map)) return BI8_OK;
+    const int rc = make_x_map(map, ptr, rows, cols, ld);
+    if (rc == BI8_OK) map_cache().put(key, *map);
+    return rc;
+}
+int cached_q_map(CUtensorMap* map, int dev, int8_t* ptr, int64_t rows, int64_t cols) {
+    const MapKey key{dev, 6, ptr, rows, cols, cols, 128, 128};
+    if (map_cache().find(key, map)) return BI8_OK;
+    const int rc = make_q_map(map, ptr, rows, cols);
+    if (rc == BI8_OK) map_cache().put(key, *map);
+    return rc;
+}
+
 template <typename T, int B, bool DUAL>
 int launch_tile(const CUtensorMap& tx, const CUtensorMap& tqc, const CUtensorMap& tqr, float* s_col, float* s_row, int64_t R,
                 int64_t C, cudaStream_t st) {
@@ -428,14 +445,16 @@ template <typename T>
 int tile_dispatch(const void* x, int64_t ldx, int8_t* q_col, float* s_col, int8_t* q_row, float* s_row, int64_t R, int64_t C, int block,
                   cudaStream_t st) {
     CUtensorMap tx, tqc, tqr;
-    int rc = make_x_map(&tx, x, R, C, ldx);
+    int dev = 0;
+    BI8_CUDA_TRY(cudaGetDevice(&dev));
+    int rc = cached_x_map(&tx, dev, x, R, C, ldx);
     if (rc != BI8_OK) return rc;
-    rc = make_q_map(&tqc, q_col, C, R);
+    rc = cached_q_map(&tqc, dev, q_col, C, R);
     if (rc != BI8_OK) return rc;
     tqr = tqc;
     const bool dual = q_row != nullptr;
     if (dual) {
-        rc = make_q_map(&tqr, q_row, R, C);
+        rc = cached_q_map(&tqr, dev, q_row, R, C);
         if (rc != BI8_OK) return rc;
     }
 #define BI8_TILE(BB)                                                                                  \

@@ -115,7 +115,7 @@ inline int make_output_map(CUtensorMap* map, void* ptr, int esz, int64_t rows, i
 // a small table guarded by a mutex and looked up by those values (a stale entry for a freed and re-used address is
 // still a correct description of that address).
 struct MapKey {
-    int dev, kind;            // kind 0: int8 operand, 1: fp32 scales, 2 / 4: output of 2- / 4-byte elements
+    int dev, kind;            // kind 0: int8 operand, 1: fp32 scales, 2 / 4: output of 2- / 4-byte elements, 5 / 6: input and int8 tiles of the tile quantizer
     const void* ptr;
     int64_t rows, cols, ld;
     int box_rows, box_cols;

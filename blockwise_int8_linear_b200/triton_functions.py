@@ -101,7 +101,9 @@ def quantize_block_rowwise(x: torch.Tensor, fblock_size=None):
 
     Returns ``(q, state)``: ``q`` int8 ``[M, K]``; ``state`` float32 ``[ceil(K/block), M]`` holding
     ``max|x|`` of each block.  ``q = rint(127 * (x / state))`` (fp32 divide, fp32 multiply, round half to
-    even); an all-zero block gives state 0 and q 0."""
+    even); an all-zero block gives state 0 and q 0.  For a large 16-bit ``x`` whose ``K`` is not a multiple of 16 the
+    returned ``q`` is a view of a zero-padded buffer (row pitch rounded up to 16; same values), which the GEMM takes
+    without a copy; call ``.contiguous()`` where a dense tensor is needed."""
     block = _block(fblock_size)
     m, k = x.shape
     assert x.is_cuda

@@ -33,6 +33,7 @@ import json
 import os
 import subprocess
 import sys
+import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -80,30 +81,44 @@ class ClockSampler:
     def __init__(self, gpu_index: int):
         self.gpu = gpu_index
         self.proc = None
+        self.rows = []          # (arrival time, fields) of every sample line, appended by the reader thread
+        self.thread = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.perf_counter(), [x.strip() for x in line.split(",")]))
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
                                           "-lms", "25", "-i", str(self.gpu)], stdout=subprocess.PIPE,
-                                         stderr=subprocess.DEVNULL, text=True)
+                                         stderr=subprocess.DEVNULL, text=True, bufsize=1)
         except OSError:
             self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
 
-    def stop(self):
+    def count_since(self, t0: float) -> int:
+        return sum(1 for t, f in list(self.rows) if t >= t0 and len(f) >= 9)
+
+    def stop(self, since: float = None):
+        """Summary of the samples that arrived from `since` (a time.perf_counter() value) on; all of them without it."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        if since is None:
+            time.sleep(0.15)
         self.proc.terminate()
         try:
-            out, _ = self.proc.communicate(timeout=5)
+            self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-            out = ""
+        if self.thread is not None:
+            self.thread.join(timeout=2)
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in out.strip().splitlines():
-            f = [x.strip() for x in line.split(",")]
-            if len(f) < 9:
+        for t_arr, f in list(self.rows):
+            if len(f) < 9 or (since is not None and t_arr < since):
                 continue
             try:
                 sm.append(float(f[1]))
@@ -634,21 +649,36 @@ def run_ours(args):
             torch.distributed.barrier()
             torch.cuda.synchronize()
 
-    for i in range(args.warmup):
-        step(i)
-    barrier()
+    # the sampler starts before the warm-up (nvidia-smi needs a few hundred milliseconds to deliver its first line); only
+    # samples that arrive from the start of the timed region on are kept
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    for i in range(args.warmup):
+        step(i)
+    barrier()
     gemm_events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    t_clock0 = time.perf_counter()
     t_start.record()
     for i in range(args.steps):
         step(i, gemm_events[i])
     t_end.record()
     barrier()
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = None
+    if rank == 0:
+        # A timed region shorter than a few sample periods: the same loop keeps running, untimed, until three samples have
+        # arrived under this load (one second at most).
+        extra_steps = 0
+        while sampler.proc is not None and sampler.count_since(t_clock0) < 3 and time.perf_counter() - t_clock0 < 1.0:
+            for i in range(args.steps):
+                step(i)
+            torch.cuda.synchronize()
+            extra_steps += args.steps
+        clocks = sampler.stop(since=t_clock0)
+        clocks["window"] = "timed region" if extra_steps == 0 else f"timed region + {extra_steps} further untimed steps of the same loop"
+    barrier()
     ms_total = t_start.elapsed_time(t_end)
     gemm_ms = sum(a.elapsed_time(b) for a, b in gemm_events) / args.steps
     if world > 1:

@@ -1,0 +1,246 @@
+// Row-wise block quantizers with the elementwise step that produces their input fused in front.
+//
+// In a transformer layer the input of every quantized projection comes out of a short elementwise step: the
+// normalisation in front of q/k/v and gate/up, the gated activation in front of the down projection.  Run as separate
+// kernels these write a [M, K] tensor in the activation type that the quantizer (triton_functions.py:411-423 in the
+// reference, one program per row) reads back at once.  The kernels here compute that tensor in registers, round every
+// value to the activation type exactly as the separate kernel would have stored it, and quantize it with the same
+// arithmetic as the stand-alone quantizer (quant_math.cuh), so that the int8 values and scales are those of
+// quantize_block_rowwise applied to the rounded tensor.
+//
+//   BI8_PRE_RMSNORM   y = cast(x * rsqrt(sum(x^2) / K + eps) [* weight])        one rounding, fp32 arithmetic
+//   BI8_PRE_SILU_MUL  y = cast(cast(x / (1 + exp(-x))) * x2)                    two roundings: silu(x), then the product
+//
+// Both start their programmatic dependents at once (the decode GEMM launched behind them sets up and streams its first
+// weights while they run; it waits for their completion before it reads the activations).
+#include "bi8_common.cuh"
+#include "quant_math.cuh"
+
+namespace bi8 {
+namespace {
+
+constexpr int kPreThreads = 256;
+constexpr int kPreHold = 4;        // 8-element units of a row a thread keeps in registers between the two passes
+
+// eight consecutive elements of a row, beginning at element `k` of `K`; elements from K on read as zero
+__device__ __forceinline__ void load8(float* f, const void* base, int64_t row_off, int k, int K, int dt, bool vec) {
+    const int esz = dt == BI8_F32 ? 4 : 2;
+    const unsigned char* src = static_cast<const unsigned char*>(base) + (row_off + k) * esz;
+    if (vec && k + 8 <= K) {
+        const uint4 a = ld_nc_v4(src);
+        if (dt == BI8_F32) {
+            const uint4 b = ld_nc_v4(src + 16);
+            f[0] = __uint_as_float(a.x); f[1] = __uint_as_float(a.y); f[2] = __uint_as_float(a.z); f[3] = __uint_as_float(a.w);
+            f[4] = __uint_as_float(b.x); f[5] = __uint_as_float(b.y); f[6] = __uint_as_float(b.z); f[7] = __uint_as_float(b.w);
+        } else {
+            const uint32_t w4[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+                if (dt == BI8_BF16) {
+                    f[2 * h] = bf16lo(w4[h]);
+                    f[2 * h + 1] = bf16hi(w4[h]);
+                } else {
+                    const float2 t2 = __half22float2(*reinterpret_cast<const __half2*>(&w4[h]));
+                    f[2 * h] = t2.x;
+                    f[2 * h + 1] = t2.y;
+                }
+            }
+        }
+        return;
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        float v = 0.0f;
+        if (k + e < K) {
+            if (dt == BI8_F32) v = reinterpret_cast<const float*>(src)[e];
+            else if (dt == BI8_BF16) v = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(src)[e]);
+            else v = __half2float(reinterpret_cast<const __half*>(src)[e]);
+        }
+        f[e] = v;
+    }
+}
+
+// the value a kernel storing `v` in the activation type would have left in memory
+__device__ __forceinline__ float round_to(float v, int dt) {
+    if (dt == BI8_BF16) return __bfloat162float(__float2bfloat16_rn(v));
+    if (dt == BI8_F16) return __half2float(__float2half_rn(v));
+    return v;
+}
+
+// Quantizes the eight values of a unit whose block's other units sit in the neighbouring lanes (LPB lanes per block)
+// and stores them; all 32 lanes of the warp must call it.
+template <int QB>
+__device__ __forceinline__ void quantize_unit(const float* y, bool valid, bool short_mantissa, int8_t* q, float* sx, int m, int k,
+                                              int M, int K, bool vec) {
+    constexpr int LPB = QB / 8;
+    float amax = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(y[e]));
+#pragma unroll
+    for (int off = 1; off < LPB; off <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    if (!valid) return;
+    BlockQ bq;
+    bq.set(amax, short_mantissa);
+    const uint32_t lo = pack4(bq.q(y[0]), bq.q(y[1]), bq.q(y[2]), bq.q(y[3]));
+    const uint32_t hi = pack4(bq.q(y[4]), bq.q(y[5]), bq.q(y[6]), bq.q(y[7]));
+    int8_t* dst = q + (int64_t)m * K + k;
+    if (vec && k + 8 <= K) {
+        *reinterpret_cast<uint2*>(dst) = make_uint2(lo, hi);
+    } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+            if (k + e < K) dst[e] = (int8_t)(((e < 4 ? lo : hi) >> (8 * (e & 3))) & 0xffu);
+    }
+    if (((k / 8) % LPB) == 0) sx[(int64_t)(k / QB) * M + m] = amax;
+}
+
+// One CTA per row.  Pass 1: the row's sum of squares (a thread's units in ascending order, lanes by butterfly, warps in
+// ascending order: the same bits on every launch).  Pass 2: normalise, round, quantize.  Rows of up to
+// kPreHold * 256 * 8 elements stay in registers between the passes; longer rows are read again.
+template <int QB>
+__global__ void __launch_bounds__(kPreThreads) rmsnorm_quantize_kernel(const void* __restrict__ x, int dt, int64_t ldx,
+                                                                       const void* __restrict__ weight, float eps,
+                                                                       int8_t* __restrict__ q, float* __restrict__ sx, int M, int K,
+                                                                       int nb, int vec_in, int vec_out) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    constexpr int LPB = QB / 8;
+    __shared__ float warp_sum[kPreThreads / 32];
+    const int m = blockIdx.x, tid = threadIdx.x;
+    const int upr = nb * LPB;                                   // units per row, padded to whole blocks
+    const bool hold = upr <= kPreHold * kPreThreads;
+    const int64_t row_off = (int64_t)m * ldx;
+    float f[kPreHold][8];
+    float ss = 0.0f;
+    if (hold) {
+#pragma unroll
+        for (int i = 0; i < kPreHold; ++i) {
+            const int k = (i * kPreThreads + tid) * 8;
+            if (k < K) load8(f[i], x, row_off, k, K, dt, vec_in != 0);
+            else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[i][e] = 0.0f;
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss = __fmaf_rn(f[i][e], f[i][e], ss);
+        }
+    } else {
+        for (int u = tid; u < upr; u += kPreThreads) {
+            const int k = u * 8;
+            if (k >= K) break;
+            float t[8];
+            load8(t, x, row_off, k, K, dt, vec_in != 0);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss = __fmaf_rn(t[e], t[e], ss);
+        }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    if ((tid & 31) == 0) warp_sum[tid >> 5] = ss;
+    __syncthreads();
+    float total = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kPreThreads / 32; ++w) total += warp_sum[w];
+    const float rstd = rsqrtf(__fadd_rn(__fdiv_rn(total, (float)K), eps));
+    const bool short_mantissa = dt != BI8_F32;
+    for (int i = 0; i * kPreThreads < upr; ++i) {
+        const int u = i * kPreThreads + tid, k = u * 8;
+        const bool valid = u < upr && k < K;
+        float y[8];
+        if (hold && i < kPreHold) {
+#pragma unroll
+            for (int j = 0; j < kPreHold; ++j)
+                if (j == i) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) y[e] = f[j][e];
+                }
+        } else if (valid) {
+            load8(y, x, row_off, k, K, dt, vec_in != 0);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) y[e] = 0.0f;
+        }
+        if (valid) {
+            float w8[8];
+            if (weight) load8(w8, weight, 0, k, K, dt, vec_in != 0);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                float v = __fmul_rn(y[e], rstd);
+                if (weight) v = __fmul_rn(v, w8[e]);
+                y[e] = round_to(v, dt);
+            }
+        }
+        quantize_unit<QB>(y, valid, short_mantissa, q, sx, m, k, M, K, vec_out != 0);
+    }
+}
+
+// One thread per unit of eight elements, as in the decode quantizer.
+template <int QB>
+__global__ void __launch_bounds__(kPreThreads) silu_mul_quantize_kernel(const void* __restrict__ gate, const void* __restrict__ up,
+                                                                        int dt, int64_t ldx, int8_t* __restrict__ q,
+                                                                        float* __restrict__ sx, int M, int K, int nb, int vec_in,
+                                                                        int vec_out) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    constexpr int LPB = QB / 8;
+    const int upr = nb * LPB;
+    const int64_t u = (int64_t)blockIdx.x * kPreThreads + threadIdx.x;
+    const int m = (int)(u / upr), k = (int)(u % upr) * 8;
+    const bool valid = m < M && k < K;
+    float y[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) y[e] = 0.0f;
+    if (valid) {
+        float g[8], v[8];
+        load8(g, gate, (int64_t)m * ldx, k, K, dt, vec_in != 0);
+        load8(v, up, (int64_t)m * ldx, k, K, dt, vec_in != 0);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float s = round_to(__fdiv_rn(g[e], __fadd_rn(1.0f, expf(-g[e]))), dt);
+            y[e] = round_to(__fmul_rn(s, v[e]), dt);
+        }
+    }
+    quantize_unit<QB>(y, valid, dt != BI8_F32, q, sx, m, k, M, K, vec_out != 0);
+}
+
+}  // namespace
+
+int launch_quantize_pre(int op, const void* x, const void* x2, int dt, int64_t ldx, const void* weight, float eps, int8_t* q, float* sx,
+                        int64_t M, int64_t K, int block, cudaStream_t st) {
+    if (M == 0 || K == 0) return BI8_OK;
+    if (M > 0x7fffffff || K > 0x3fffffff) return fail(BI8_ERR_LIMIT, "quantize_pre: M or K too large");
+    const int esz = dt == BI8_F32 ? 4 : 2;
+    const int nb = (int)((K + block - 1) / block);
+    const bool rows16 = (ldx * esz) % 16 == 0 && K % 8 == 0;
+    const int vec_in = rows16 && aligned(x, 16) && (!x2 || aligned(x2, 16)) && (!weight || aligned(weight, 16));
+    const int vec_out = K % 8 == 0 && aligned(q, 8);
+    if (op == BI8_PRE_RMSNORM) {
+        const unsigned grid = (unsigned)M;
+#define BI8_PRE_RMS(QB)                                                                                                     \
+    rmsnorm_quantize_kernel<QB><<<grid, kPreThreads, 0, st>>>(x, dt, ldx, weight, eps, q, sx, (int)M, (int)K, nb, vec_in, vec_out)
+        switch (block) {
+            case 32: BI8_PRE_RMS(32); break;
+            case 64: BI8_PRE_RMS(64); break;
+            case 128: BI8_PRE_RMS(128); break;
+            default: return fail(BI8_ERR_BLOCK, "quantize_pre supports block 32, 64, 128 (got %d)", block);
+        }
+#undef BI8_PRE_RMS
+    } else if (op == BI8_PRE_SILU_MUL) {
+        if (!x2) return fail(BI8_ERR_NULL, "quantize_pre: the gated activation needs its second operand");
+        const int64_t units = M * nb * (block / 8);
+        const unsigned grid = (unsigned)((units + kPreThreads - 1) / kPreThreads);
+#define BI8_PRE_SILU(QB)                                                                                                    \
+    silu_mul_quantize_kernel<QB><<<grid, kPreThreads, 0, st>>>(x, x2, dt, ldx, q, sx, (int)M, (int)K, nb, vec_in, vec_out)
+        switch (block) {
+            case 32: BI8_PRE_SILU(32); break;
+            case 64: BI8_PRE_SILU(64); break;
+            case 128: BI8_PRE_SILU(128); break;
+            default: return fail(BI8_ERR_BLOCK, "quantize_pre supports block 32, 64, 128 (got %d)", block);
+        }
+#undef BI8_PRE_SILU
+    } else {
+        return fail(BI8_ERR_SHAPE, "quantize_pre: unknown operation code %d", op);
+    }
+    BI8_CUDA_TRY(cudaGetLastError());
+    return BI8_OK;
+}
+
+}  // namespace bi8

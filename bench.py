@@ -344,7 +344,64 @@ def extras(dev, hbm_gbs, flush):
                                 "tops": ops / ms / 1e9, "gbs": nbytes / ms / 1e6,
                                 "frac_int8_nominal": ops / ms / 1e9 / INT8_NOMINAL_TOPS, "frac_hbm": nbytes / ms / 1e6 / hbm_gbs})
         del wqs, wss
+    try:
+        out["fused_producers"] = fused_producers(dev, hbm_gbs, flush)
+    except Exception as e:                # comparison table only
+        out["fused_producers"] = {"error": f"{type(e).__name__}: {e}"}
     return out
+
+
+def fused_producers(dev, hbm_gbs, flush):
+    """The quantizers with the producing elementwise step fused in front, and the layer call with the residual sum fused
+    behind, against the same steps as separate kernels: the stand-alone quantizers at M = 4096 (HBM-bound: algorithmic
+    bytes = input + int8 + scales) and the MLP half of a Llama-7B layer at M = 8 (rms_norm -> gate_up -> silu * up ->
+    down -> residual sum), both forms producing identical tensors except for the last bit of the normalisation."""
+    import block_linear_config as cfg
+    import torch.nn.functional as F
+    from triton_functions import (pre_quantize_matmul_block_rowwise_dequantize as pre_mm, quantize_block_rowwise,
+                                  quantize_matmul_block_rowwise_dequantize as q_mm, rmsnorm_quantize_block_rowwise,
+                                  silu_mul_quantize_block_rowwise)
+    cfg.GROUP_SIZE, cfg.INPUT_OUTPUT_TORCH_TYPE = BLOCK, torch.bfloat16
+    res = {"quantizers": [], "mlp_half_decode": None}
+    m, h, f = 4096, 4096, 11008
+    g = torch.Generator(device=dev).manual_seed(77)
+    copies = 5                                                   # 5 x (32 + 180) MB of inputs: larger than L2
+    xs = [torch.randn((m, h), device=dev, generator=g).to(torch.bfloat16) for _ in range(copies)]
+    gus = [torch.randn((m, 2 * f), device=dev, generator=g).to(torch.bfloat16) for _ in range(copies)]
+    rows = (("rmsnorm_quantize", lambda i: rmsnorm_quantize_block_rowwise(xs[i % copies]),
+             lambda i: quantize_block_rowwise(F.rms_norm(xs[i % copies], (h,), eps=1e-5)), m * h * (2 + 1 + 4 / BLOCK), [m, h]),
+            ("silu_mul_quantize", lambda i: silu_mul_quantize_block_rowwise(gus[i % copies][:, :f], gus[i % copies][:, f:]),
+             lambda i: quantize_block_rowwise(F.silu(gus[i % copies][:, :f]) * gus[i % copies][:, f:]), m * f * (4 + 1 + 4 / BLOCK), [m, f]))
+    for name, fused, separate, nbytes, shape in rows:
+        ms_f, ms_s = time_graph(fused, 2 * copies), time_graph(separate, 2 * copies)
+        res["quantizers"].append({"name": name, "shape": shape, "us": ms_f * 1e3, "frac_hbm": nbytes / ms_f / 1e6 / hbm_gbs,
+                                  "us_separate_kernels": ms_s * 1e3})
+    del xs, gus
+    m = 8
+    wcopies = 3                                                  # 3 x 135 MB of weights
+    gate_up, down = [], []
+    for c in range(wcopies):
+        w1 = (torch.randn((2 * f, h), device=dev, generator=g) * 0.02).to(torch.bfloat16)
+        w2 = (torch.randn((h, f), device=dev, generator=g) * 0.02).to(torch.bfloat16)
+        gate_up.append(quantize_block_rowwise(w1))
+        down.append(quantize_block_rowwise(w2))
+        del w1, w2
+    x = torch.randn((m, h), device=dev, generator=g).to(torch.bfloat16)
+
+    def separate(i):
+        (w1, s1), (w2, s2) = gate_up[i % wcopies], down[i % wcopies]
+        gu = q_mm(F.rms_norm(x, (h,), eps=1e-5), w1.t(), s1)
+        return x + q_mm(F.silu(gu[:, :f]) * gu[:, f:], w2.t(), s2)
+
+    def fused(i):
+        (w1, s1), (w2, s2) = gate_up[i % wcopies], down[i % wcopies]
+        gu = pre_mm("rmsnorm", x, w1.t(), s1, eps=1e-5)
+        return pre_mm("silu_mul", gu[:, :f], w2.t(), s2, x2=gu[:, f:], residual=x)
+
+    ms_f, ms_s = time_graph(fused, 12), time_graph(separate, 12)
+    res["mlp_half_decode"] = {"M": m, "us": ms_f * 1e3, "us_separate_kernels": ms_s * 1e3, "launches": "6 against 10",
+                              "timing": "CUDA-graph replays of 12 calls rotating over 3 weight copies (405 MB)"}
+    return res
 
 
 def kernel_rows(extra, hbm_gbs):
@@ -356,6 +413,9 @@ def kernel_rows(extra, hbm_gbs):
             rows.append({"name": name, "shape": r["shape"], "us": round(r["us"], 2), "bound": "hbm", "frac": round(r["frac_hbm"], 3)})
     for r in extra.get("quantize_dual", []):
         rows.append({"name": "quantize_dual", "shape": r["shape"], "us": round(r["us"], 2), "bound": "hbm", "frac": round(r["frac_hbm"], 3)})
+    fp = extra.get("fused_producers") or {}
+    for r in fp.get("quantizers", []) if isinstance(fp, dict) else []:
+        rows.append({"name": r["name"], "shape": r["shape"], "us": round(r["us"], 2), "bound": "hbm", "frac": round(r["frac_hbm"], 3)})
     for r in extra.get("gemm", []):
         hbm_bound = r["M"] <= 128
         rows.append({"name": "gemm", "shape": [r["M"], r["K"], r["N"]], "us": round(r["us"], 2), "bound": "hbm" if hbm_bound else "tensor",
@@ -813,6 +873,7 @@ def run_ours(args):
         extra["timing"] = ("us: CUDA-graph replays over rotating inputs larger than L2, median of 5 replays; us_flushed and the "
                            "GEMM rows marked so: CUDA events around one launch behind a 256 MB fill, median of 7")
         roofline["kernels"] = kernel_rows(extra, hbm_gbs)
+        roofline["fused_producers"] = extra.get("fused_producers")
         try:
             roofline["k512_sweep"] = k512_sweep(dev, flush)
         except Exception as e:            # comparator table only

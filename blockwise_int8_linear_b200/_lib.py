@@ -24,8 +24,11 @@ EXPORTS = [
     "bi8_version", "bi8_last_error_string", "bi8_device_status", "bi8_quantize_rowwise", "bi8_quantize_colwise", "bi8_quantize_dual", "bi8_peer_allreduce", "bi8_peer_allreduce_buffer_bytes", "bi8_row_parallel_linear",
     "bi8_dequantize_rowwise", "bi8_gemm_dequant", "bi8_gemm_workspace_bytes", "bi8_gemm_block_partials",
     "bi8_gemm_dequant_fused_quant", "bi8_mma_peak_probe", "bi8_gemm_dequant_static", "bi8_gemm_static_scratch_bytes",
-    "bi8_gemm_wait_selftest", "bi8_stream_capture_id",
+    "bi8_gemm_wait_selftest", "bi8_stream_capture_id", "bi8_quantize_rowwise_pre", "bi8_gemm_dequant_fused_pre",
+    "bi8_row_parallel_linear_pre",
 ]
+ADDEND_FULL = 0x100
+PRE_NONE, PRE_RMSNORM, PRE_SILU_MUL = 0, 1, 2
 
 _lib = None
 
@@ -55,6 +58,8 @@ def lib() -> ctypes.CDLL:
         L.bi8_peer_allreduce_buffer_bytes.restype = sz
         L.bi8_row_parallel_linear.argtypes = [vp, i32, i64, vp, vp, vp, i64, vp, vp, i64, i64, i64, i32, vp, sz, c.POINTER(vp), i32, i32,
                                               i64, vp, i32, vp, i32, c.c_uint, i32, vp]
+        L.bi8_row_parallel_linear_pre.argtypes = [i32, vp, vp, i32, i64, vp, c.c_float, vp, vp, vp, i64, vp, vp, i64, i64, i64, i32, vp, sz,
+                                                  c.POINTER(vp), i32, i32, i64, vp, i32, vp, i32, c.c_uint, i32, vp]
         L.bi8_peer_allreduce.argtypes = [c.POINTER(vp), i32, i32, i64, vp, i64, i64, vp, i32, vp, i32, c.c_uint, vp]
         L.bi8_gemm_dequant.argtypes = [vp, i64, vp, i64, vp, vp, vp, i32, vp, i64, i32, i64, i64, i64, i32, vp, sz, i32, vp]
         L.bi8_gemm_workspace_bytes.argtypes = [i64, i64, i64, i32]
@@ -62,12 +67,16 @@ def lib() -> ctypes.CDLL:
         L.bi8_gemm_block_partials.argtypes = [vp, i64, vp, i64, vp, i64, i64, i64, i32, i32, vp]
         L.bi8_gemm_dequant_fused_quant.argtypes = [vp, i32, i64, vp, vp, vp, i64, vp, vp, i32, vp, i64, i32, i64, i64, i64, i32, vp,
                                                    sz, i32, vp]
+        L.bi8_quantize_rowwise_pre.argtypes = [i32, vp, vp, i32, i64, vp, c.c_float, vp, vp, i64, i64, i32, vp]
+        L.bi8_gemm_dequant_fused_pre.argtypes = [i32, vp, vp, i32, i64, vp, c.c_float, vp, vp, vp, i64, vp, vp, i32, vp, i64, vp, i64, i32,
+                                                 i64, i64, i64, i32, vp, sz, i32, vp]
         L.bi8_gemm_wait_selftest.argtypes = [vp, i64, vp, i64, vp, vp, vp, i64, i32, i64, i64, i64, i32, c.c_uint, i32, vp]
         L.bi8_stream_capture_id.argtypes = [vp, c.POINTER(c.c_ulonglong)]
         L.bi8_mma_peak_probe.argtypes = [i32, c.POINTER(c.c_float), c.POINTER(i32)]
         for name in EXPORTS:
             fn = getattr(L, name)
-            if name not in ("bi8_last_error_string", "bi8_gemm_workspace_bytes", "bi8_gemm_static_scratch_bytes"):
+            if name not in ("bi8_last_error_string", "bi8_gemm_workspace_bytes", "bi8_gemm_static_scratch_bytes",
+                            "bi8_peer_allreduce_buffer_bytes"):
                 fn.restype = i32
         _lib = L
     return _lib

@@ -14,6 +14,7 @@ from .triton_functions import (
     dequantize_block_rowwise,
     int8_matmul_block64_rowwise_dequantize,
     quantize_block_colwise,
+    pre_quantize_matmul_block_rowwise_dequantize,
     quantize_block_dual,
     quantize_block_rowwise,
     quantize_matmul_block_rowwise_dequantize,
@@ -201,6 +202,23 @@ class BlockInt8Linear(nn.Linear):
         return int8_matmul_block64_rowwise_dequantize(
             X_int8, self.W_int8.t(), state_X, self.state_W, self.bias
         ).view(*x.size()[:-1], -1)
+
+    def infer_pre(self, x, op="none", x2=None, norm_weight=None, eps=1e-5, residual=None):
+        """``infer`` with the elementwise step that produces this projection's input fused into the quantizer, and the
+        residual sum that consumes its output fused behind the GEMM (neither exists in the reference, whose ``infer``
+        quantizes a stored tensor, ``block_linear.py:141``):
+
+        ``op='rmsnorm'``   ``infer(rms_norm(x, eps) [* norm_weight])``
+        ``op='silu_mul'``  ``infer(F.silu(x) * x2)``
+        ``residual``       ``residual + infer(...)`` in the activation type; ``residual`` has the output's shape."""
+        if not hasattr(self, "W_int8"):
+            self.prepare_for_eval()
+        X = x.reshape(-1, x.size(-1))
+        X2 = x2.reshape(-1, x2.size(-1)) if x2 is not None else None
+        R = residual.reshape(-1, residual.size(-1)) if residual is not None else None
+        out = pre_quantize_matmul_block_rowwise_dequantize(op, X, self.W_int8.t(), self.state_W, self.bias, x2=X2,
+                                                           norm_weight=norm_weight, eps=eps, residual=R)
+        return out.view(*x.size()[:-1], -1)
 
     def forward(self, x):
         if not self.training:

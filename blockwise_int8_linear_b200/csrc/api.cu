@@ -169,7 +169,7 @@ size_t bi8_peer_allreduce_buffer_bytes(int world, int64_t capacity) {
 int bi8_peer_allreduce(void* const* peer_bufs, int rank, int world, int64_t capacity, const float* partial, int64_t M, int64_t N,
                        const void* bias, int bias_dtype, void* out, int out_dtype, unsigned wait_limit_us, void* stream) {
     if (!peer_bufs || !partial || !out) return fail(BI8_ERR_NULL, "peer all-reduce: null pointer");
-    if (!dtype_ok(out_dtype) || (bias && !dtype_ok(bias_dtype))) return fail(BI8_ERR_DTYPE, "peer all-reduce: unknown dtype code");
+    if (!dtype_ok(out_dtype) || (bias && !dtype_ok(bias_dtype & ~BI8_ADDEND_FULL))) return fail(BI8_ERR_DTYPE, "peer all-reduce: unknown dtype code");
     return launch_peer_allreduce(peer_bufs, rank, world, capacity, partial, M, N, bias, bias_dtype, out, out_dtype, wait_limit_us,
                                  static_cast<cudaStream_t>(stream));
 }
@@ -257,12 +257,85 @@ int bi8_gemm_dequant_fused_quant(const void* x, int x_dtype, int64_t ldx, int8_t
                             workspace_bytes, flags & ~BI8_GEMM_FORCE_SKINNY, stream);
 }
 
-int bi8_row_parallel_linear(const void* x, int x_dtype, int64_t ldx, int8_t* xq, float* sx, const int8_t* Wq, int64_t ldw,
-                            const float* sW, float* partial, int64_t M, int64_t N, int64_t K, int block, void* workspace,
-                            size_t workspace_bytes, void* const* peer_bufs, int rank, int world, int64_t capacity, const void* bias,
-                            int bias_dtype, void* out, int out_dtype, unsigned wait_limit_us, int flags, void* stream) {
+int bi8_quantize_rowwise_pre(int op, const void* x, const void* x2, int x_dtype, int64_t ldx, const void* weight, float eps, int8_t* q,
+                             float* scales, int64_t M, int64_t K, int block, void* stream) {
+    if (!dtype_ok(x_dtype)) return fail(BI8_ERR_DTYPE, "quantize_rowwise_pre: unknown dtype code %d", x_dtype);
+    if (op != BI8_PRE_NONE && op != BI8_PRE_RMSNORM && op != BI8_PRE_SILU_MUL)
+        return fail(BI8_ERR_SHAPE, "quantize_rowwise_pre: unknown operation code %d", op);
+    if (M < 0 || K < 0 || ldx < K) return fail(BI8_ERR_SHAPE, "quantize_rowwise_pre: bad shape M %lld K %lld ldx %lld", (long long)M, (long long)K, (long long)ldx);
+    if (M == 0 || K == 0) return BI8_OK;
+    if (!x || !q || !scales || (op == BI8_PRE_SILU_MUL && !x2)) return fail(BI8_ERR_NULL, "quantize_rowwise_pre: null pointer");
+    const size_t esz = dtype_size(x_dtype);
+    if (!aligned(x, esz) || (x2 && !aligned(x2, esz)) || (weight && !aligned(weight, esz)) || !aligned(scales, 4))
+        return fail(BI8_ERR_ALIGN, "quantize_rowwise_pre: pointer not element aligned");
+    return launch_quantize_pre(op, x, x2, x_dtype, ldx, weight, eps, q, scales, M, K, block, static_cast<cudaStream_t>(stream));
+}
+
+int bi8_gemm_dequant_fused_pre(int op, const void* x, const void* x2, int x_dtype, int64_t ldx, const void* norm_weight, float eps,
+                               int8_t* xq, float* sx, const int8_t* Wq, int64_t ldw, const float* sW, const void* bias, int bias_dtype,
+                               const void* residual, int64_t ldr, void* C, int64_t ldc, int out_dtype, int64_t M, int64_t N, int64_t K,
+                               int block, void* workspace, size_t workspace_bytes, int flags, void* stream) {
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (M > 0 && K > 0 && (!xq || !sx)) return fail(BI8_ERR_WORKSPACE, "gemm_dequant_fused_pre: the xq / sx scratch is required");
+    if (residual && ldr < N) return fail(BI8_ERR_SHAPE, "gemm_dequant_fused_pre: residual row pitch smaller than the row");
+    if (!dtype_ok(out_dtype)) return fail(BI8_ERR_DTYPE, "gemm_dequant_fused_pre: unknown output dtype code %d", out_dtype);
+    if (residual && !aligned(residual, dtype_size(out_dtype))) return fail(BI8_ERR_ALIGN, "gemm_dequant_fused_pre: residual not element aligned");
+    if (M == 0 || N == 0) return BI8_OK;
+    // C over the residual: only the decode path reads an element of the residual in the thread that then writes C
+    const size_t osz = dtype_size(out_dtype);
+    const char *c0 = static_cast<const char*>(C), *c1 = c0 + ((M - 1) * ldc + N) * osz;
+    const char *r0 = static_cast<const char*>(residual), *r1 = residual ? r0 + ((M - 1) * ldr + N) * osz : r0;
+    const bool overlap = residual && C && r0 < c1 && c0 < r1;
+    if (overlap && (residual != C || ldr != ldc))
+        return fail(BI8_ERR_SHAPE, "gemm_dequant_fused_pre: residual and C overlap without being the same tensor");
+    if (op == BI8_PRE_NONE && !residual)
+        return bi8_gemm_dequant_fused_quant(x, x_dtype, ldx, xq, sx, Wq, ldw, sW, bias, bias_dtype, C, ldc, out_dtype, M, N, K, block,
+                                            workspace, workspace_bytes, flags, stream);
+    // the decode path: this op's quantizer in the decode quantizer's place, the GEMM overlapped with it, the residual
+    // added by the kernel that writes C (through the bias operand, which gets a row pitch)
+    const bool forced = (flags & (BI8_GEMM_FORCE_GENERIC | BI8_GEMM_FORCE_TC | BI8_GEMM_FORCE_SMALLM | BI8_GEMM_QUANT_IN_KERNEL)) != 0;
+    GemmArgs g{xq, K, Wq, ldw, sx, sW, bias, bias_dtype, C, ldc, out_dtype, nullptr, M, N, K, block, flags, workspace, workspace_bytes};
+    if (!forced && K > 0 && K % 16 == 0 && aligned(xq, 16) && gemm_skinny_applicable(g)) {
+        int rc = check_gemm(g, false);
+        if (rc != BI8_OK) return rc;
+        const bool in_kernel_residual = residual && !bias;
+        if (overlap && !in_kernel_residual)
+            return fail(BI8_ERR_ALIGN, "gemm_dequant_fused_pre: C may be the residual itself only without bias");
+        if (in_kernel_residual) {
+            g.bias = residual;
+            g.bias_dtype = out_dtype;
+            g.bias_ld = ldr;
+        }
+        const bool x_vec = dtype_ok(x_dtype) && x && aligned(x, 16) && (ldx * dtype_size(x_dtype)) % 16 == 0 && K % 8 == 0 && ldx >= K;
+        if (op == BI8_PRE_NONE && x_vec) rc = launch_skinny_quantize(x, x_dtype, ldx, xq, sx, M, K, block, st);
+        else rc = bi8_quantize_rowwise_pre(op, x, x2, x_dtype, ldx, norm_weight, eps, xq, sx, M, K, block, stream);
+        if (rc != BI8_OK) return rc;
+        // every quantizer of this library may be overlapped with the GEMM's set-up and first weight copies: none of them
+        // writes weights, and the GEMM waits for the quantizer's completion before it reads the activations
+        g.after_own_quantizer = true;
+        rc = launch_gemm_skinny(g, st);
+        if (rc != BI8_OK || !residual || in_kernel_residual) return rc;
+        return launch_residual_add(C, ldc, residual, ldr, out_dtype, M, N, st);
+    }
+    if (overlap)
+        return fail(BI8_ERR_ALIGN, "gemm_dequant_fused_pre: C may be the residual itself only on the decode path (M <= 64, N %% 4 == 0, "
+                                   "K %% 16 == 0, workspace given, no bias)");
+    int rc = bi8_quantize_rowwise_pre(op, x, x2, x_dtype, ldx, norm_weight, eps, xq, sx, M, K, block, stream);
+    if (rc != BI8_OK) return rc;
+    rc = bi8_gemm_dequant(xq, K, Wq, ldw, sx, sW, bias, bias_dtype, C, ldc, out_dtype, M, N, K, block, workspace, workspace_bytes,
+                          flags & ~BI8_GEMM_QUANT_IN_KERNEL, stream);
+    if (rc != BI8_OK || !residual) return rc;
+    return launch_residual_add(C, ldc, residual, ldr, out_dtype, M, N, st);
+}
+
+int bi8_row_parallel_linear_pre(int op, const void* x, const void* x2, int x_dtype, int64_t ldx, const void* norm_weight, float eps,
+                                int8_t* xq, float* sx, const int8_t* Wq, int64_t ldw, const float* sW, float* partial, int64_t M, int64_t N,
+                                int64_t K, int block, void* workspace, size_t workspace_bytes, void* const* peer_bufs, int rank, int world,
+                                int64_t capacity, const void* bias, int bias_dtype, void* out, int out_dtype, unsigned wait_limit_us,
+                                int flags, void* stream) {
     if (!x || !xq || !sx || !Wq || !sW || !partial || !peer_bufs || !out) return fail(BI8_ERR_NULL, "row_parallel_linear: null pointer");
-    if (!dtype_ok(x_dtype) || !dtype_ok(out_dtype) || (bias && !dtype_ok(bias_dtype))) return fail(BI8_ERR_DTYPE, "row_parallel_linear: unknown dtype code");
+    if (!dtype_ok(x_dtype) || !dtype_ok(out_dtype) || (bias && !dtype_ok(bias_dtype & ~BI8_ADDEND_FULL)))
+        return fail(BI8_ERR_DTYPE, "row_parallel_linear: unknown dtype code");
     if (M <= 0 || N <= 0 || K <= 0 || ldx < K || ldw < K) return fail(BI8_ERR_SHAPE, "row_parallel_linear: bad shape M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
     if (!aligned(partial, 16) || !aligned(out, 16)) return fail(BI8_ERR_ALIGN, "row_parallel_linear: partial and out must be 16-byte aligned");
     PeerArgs pa;
@@ -270,12 +343,14 @@ int bi8_row_parallel_linear(const void* x, int x_dtype, int64_t ldx, int8_t* xq,
     if (rc != BI8_OK) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool forced = (flags & (BI8_GEMM_FORCE_GENERIC | BI8_GEMM_FORCE_TC | BI8_GEMM_FORCE_SMALLM | BI8_GEMM_QUANT_IN_KERNEL)) != 0;
-    if (!forced && aligned(x, 16) && (ldx * dtype_size(x_dtype)) % 16 == 0 && K % 16 == 0 && aligned(xq, 16)) {
+    const bool x_vec = aligned(x, 16) && (ldx * dtype_size(x_dtype)) % 16 == 0;
+    if (!forced && (x_vec || op != BI8_PRE_NONE) && K % 16 == 0 && aligned(xq, 16)) {
         // decode-sized M: quantizer, weight-streaming GEMM, and a reduction kernel that sums the tile parts AND the ranks
         GemmArgs g{xq, K, Wq, ldw, sx, sW, nullptr, 0, partial, N, BI8_F32, nullptr, M, N, K, block, flags, workspace, workspace_bytes};
         if (gemm_skinny_applicable(g)) {
             PeerEpilogue pe{&pa, bias, bias_dtype, out, out_dtype, peer_wait_limit_cycles(wait_limit_us)};
-            rc = launch_skinny_quantize(x, x_dtype, ldx, xq, sx, M, K, block, st);
+            if (op == BI8_PRE_NONE) rc = launch_skinny_quantize(x, x_dtype, ldx, xq, sx, M, K, block, st);
+            else rc = bi8_quantize_rowwise_pre(op, x, x2, x_dtype, ldx, norm_weight, eps, xq, sx, M, K, block, stream);
             if (rc != BI8_OK) return rc;
             g.after_own_quantizer = true;
             g.peer = &pe;
@@ -283,10 +358,19 @@ int bi8_row_parallel_linear(const void* x, int x_dtype, int64_t ldx, int8_t* xq,
         }
     }
     // other shapes: the layer's two steps into `partial`, then the stand-alone reduction
-    rc = bi8_gemm_dequant_fused_quant(x, x_dtype, ldx, xq, sx, Wq, ldw, sW, nullptr, 0, partial, N, BI8_F32, M, N, K, block, workspace,
-                                      workspace_bytes, flags, stream);
+    rc = bi8_gemm_dequant_fused_pre(op, x, x2, x_dtype, ldx, norm_weight, eps, xq, sx, Wq, ldw, sW, nullptr, 0, nullptr, 0, partial, N,
+                                    BI8_F32, M, N, K, block, workspace, workspace_bytes, flags, stream);
     if (rc != BI8_OK) return rc;
     return launch_peer_allreduce(peer_bufs, rank, world, capacity, partial, M, N, bias, bias_dtype, out, out_dtype, wait_limit_us, st);
+}
+
+int bi8_row_parallel_linear(const void* x, int x_dtype, int64_t ldx, int8_t* xq, float* sx, const int8_t* Wq, int64_t ldw,
+                            const float* sW, float* partial, int64_t M, int64_t N, int64_t K, int block, void* workspace,
+                            size_t workspace_bytes, void* const* peer_bufs, int rank, int world, int64_t capacity, const void* bias,
+                            int bias_dtype, void* out, int out_dtype, unsigned wait_limit_us, int flags, void* stream) {
+    return bi8_row_parallel_linear_pre(BI8_PRE_NONE, x, nullptr, x_dtype, ldx, nullptr, 0.0f, xq, sx, Wq, ldw, sW, partial, M, N, K, block,
+                                       workspace, workspace_bytes, peer_bufs, rank, world, capacity, bias, bias_dtype, out, out_dtype,
+                                       wait_limit_us, flags, stream);
 }
 
 int bi8_stream_capture_id(void* stream, unsigned long long* id) {

@@ -58,6 +58,11 @@ int launch_quantize_tile(const void* x, int dt, int64_t ldx, int8_t* q_col, floa
 size_t peer_allreduce_buffer_bytes(int world, int64_t capacity);
 int launch_peer_allreduce(void* const* peer_bufs, int rank, int world, int64_t capacity, const float* partial, int64_t M, int64_t N,
                           const void* bias, int bias_dtype, void* out, int out_dtype, unsigned wait_limit_us, cudaStream_t st);
+// quantizers with the producing elementwise step in front (quantize_pre.cu); q has row pitch K
+int launch_quantize_pre(int op, const void* x, const void* x2, int dt, int64_t ldx, const void* weight, float eps, int8_t* q, float* sx,
+                        int64_t M, int64_t K, int block, cudaStream_t st);
+// C[m, n] += R[m, n] in the type of C (C may be R)
+int launch_residual_add(void* C, int64_t ldc, const void* R, int64_t ldr, int dt, int64_t M, int64_t N, cudaStream_t st);
 int launch_dequantize_rowwise(const int8_t* q, const float* s, void* out, int dt, int64_t M, int64_t K,
                               int block, cudaStream_t st);
 
@@ -97,6 +102,7 @@ struct GemmArgs {
     unsigned wait_limit_us = 0;         // diagnostic: limit of the general kernel's bounded waits (0 = default, about 2 s)
     int skip_stage = -1;                // diagnostic: the general kernel's producer leaves this stage of its first item out
     const PeerEpilogue* peer = nullptr; // decode kernel only: reduce over the ranks inside its reduction kernel
+    int64_t bias_ld = 0;                // decode kernel only: row pitch of `bias` in elements; non-zero makes it an [M, N] addend
 };
 
 bool gemm_tc_applicable(const GemmArgs& g, const char** why);

@@ -92,6 +92,7 @@ struct SkParams {
     int64_t ldx;
     int x_dtype;
     const void* bias;
+    int64_t bias_ld;        // row pitch of `bias` in elements: 0 = one row for all (a bias), else an [M, N] addend (a residual)
     void* C;
     float* ws;
     int* status;
@@ -106,15 +107,16 @@ struct SkParams {
 // first (tile, stage) pair of CTA c when `total` pairs are divided over `ctas` CTAs
 __host__ __device__ __forceinline__ long long range_start(long long c, long long total, long long ctas) { return c * total / ctas; }
 
-// C[m, n] = cast(acc) (+ cast(bias[n]) in the output type: reference lines 125-131)
-__device__ __forceinline__ void finish_store(float acc, int m, int n, const void* bias, int bias_dtype, void* C, int64_t ldc,
-                                             int out_dtype) {
+// C[m, n] = cast(acc) (+ cast(bias[m * bias_ld + n]) in the output type: reference lines 125-131)
+__device__ __forceinline__ void finish_store(float acc, int m, int n, const void* bias, int bias_dtype, int64_t bias_ld, void* C,
+                                             int64_t ldc, int out_dtype) {
     float bv = 0.0f;
     const bool hb = bias != nullptr;
     if (hb) {
-        if (bias_dtype == BI8_BF16) bv = __bfloat162float(static_cast<const __nv_bfloat16*>(bias)[n]);
-        else if (bias_dtype == BI8_F16) bv = __half2float(static_cast<const __half*>(bias)[n]);
-        else bv = static_cast<const float*>(bias)[n];
+        const int64_t bi = (int64_t)m * bias_ld + n;
+        if (bias_dtype == BI8_BF16) bv = __bfloat162float(static_cast<const __nv_bfloat16*>(bias)[bi]);
+        else if (bias_dtype == BI8_F16) bv = __half2float(static_cast<const __half*>(bias)[bi]);
+        else bv = static_cast<const float*>(bias)[bi];
     }
     const int64_t o = (int64_t)m * ldc + n;
     if (out_dtype == BI8_F32) {
@@ -499,7 +501,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
 #pragma unroll
                     for (int i = 0; i < CW; ++i) {
                         const int m = chunk * CW + i;
-                        if (m < p.M) finish_store(acc[i], m, n, p.bias, p.bias_dtype, p.C, p.ldc, p.out_dtype);
+                        if (m < p.M) finish_store(acc[i], m, n, p.bias, p.bias_dtype, p.bias_ld, p.C, p.ldc, p.out_dtype);
                     }
                 }
             } else {
@@ -531,6 +533,10 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
 template <int QB>
 __global__ void __launch_bounds__(256) skinny_quantize_kernel(const void* __restrict__ x, int x_dtype, int64_t ldx,
                                                               int8_t* __restrict__ q, float* __restrict__ sx, int M, int K, int nb) {
+    // Launched with programmatic stream serialisation itself: resident while the kernel before it (the previous layer's
+    // reduction) finishes.  Its own dependent, the GEMM, is released only after that kernel has completed, so that
+    // whatever the GEMM reads early (weights, weight scales) has been at rest for a full kernel boundary.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr int LPB = QB / 8;
     const int upr = nb * LPB;                                  // units per row, padded to whole blocks
@@ -581,10 +587,12 @@ __global__ void __launch_bounds__(256) skinny_quantize_kernel(const void* __rest
 // already written by it.  One thread per output element (a thread per tile row with a loop over the activation rows
 // serialises the loads and is several times slower); `ctas` and `total_stages` are those of the GEMM launch, bns its BNS.
 __global__ void __launch_bounds__(256) skinny_reduce_kernel(const float* __restrict__ ws, long long total_stages, int ctas,
-                                                            int nks, int bns, const void* __restrict__ bias, int bias_dtype,
-                                                            void* __restrict__ C, int64_t ldc, int out_dtype, int M, int N) {
+                                                            int nks, int bns, const void* bias, int bias_dtype,
+                                                            int64_t bias_ld, void* C, int64_t ldc, int out_dtype, int M, int N) {
     // Launched with programmatic stream serialisation: the blocks may become resident while the GEMM still runs and do
     // their index arithmetic; griddepcontrol.wait returns when the GEMM grid has completed and its stores are visible.
+    // A quantizer of this library launched the same way behind this kernel (the next layer's) may become resident now.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
     const bool live = i < (int64_t)M * N;
     const int m = live ? (int)(i / N) : 0, n = live ? (int)(i % N) : 0;
@@ -610,7 +618,7 @@ __global__ void __launch_bounds__(256) skinny_reduce_kernel(const float* __restr
         for (int u = 0; u < 4; ++u)
             if (q + u < parts) acc = __fadd_rn(acc, v[u]);
     }
-    finish_store(acc, m, n, bias, bias_dtype, C, ldc, out_dtype);
+    finish_store(acc, m, n, bias, bias_dtype, bias_ld, C, ldc, out_dtype);
 }
 
 // The same reduction for a row-parallel layer: the tile sums are this rank's partial result, and instead of writing them
@@ -619,9 +627,10 @@ __global__ void __launch_bounds__(256) skinny_reduce_kernel(const float* __restr
 // GEMM wrote the tiles that one CTA covered completely.  Launched for every shape, divided tiles or not.
 __global__ void __launch_bounds__(kPeerThreads) skinny_reduce_peer_kernel(const float* __restrict__ ws, long long total_stages, int ctas,
                                                                           int nks, int bns, const float* __restrict__ part, int M,
-                                                                          int N, const PeerArgs a, const void* __restrict__ bias,
-                                                                          int bias_dtype, void* __restrict__ out, int out_dtype,
+                                                                          int N, const PeerArgs a, const void* bias,
+                                                                          int bias_dtype, void* out, int out_dtype,
                                                                           long long limit_cycles, int* status) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");       // as in skinny_reduce_kernel
     const int64_t count = (int64_t)M * N;
     const int64_t i = (int64_t)blockIdx.x * kPeerChunk + (int64_t)threadIdx.x * 4;
     const bool live = i < count;
@@ -733,10 +742,20 @@ int launch_skinny_quantize(const void* x, int x_dtype, int64_t ldx, int8_t* q, f
     const int nb = (int)((K + block - 1) / block);
     const int64_t units = M * nb * (block / 8);
     const unsigned blocks = (unsigned)((units + 255) / 256);
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;     // the kernel waits for its predecessor itself
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
     switch (block) {
-        case 32: skinny_quantize_kernel<32><<<blocks, 256, 0, st>>>(x, x_dtype, ldx, q, sx, (int)M, (int)K, nb); break;
-        case 64: skinny_quantize_kernel<64><<<blocks, 256, 0, st>>>(x, x_dtype, ldx, q, sx, (int)M, (int)K, nb); break;
-        case 128: skinny_quantize_kernel<128><<<blocks, 256, 0, st>>>(x, x_dtype, ldx, q, sx, (int)M, (int)K, nb); break;
+        case 32: BI8_CUDA_TRY(cudaLaunchKernelEx(&cfg, skinny_quantize_kernel<32>, x, x_dtype, ldx, q, sx, (int)M, (int)K, nb)); break;
+        case 64: BI8_CUDA_TRY(cudaLaunchKernelEx(&cfg, skinny_quantize_kernel<64>, x, x_dtype, ldx, q, sx, (int)M, (int)K, nb)); break;
+        case 128: BI8_CUDA_TRY(cudaLaunchKernelEx(&cfg, skinny_quantize_kernel<128>, x, x_dtype, ldx, q, sx, (int)M, (int)K, nb)); break;
         default: return fail(BI8_ERR_BLOCK, "skinny quantizer supports block 32, 64, 128 (got %d)", block);
     }
     BI8_CUDA_TRY(cudaGetLastError());
@@ -768,6 +787,7 @@ int launch_gemm_skinny(const GemmArgs& g, cudaStream_t st) {
     p.ldx = g.ldx;
     p.x_dtype = g.x_dtype;
     p.bias = g.bias;
+    p.bias_ld = g.bias_ld;
     p.C = g.C;
     p.ws = static_cast<float*>(g.workspace);
     p.status = device_status_ptr();
@@ -833,7 +853,7 @@ int launch_gemm_skinny(const GemmArgs& g, cudaStream_t st) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     BI8_CUDA_TRY(cudaLaunchKernelEx(&cfg, skinny_reduce_kernel, (const float*)p.ws, p.total_stages, grid, p.nks, bns,
-                                    g.bias, g.bias_dtype, g.C, g.ldc, g.out_dtype, (int)g.M, (int)g.N));
+                                    g.bias, g.bias_dtype, g.bias_ld, g.C, g.ldc, g.out_dtype, (int)g.M, (int)g.N));
     return BI8_OK;
 }
 

@@ -52,7 +52,7 @@ __device__ __forceinline__ uint32_t peer_sequence(const PeerArgs& a) { return *r
 // Steps 1-3 for the chunk blockIdx.x: `v` are this thread's four values (elements i0 .. i0+3 of the flattened [M, n_cols]
 // result, i0 = chunk * kPeerChunk + 4 * threadIdx.x; ignored where i0 >= count).  Must be called by all threads of the CTA.
 __device__ __forceinline__ void peer_exchange_store(const PeerArgs& a, uint32_t seq, float4 v, int64_t count, int64_t n_cols,
-                                                    const void* __restrict__ bias, int bias_dtype, void* __restrict__ out,
+                                                    const void* bias, int bias_dtype, void* out,
                                                     int out_dtype, long long limit_cycles, int* status) {
     __shared__ int ok_flag;
     const int tid = threadIdx.x;
@@ -105,7 +105,11 @@ __device__ __forceinline__ void peer_exchange_store(const PeerArgs& a, uint32_t 
             }
         }
         float s[4] = {acc.x, acc.y, acc.z, acc.w};
-        const int64_t col = i0 % n_cols;              // n_cols is a multiple of 4: the four values share a row
+        // n_cols is a multiple of 4: the four values share a row.  A bias has one value per column; with BI8_ADDEND_FULL in
+        // its type code the operand is a contiguous [M, n_cols] addend (a residual) indexed like the result.
+        const bool full = (bias_dtype & BI8_ADDEND_FULL) != 0;
+        bias_dtype &= ~BI8_ADDEND_FULL;
+        const int64_t col = full ? i0 : i0 % n_cols;
         float b[4] = {0.f, 0.f, 0.f, 0.f};
         const bool hb = bias != nullptr;
         if (hb) {

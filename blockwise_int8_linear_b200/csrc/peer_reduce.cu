@@ -13,8 +13,8 @@ namespace bi8 {
 namespace {
 
 __global__ void __launch_bounds__(kPeerThreads) peer_allreduce_kernel(const PeerArgs a, const float* __restrict__ partial,
-                                                                      int64_t count, int64_t n_cols, const void* __restrict__ bias,
-                                                                      int bias_dtype, void* __restrict__ out, int out_dtype,
+                                                                      int64_t count, int64_t n_cols, const void* bias,
+                                                                      int bias_dtype, void* out, int out_dtype,
                                                                       long long limit_cycles, int* status) {
     const uint32_t seq = peer_sequence(a);
     const int64_t i0 = (int64_t)blockIdx.x * kPeerChunk + (int64_t)threadIdx.x * 4;

@@ -11,10 +11,15 @@
 //   BI8_PRE_RMSNORM   y = cast(x * rsqrt(sum(x^2) / K + eps) [* weight])        one rounding, fp32 arithmetic
 //   BI8_PRE_SILU_MUL  y = cast(cast(x / (1 + exp(-x))) * x2)                    two roundings: silu(x), then the product
 //
-// Both start their programmatic dependents at once (the decode GEMM launched behind them sets up and streams its first
-// weights while they run; it waits for their completion before it reads the activations).
+// Both release their programmatic dependents at once (the decode GEMM launched behind them sets up and streams its first
+// weights while they run; it waits for their completion before it reads the activations).  For decode-sized batches they
+// are themselves launched as programmatic dependents of whatever precedes them in the stream, wait for it first thing,
+// and release their own dependents only then: behind one of this library's reduction kernels (the previous layer's)
+// they are resident before that kernel has finished.
 #include "bi8_common.cuh"
 #include "quant_math.cuh"
+
+#include <cstring>
 
 namespace bi8 {
 namespace {
@@ -60,6 +65,36 @@ __device__ __forceinline__ void load8(float* f, const void* base, int64_t row_of
     }
 }
 
+// the same eight elements of a 16-bit type as four packed words (what a thread keeps between the two passes of a row)
+__device__ __forceinline__ void load_raw8(uint32_t* w, const void* base, int64_t row_off, int k, int K, bool vec) {
+    const unsigned char* src = static_cast<const unsigned char*>(base) + (row_off + k) * 2;
+    if (vec && k + 8 <= K) {
+        const uint4 a = ld_nc_v4(src);
+        w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+        return;
+    }
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+        const uint32_t lo = k + 2 * h < K ? reinterpret_cast<const unsigned short*>(src)[2 * h] : 0u;
+        const uint32_t hi = k + 2 * h + 1 < K ? reinterpret_cast<const unsigned short*>(src)[2 * h + 1] : 0u;
+        w[h] = lo | (hi << 16);
+    }
+}
+
+__device__ __forceinline__ void unpack8(float* f, const uint32_t* w, int dt) {
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+        if (dt == BI8_BF16) {
+            f[2 * h] = bf16lo(w[h]);
+            f[2 * h + 1] = bf16hi(w[h]);
+        } else {
+            const float2 t2 = __half22float2(*reinterpret_cast<const __half2*>(&w[h]));
+            f[2 * h] = t2.x;
+            f[2 * h + 1] = t2.y;
+        }
+    }
+}
+
 // the value a kernel storing `v` in the activation type would have left in memory
 __device__ __forceinline__ float round_to(float v, int dt) {
     if (dt == BI8_BF16) return __bfloat162float(__float2bfloat16_rn(v));
@@ -95,36 +130,42 @@ __device__ __forceinline__ void quantize_unit(const float* y, bool valid, bool s
 }
 
 // One CTA per row.  Pass 1: the row's sum of squares (a thread's units in ascending order, lanes by butterfly, warps in
-// ascending order: the same bits on every launch).  Pass 2: normalise, round, quantize.  Rows of up to
-// kPreHold * 256 * 8 elements stay in registers between the passes; longer rows are read again.
-template <int QB>
-__global__ void __launch_bounds__(kPreThreads) rmsnorm_quantize_kernel(const void* __restrict__ x, int dt, int64_t ldx,
+// ascending order: the same bits on every launch with the same THREADS, which the launcher picks from M and K).  Pass 2: normalise, round, quantize.  Rows of up
+// to kPreHold * THREADS * 8 elements stay in registers between the passes; longer rows are read again.  THREADS = 128
+// for rows of up to 4096 elements: a row is in flight for a load latency plus a reduction, so what bounds a large
+// batch is the number of rows resident per SM (ten CTAs of 128 threads against four of 256).
+template <int QB, int THREADS>
+__global__ void __launch_bounds__(THREADS, THREADS == 128 ? 10 : 4) rmsnorm_quantize_kernel(const void* __restrict__ x, int dt, int64_t ldx,
                                                                        const void* __restrict__ weight, float eps,
                                                                        int8_t* __restrict__ q, float* __restrict__ sx, int M, int K,
                                                                        int nb, int vec_in, int vec_out) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");           // a no-op unless launched as a programmatic dependent
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr int LPB = QB / 8;
-    __shared__ float warp_sum[kPreThreads / 32];
+    __shared__ float warp_sum[THREADS / 32];
     const int m = blockIdx.x, tid = threadIdx.x;
     const int upr = nb * LPB;                                   // units per row, padded to whole blocks
-    const bool hold = upr <= kPreHold * kPreThreads;
+    // 16-bit rows that fit are kept as packed words (four registers per unit); fp32 rows and longer ones are read again
+    const bool hold = dt != BI8_F32 && upr <= kPreHold * THREADS;
     const int64_t row_off = (int64_t)m * ldx;
-    float f[kPreHold][8];
+    uint32_t raw[kPreHold][4];
     float ss = 0.0f;
     if (hold) {
 #pragma unroll
         for (int i = 0; i < kPreHold; ++i) {
-            const int k = (i * kPreThreads + tid) * 8;
-            if (k < K) load8(f[i], x, row_off, k, K, dt, vec_in != 0);
-            else {
+            const int k = (i * THREADS + tid) * 8;
+            if (k < K) load_raw8(raw[i], x, row_off, k, K, vec_in != 0);
+            else raw[i][0] = raw[i][1] = raw[i][2] = raw[i][3] = 0u;
+        }
 #pragma unroll
-                for (int e = 0; e < 8; ++e) f[i][e] = 0.0f;
-            }
+        for (int i = 0; i < kPreHold; ++i) {
+            float t[8];
+            unpack8(t, raw[i], dt);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) ss = __fmaf_rn(f[i][e], f[i][e], ss);
+            for (int e = 0; e < 8; ++e) ss = __fmaf_rn(t[e], t[e], ss);
         }
     } else {
-        for (int u = tid; u < upr; u += kPreThreads) {
+        for (int u = tid; u < upr; u += THREADS) {
             const int k = u * 8;
             if (k >= K) break;
             float t[8];
@@ -139,26 +180,11 @@ __global__ void __launch_bounds__(kPreThreads) rmsnorm_quantize_kernel(const voi
     __syncthreads();
     float total = 0.0f;
 #pragma unroll
-    for (int w = 0; w < kPreThreads / 32; ++w) total += warp_sum[w];
+    for (int w = 0; w < THREADS / 32; ++w) total += warp_sum[w];
     const float rstd = rsqrtf(__fadd_rn(__fdiv_rn(total, (float)K), eps));
     const bool short_mantissa = dt != BI8_F32;
-    for (int i = 0; i * kPreThreads < upr; ++i) {
-        const int u = i * kPreThreads + tid, k = u * 8;
-        const bool valid = u < upr && k < K;
-        float y[8];
-        if (hold && i < kPreHold) {
-#pragma unroll
-            for (int j = 0; j < kPreHold; ++j)
-                if (j == i) {
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) y[e] = f[j][e];
-                }
-        } else if (valid) {
-            load8(y, x, row_off, k, K, dt, vec_in != 0);
-        } else {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) y[e] = 0.0f;
-        }
+    // normalises, rounds and quantizes the unit whose elements are in y (all lanes of a warp call it together)
+    auto finish_unit = [&](float* y, int k, bool valid) {
         if (valid) {
             float w8[8];
             if (weight) load8(w8, weight, 0, k, K, dt, vec_in != 0);
@@ -170,6 +196,30 @@ __global__ void __launch_bounds__(kPreThreads) rmsnorm_quantize_kernel(const voi
             }
         }
         quantize_unit<QB>(y, valid, short_mantissa, q, sx, m, k, M, K, vec_out != 0);
+    };
+    if (hold) {
+#pragma unroll
+        for (int i = 0; i < kPreHold; ++i) {
+            if (i * THREADS < upr) {                            // the same for all threads of the CTA
+                const int u = i * THREADS + tid, k = u * 8;
+                float y[8];
+                unpack8(y, raw[i], dt);
+                finish_unit(y, k, u < upr && k < K);
+            }
+        }
+    } else {
+        for (int i = 0; i * THREADS < upr; ++i) {
+            const int u = i * THREADS + tid, k = u * 8;
+            const bool valid = u < upr && k < K;
+            float y[8];
+            if (valid) {
+                load8(y, x, row_off, k, K, dt, vec_in != 0);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) y[e] = 0.0f;
+            }
+            finish_unit(y, k, valid);
+        }
     }
 }
 
@@ -179,6 +229,7 @@ __global__ void __launch_bounds__(kPreThreads) silu_mul_quantize_kernel(const vo
                                                                         int dt, int64_t ldx, int8_t* __restrict__ q,
                                                                         float* __restrict__ sx, int M, int K, int nb, int vec_in,
                                                                         int vec_out) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");           // a no-op unless launched as a programmatic dependent
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr int LPB = QB / 8;
     const int upr = nb * LPB;
@@ -201,7 +252,33 @@ __global__ void __launch_bounds__(kPreThreads) silu_mul_quantize_kernel(const vo
     quantize_unit<QB>(y, valid, dt != BI8_F32, q, sx, m, k, M, K, vec_out != 0);
 }
 
+// C[m, n] = cast(C[m, n] + R[m, n]): the addition a layer's `x + proj(...)` performs in the activation type
+__global__ void __launch_bounds__(kPreThreads) residual_add_kernel(void* C, int64_t ldc, const void* R, int64_t ldr, int dt, int64_t M,
+                                                                   int64_t N) {
+    const int64_t i = (int64_t)blockIdx.x * kPreThreads + threadIdx.x;
+    if (i >= M * N) return;
+    const int64_t m = i / N, n = i % N, c = m * ldc + n, r = m * ldr + n;
+    if (dt == BI8_F32) {
+        static_cast<float*>(C)[c] = __fadd_rn(static_cast<float*>(C)[c], static_cast<const float*>(R)[r]);
+    } else if (dt == BI8_BF16) {
+        __nv_bfloat16* cp = static_cast<__nv_bfloat16*>(C);
+        cp[c] = __float2bfloat16_rn(__fadd_rn(__bfloat162float(cp[c]), __bfloat162float(static_cast<const __nv_bfloat16*>(R)[r])));
+    } else {
+        __half* cp = static_cast<__half*>(C);
+        cp[c] = __float2half_rn(__fadd_rn(__half2float(cp[c]), __half2float(static_cast<const __half*>(R)[r])));
+    }
+}
+
 }  // namespace
+
+int launch_residual_add(void* C, int64_t ldc, const void* R, int64_t ldr, int dt, int64_t M, int64_t N, cudaStream_t st) {
+    if (M <= 0 || N <= 0) return BI8_OK;
+    const int64_t blocks = (M * N + kPreThreads - 1) / kPreThreads;
+    if (blocks > 0x7fffffff) return fail(BI8_ERR_LIMIT, "residual add: more than 2^31 blocks");
+    residual_add_kernel<<<(unsigned)blocks, kPreThreads, 0, st>>>(C, ldc, R, ldr, dt, M, N);
+    BI8_CUDA_TRY(cudaGetLastError());
+    return BI8_OK;
+}
 
 int launch_quantize_pre(int op, const void* x, const void* x2, int dt, int64_t ldx, const void* weight, float eps, int8_t* q, float* sx,
                         int64_t M, int64_t K, int block, cudaStream_t st) {
@@ -212,10 +289,27 @@ int launch_quantize_pre(int op, const void* x, const void* x2, int dt, int64_t l
     const bool rows16 = (ldx * esz) % 16 == 0 && K % 8 == 0;
     const int vec_in = rows16 && aligned(x, 16) && (!x2 || aligned(x2, 16)) && (!weight || aligned(weight, 16));
     const int vec_out = K % 8 == 0 && aligned(q, 8);
+    if (op == BI8_PRE_NONE) return launch_quantize_rowwise(x, dt, ldx, q, sx, M, K, block, st);
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof(cfg));
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = M <= 64 ? 1 : 0;       // decode: resident while the predecessor finishes (the kernels wait for it themselves)
+    const int Mi = (int)M, Ki = (int)K;
     if (op == BI8_PRE_RMSNORM) {
-        const unsigned grid = (unsigned)M;
-#define BI8_PRE_RMS(QB)                                                                                                     \
-    rmsnorm_quantize_kernel<QB><<<grid, kPreThreads, 0, st>>>(x, dt, ldx, weight, eps, q, sx, (int)M, (int)K, nb, vec_in, vec_out)
+        // 128 threads per row where the row fits their registers and there are rows enough to fill the SMs ten deep; a
+        // handful of decode rows finish sooner with 256 threads each
+        const bool narrow = (int64_t)nb * (block / 8) <= kPreHold * 128 && M > 1024;
+        cfg.gridDim = dim3((unsigned)M);
+        cfg.blockDim = dim3(narrow ? 128 : 256);
+#define BI8_PRE_RMS(QB)                                                                                                              \
+    if (narrow)                                                                                                                      \
+        BI8_CUDA_TRY(cudaLaunchKernelEx(&cfg, rmsnorm_quantize_kernel<QB, 128>, x, dt, ldx, weight, eps, q, sx, Mi, Ki, nb, vec_in, vec_out)); \
+    else                                                                                                                             \
+        BI8_CUDA_TRY(cudaLaunchKernelEx(&cfg, rmsnorm_quantize_kernel<QB, 256>, x, dt, ldx, weight, eps, q, sx, Mi, Ki, nb, vec_in, vec_out))
         switch (block) {
             case 32: BI8_PRE_RMS(32); break;
             case 64: BI8_PRE_RMS(64); break;
@@ -226,9 +320,9 @@ int launch_quantize_pre(int op, const void* x, const void* x2, int dt, int64_t l
     } else if (op == BI8_PRE_SILU_MUL) {
         if (!x2) return fail(BI8_ERR_NULL, "quantize_pre: the gated activation needs its second operand");
         const int64_t units = M * nb * (block / 8);
-        const unsigned grid = (unsigned)((units + kPreThreads - 1) / kPreThreads);
-#define BI8_PRE_SILU(QB)                                                                                                    \
-    silu_mul_quantize_kernel<QB><<<grid, kPreThreads, 0, st>>>(x, x2, dt, ldx, q, sx, (int)M, (int)K, nb, vec_in, vec_out)
+        cfg.gridDim = dim3((unsigned)((units + kPreThreads - 1) / kPreThreads));
+        cfg.blockDim = dim3(kPreThreads);
+#define BI8_PRE_SILU(QB) BI8_CUDA_TRY(cudaLaunchKernelEx(&cfg, silu_mul_quantize_kernel<QB>, x, x2, dt, ldx, q, sx, Mi, Ki, nb, vec_in, vec_out))
         switch (block) {
             case 32: BI8_PRE_SILU(32); break;
             case 64: BI8_PRE_SILU(64); break;

@@ -3,6 +3,8 @@
     python -m blockwise_int8_linear_b200.microbench quantize 8192 8192
     python -m blockwise_int8_linear_b200.microbench dequantize 8192 8192
     python -m blockwise_int8_linear_b200.microbench colwise 8192 8192
+    python -m blockwise_int8_linear_b200.microbench rmsnorm 4096 4096             # normalise + quantize in one kernel
+    python -m blockwise_int8_linear_b200.microbench silu_mul 4096 11008           # silu(gate) * up + quantize in one kernel
     python -m blockwise_int8_linear_b200.microbench gemm 4096 4096 11008          # M K N, int8 operands given
     python -m blockwise_int8_linear_b200.microbench gemm 16 4096 4096 --block 64
 
@@ -23,7 +25,7 @@ if ROOT not in sys.path:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["quantize", "dequantize", "colwise", "dual", "gemm"])
+    ap.add_argument("op", choices=["quantize", "dequantize", "colwise", "dual", "rmsnorm", "silu_mul", "gemm"])
     ap.add_argument("dims", type=int, nargs="+")
     ap.add_argument("--block", type=int, default=64)
     ap.add_argument("--reps", type=int, default=7)
@@ -51,10 +53,13 @@ def main():
         m, k = a.dims
         x = torch.randn((m, k), device=dev, generator=g).to(torch.bfloat16)
         q, s = F.quantize_block_rowwise(x)
+        gu = torch.randn((m, 2 * k), device=dev, generator=g).to(torch.bfloat16) if a.op == "silu_mul" else None
         fn = {"quantize": lambda: F.quantize_block_rowwise(x), "dequantize": lambda: F.dequantize_block_rowwise(q, s),
-              "colwise": lambda: F.quantize_block_colwise(x), "dual": lambda: F.quantize_block_dual(x)}[a.op]
+              "colwise": lambda: F.quantize_block_colwise(x), "dual": lambda: F.quantize_block_dual(x),
+              "rmsnorm": lambda: F.rmsnorm_quantize_block_rowwise(x),
+              "silu_mul": lambda: F.silu_mul_quantize_block_rowwise(gu[:, :k], gu[:, k:])}[a.op]
         work = 0.0
-        nbytes = m * k * (2 + (2 if a.op == "dual" else 1) * (1 + 4.0 / a.block))
+        nbytes = m * k * ((4 if a.op == "silu_mul" else 2) + (2 if a.op == "dual" else 1) * (1 + 4.0 / a.block))
     flush = None if a.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     for _ in range(a.warmup):
         fn()

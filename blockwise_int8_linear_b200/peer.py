@@ -73,7 +73,24 @@ class PeerAllReduce:
             dist.barrier(group)         # every rank's buffer is zeroed before anybody's first kernel writes into it
         self._ptrs = (ctypes.c_void_p * 8)(*(ptrs + [ptrs[0]] * (8 - len(ptrs))))
 
-    def __call__(self, partial: torch.Tensor, bias: torch.Tensor = None, out: torch.Tensor = None, wait_limit_us: int = None):
+    @staticmethod
+    def _addend(bias, residual, m, n, out_dtype):
+        """The one operand the kernels add after the cast: a bias [N], or a residual [M, N] of the output type."""
+        if residual is not None:
+            if bias is not None:
+                raise ValueError("bias and residual cannot be combined in the peer-memory reduction")
+            if residual.numel() != m * n or residual.dtype != out_dtype or not residual.is_contiguous():
+                raise ValueError(f"residual must be a contiguous {out_dtype} tensor of {m} x {n} elements")
+            return residual, _lib.dtype_code(residual.dtype) | _lib.ADDEND_FULL
+        if bias is not None:
+            bias = bias.reshape(n).contiguous()
+            return bias, _lib.dtype_code(bias.dtype)
+        return None, 0
+
+    def __call__(self, partial: torch.Tensor, bias: torch.Tensor = None, out: torch.Tensor = None, wait_limit_us: int = None,
+                 residual: torch.Tensor = None):
+        """``cast(sum over ranks of partial) + bias`` or ``... + residual`` (a ``[M, N]`` tensor of the output type, e.g. the
+        layer's input stream; it may be ``out``)."""
         if partial.dtype != torch.float32 or not partial.is_contiguous():
             raise ValueError("partial must be a contiguous float32 tensor")
         n = partial.shape[-1]
@@ -81,29 +98,35 @@ class PeerAllReduce:
         out_dtype = block_linear_config.INPUT_OUTPUT_TORCH_TYPE
         if out is None:
             out = torch.empty(partial.shape, dtype=out_dtype, device=partial.device)
-        if bias is not None:
-            bias = bias.contiguous()
+        addend, code = self._addend(bias, residual, m, n, out.dtype)
         if wait_limit_us is None:
             wait_limit_us = self.wait_limit_us
         with torch.cuda.device(partial.device):
             rc = _lib.lib().bi8_peer_allreduce(self._ptrs, self.rank, self.world, self.capacity, _lib.ptr(partial), m, n,
-                                               _lib.ptr(bias), _lib.dtype_code(bias.dtype) if bias is not None else 0,
-                                               _lib.ptr(out), _lib.dtype_code(out.dtype), int(wait_limit_us), _lib.stream_ptr())
+                                               _lib.ptr(addend), code, _lib.ptr(out), _lib.dtype_code(out.dtype),
+                                               int(wait_limit_us), _lib.stream_ptr())
         _lib.check(rc, "bi8_peer_allreduce")
         return out
 
     def row_parallel_linear(self, x: torch.Tensor, w_int8: torch.Tensor, state_w: torch.Tensor, bias: torch.Tensor = None,
-                            wait_limit_us: int = None):
+                            wait_limit_us: int = None, *, op: str = "none", x2: torch.Tensor = None, norm_weight: torch.Tensor = None,
+                            eps: float = 1e-5, residual: torch.Tensor = None):
         """The whole row-parallel layer in one library call: ``x [..., K_r]`` is this rank's slice of the input features,
         ``w_int8 [N, K_r]`` / ``state_w [ceil(K_r/block), N]`` this rank's weight slice.  Returns
-        ``cast(sum over ranks of x_r @ W_r^T) + bias``.  For decode-sized batches (at most 64 rows) the kernel that finishes
-        the weight-streaming GEMM exchanges its sums with the other ranks itself; the result equals
+        ``cast(sum over ranks of pre(x_r) @ W_r^T) + bias`` (or ``+ residual``, a tensor of the output's shape and type).
+        ``op`` / ``x2`` / ``norm_weight`` / ``eps``: the producer step fused into the quantizer, as in
+        ``pre_quantize_matmul_block_rowwise_dequantize`` ('silu_mul' for a gated MLP's down projection; 'rmsnorm' would
+        normalise over this rank's slice only and is rejected).  For decode-sized batches (at most 64 rows) the kernel that
+        finishes the weight-streaming GEMM exchanges its sums with the other ranks itself; the result equals
         ``self(partial)`` on the fp32 output of ``quantize_matmul_block_rowwise_dequantize``."""
-        from .triton_functions import _block, _pitch, _rows_contiguous, ceil_div
+        from .triton_functions import _block, _pitch, _pre_operands, ceil_div
+        if op == "rmsnorm" and self.world > 1:
+            raise ValueError("a row-parallel layer holds a slice of the features: normalise before the slice is taken")
         block = _block()
         lead = x.shape[:-1]
-        x2 = _rows_contiguous(x.reshape(-1, x.shape[-1]))
-        m, k = x2.shape
+        code, x2d, x2_2d, norm_weight = _pre_operands(op, x.reshape(-1, x.shape[-1]),
+                                                      None if x2 is None else x2.reshape(-1, x2.shape[-1]), norm_weight)
+        m, k = x2d.shape
         n = w_int8.shape[0]
         if w_int8.dtype != torch.int8 or w_int8.shape[1] != k or w_int8.stride(1) != 1:
             raise ValueError("w_int8 must be int8 [N, K] with contiguous rows")
@@ -112,23 +135,23 @@ class PeerAllReduce:
             raise ValueError(f"state_w must be float32 [{nb}, {n}] for block {block}")
         state_w = state_w.contiguous()
         out_dtype = block_linear_config.INPUT_OUTPUT_TORCH_TYPE
-        dev = x2.device
+        dev = x2d.device
         out = torch.empty((m, n), dtype=out_dtype, device=dev)
         partial = torch.empty((m, n), dtype=torch.float32, device=dev)
         xq = torch.empty((m, k), dtype=torch.int8, device=dev)
         sx = torch.empty((nb, m), dtype=torch.float32, device=dev)
-        if bias is not None:
-            bias = bias.reshape(n).contiguous()
+        addend, addend_code = self._addend(bias, None if residual is None else residual.reshape(m, n), m, n, out_dtype)
         if wait_limit_us is None:
             wait_limit_us = self.wait_limit_us
         L = _lib.lib()
         with torch.cuda.device(dev):
             ws_bytes = L.bi8_gemm_workspace_bytes(m, n, k, block)
             ws = _lib.workspace(dev, ws_bytes)
-            rc = L.bi8_row_parallel_linear(_lib.ptr(x2), _lib.dtype_code(x2.dtype), _pitch(x2), _lib.ptr(xq), _lib.ptr(sx),
-                                           _lib.ptr(w_int8), _pitch(w_int8), _lib.ptr(state_w), _lib.ptr(partial), m, n, k, block,
-                                           _lib.ptr(ws), ws_bytes, self._ptrs, self.rank, self.world, self.capacity,
-                                           _lib.ptr(bias), _lib.dtype_code(bias.dtype) if bias is not None else 0,
-                                           _lib.ptr(out), _lib.dtype_code(out_dtype), int(wait_limit_us), 0, _lib.stream_ptr())
-        _lib.check(rc, "bi8_row_parallel_linear")
+            rc = L.bi8_row_parallel_linear_pre(code, _lib.ptr(x2d), _lib.ptr(x2_2d), _lib.dtype_code(x2d.dtype), _pitch(x2d),
+                                               _lib.ptr(norm_weight), float(eps), _lib.ptr(xq), _lib.ptr(sx), _lib.ptr(w_int8),
+                                               _pitch(w_int8), _lib.ptr(state_w), _lib.ptr(partial), m, n, k, block, _lib.ptr(ws),
+                                               ws_bytes, self._ptrs, self.rank, self.world, self.capacity, _lib.ptr(addend),
+                                               addend_code, _lib.ptr(out), _lib.dtype_code(out_dtype), int(wait_limit_us), 0,
+                                               _lib.stream_ptr())
+        _lib.check(rc, "bi8_row_parallel_linear_pre")
         return out.view(*lead, n)

@@ -21,7 +21,7 @@ from . import block_linear_config
 __all__ = [
     "ceil_div", "quantize_block_rowwise", "quantize_block_colwise", "quantize_block_dual", "dequantize_block_rowwise",
     "int8_matmul_block64_rowwise_dequantize", "quantize_matmul_block_rowwise_dequantize", "int8_matmul_block_partials",
-    "fast_matmulT",
+    "fast_matmulT", "rmsnorm_quantize_block_rowwise", "silu_mul_quantize_block_rowwise", "pre_quantize_matmul_block_rowwise_dequantize",
 ]
 
 
@@ -308,6 +308,121 @@ def quantize_matmul_block_rowwise_dequantize(x, b, state_w, bias=None, *, flags:
                                             _lib.stream_ptr())
     _lib.check(rc, "bi8_gemm_dequant_fused_quant")
     return c
+
+
+def _pre_operands(op: str, x, x2, norm_weight):
+    """Checks the operands of a fused producer step: returns (code, x, x2, weight) with shared row pitch and dtype."""
+    if op not in ("none", "rmsnorm", "silu_mul"):
+        raise ValueError(f"unknown producer step {op!r}: expected 'none', 'rmsnorm' or 'silu_mul'")
+    assert x.is_cuda
+    if x.dim() != 2:
+        raise ValueError(f"expected a 2-D tensor, got {tuple(x.shape)}")
+    x = _rows_contiguous(x)
+    if op == "silu_mul":
+        if x2 is None or tuple(x2.shape) != tuple(x.shape) or x2.dtype != x.dtype or x2.device != x.device:
+            raise ValueError("silu_mul needs a second operand with x's shape, dtype and device")
+        x2 = _rows_contiguous(x2)
+        if _pitch(x2) != _pitch(x):         # e.g. one of the two was copied: give both the same row pitch
+            x, x2 = x.contiguous(), x2.contiguous()
+    else:
+        x2 = None
+    if op == "rmsnorm" and norm_weight is not None:
+        if norm_weight.numel() != x.shape[1]:
+            raise ValueError(f"norm weight must have {x.shape[1]} elements, got {norm_weight.numel()}")
+        norm_weight = norm_weight.reshape(-1).to(x.dtype).contiguous()
+    else:
+        norm_weight = None
+    return {"none": _lib.PRE_NONE, "rmsnorm": _lib.PRE_RMSNORM, "silu_mul": _lib.PRE_SILU_MUL}[op], x, x2, norm_weight
+
+
+def _quantize_pre(op, x, x2, norm_weight, eps, fblock_size):
+    block = _block(fblock_size)
+    code, x, x2, norm_weight = _pre_operands(op, x, x2, norm_weight)
+    m, k = x.shape
+    q = torch.empty((m, k), device=x.device, dtype=torch.int8)
+    state = torch.empty((ceil_div(k, block), m), device=x.device, dtype=_scale_dtype())
+    with _on_device(x):
+        rc = _lib.lib().bi8_quantize_rowwise_pre(code, _lib.ptr(x), _lib.ptr(x2), _lib.dtype_code(x.dtype), _pitch(x),
+                                                 _lib.ptr(norm_weight), float(eps), _lib.ptr(q), _lib.ptr(state), m, k, block,
+                                                 _lib.stream_ptr())
+    _lib.check(rc, "bi8_quantize_rowwise_pre")
+    return q, state
+
+
+def rmsnorm_quantize_block_rowwise(x: torch.Tensor, eps: float = 1e-5, weight: torch.Tensor = None, fblock_size=None):
+    """``quantize_block_rowwise(y)`` for ``y = (x * rsqrt(mean(x^2, -1) + eps) [* weight]).to(x.dtype)`` without writing
+    ``y``: the normalisation in front of a layer's q/k/v and gate/up projections fused into their quantizer (the
+    reference quantizes a tensor another kernel stored just before, ``block_linear.py:141``).  fp32 arithmetic, one
+    rounding to ``x.dtype``, then the quantizer's own arithmetic; the row's sum of squares is taken in a fixed order."""
+    return _quantize_pre("rmsnorm", x, None, weight, eps, fblock_size)
+
+
+def silu_mul_quantize_block_rowwise(gate: torch.Tensor, up: torch.Tensor, fblock_size=None):
+    """``quantize_block_rowwise(F.silu(gate) * up)`` without writing the product (the gated activation in front of a
+    layer's down projection): ``silu`` in fp32 rounded to the activation type, the product rounded again, as the two
+    separate kernels would, then quantized; bit-identical to the three-step form."""
+    return _quantize_pre("silu_mul", gate, up, None, 0.0, fblock_size)
+
+
+def pre_quantize_matmul_block_rowwise_dequantize(op: str, x, b, state_w, bias=None, *, x2=None, norm_weight=None, eps: float = 1e-5,
+                                                 residual=None, out=None, flags: int = 0):
+    """``quantize_matmul_block_rowwise_dequantize`` with the producer step ``op`` ('none', 'rmsnorm', 'silu_mul') fused
+    in front of the quantizer and an optional ``residual [M, N]`` (of the output type) added to the result in the output
+    type, the way a transformer layer's ``x + proj(act(...))`` does.  ``out`` may be given (it may be ``residual``
+    itself: updated in place, directly on the decode path, through a temporary elsewhere).  For ``M <= 64`` this is
+    quantizer + weight-streaming GEMM (+ its reduction), with the residual added by the kernel that writes the result."""
+    block = _block()
+    code, x, x2, norm_weight = _pre_operands(op, x, x2, norm_weight)
+    if b.stride(0) > 1 and b.stride(1) > 1:
+        b = b.contiguous()
+    assert x.shape[1] == b.shape[0], "incompatible dimensions"
+    if b.dtype != torch.int8:
+        raise ValueError(f"weights must be int8, got {b.dtype}")
+    bt = b.t()
+    if bt.shape[1] != 1 and bt.stride(1) != 1:
+        bt = bt.contiguous()
+    m, k = x.shape
+    n = bt.shape[0]
+    nb = ceil_div(k, block)
+    if tuple(state_w.shape) != (nb, n) or state_w.dtype != torch.float32:
+        raise ValueError(f"state_w must be float32 [{nb}, {n}] for block {block}, got {state_w.dtype} {tuple(state_w.shape)}")
+    state_w = state_w.contiguous()
+    out_dtype = block_linear_config.INPUT_OUTPUT_TORCH_TYPE
+    if out is None:
+        out = torch.empty((m, n), device=x.device, dtype=out_dtype)
+    elif tuple(out.shape) != (m, n) or out.dtype != out_dtype or out.stride(1) != 1 or out.device != x.device:
+        raise ValueError(f"out must be {out_dtype} [{m}, {n}] with contiguous rows on {x.device}")
+    if residual is not None:
+        if tuple(residual.shape) != (m, n) or residual.dtype != out_dtype or residual.stride(1) != 1 or residual.device != x.device:
+            raise ValueError(f"residual must be {out_dtype} [{m}, {n}] with contiguous rows on {x.device}")
+    bias_code = 0
+    if bias is not None:
+        if bias.numel() != n:
+            raise ValueError(f"bias must have {n} elements, got {bias.numel()}")
+        bias = bias.reshape(n).contiguous()
+        if bias.dtype not in (torch.bfloat16, torch.float16, torch.float32):
+            bias = bias.float()
+        bias_code = _lib.dtype_code(bias.dtype)
+    final = None
+    if residual is not None and out.data_ptr() == residual.data_ptr() and not (
+            m <= 64 and bias is None and n % 4 == 0 and k % 16 == 0 and _pitch(out) == _pitch(residual)):
+        final, out = out, torch.empty((m, n), device=x.device, dtype=out_dtype)    # not the path that may update in place
+    xq = torch.empty((m, k), device=x.device, dtype=torch.int8)
+    sx = torch.empty((nb, m), device=x.device, dtype=torch.float32)
+    L = _lib.lib()
+    with _on_device(x):
+        ws_bytes = L.bi8_gemm_workspace_bytes(m, n, k, block)
+        ws = _lib.workspace(x.device, ws_bytes)
+        rc = L.bi8_gemm_dequant_fused_pre(code, _lib.ptr(x), _lib.ptr(x2), _lib.dtype_code(x.dtype), _pitch(x), _lib.ptr(norm_weight),
+                                          float(eps), _lib.ptr(xq), _lib.ptr(sx), _lib.ptr(bt), _pitch(bt), _lib.ptr(state_w),
+                                          _lib.ptr(bias), bias_code, _lib.ptr(residual), _pitch(residual) if residual is not None else 0,
+                                          _lib.ptr(out), _pitch(out), _lib.dtype_code(out_dtype), m, n, k, block, _lib.ptr(ws), ws_bytes,
+                                          flags, _lib.stream_ptr())
+    _lib.check(rc, "bi8_gemm_dequant_fused_pre")
+    if final is not None:
+        final.copy_(out)
+        return final
+    return out
 
 
 def int8_matmul_block_partials(a, b, fblock_size=None, *, flags: int = 0):

@@ -106,17 +106,43 @@ class Int8Linear(nn.Module):
         dist.all_reduce(part)
         return part.to(cfg.INPUT_OUTPUT_TORCH_TYPE)
 
-    def summed(self, x):
-        """A row-parallel layer's output summed over the group, cast to the activation type: for decode-sized inputs with
-        the peer-memory reduction installed, one library call whose last kernel adds the GEMM's tile parts and the ranks."""
-        if self.world > 1 and self.mode == "row" and PEER is not None and self.lin is not None:
+    def fusable(self):
+        """Whether `fused` runs as one library call: a layer whose output needs no sum over ranks."""
+        return FUSE and self.lin is not None and (self.mode == "col" or self.world == 1)
+
+    def fused(self, x, op="none", x2=None, residual=None):
+        """``residual + self(pre(x))`` with pre = rms_norm ('rmsnorm'), silu(x) * x2 ('silu_mul') or nothing ('none'):
+        the producer step inside the layer's quantizer and the residual sum inside the kernel that writes its output
+        where the layer's output is complete on this rank, the separate torch kernels otherwise."""
+        if self.fusable():
+            return self.lin.infer_pre(x, op, x2=x2, eps=NORM_EPS, residual=residual)
+        inp = rms_norm(x) if op == "rmsnorm" else (F.silu(x) * x2 if op == "silu_mul" else x)
+        y = self.forward(inp)
+        return y if residual is None else residual + y
+
+    def summed(self, x, op="none", x2=None, residual=None):
+        """``residual + sum over the group of this row-parallel layer applied to pre(x)``, cast to the activation type: for
+        decode-sized inputs with the peer-memory reduction installed, one library call whose first kernel applies `op` and
+        quantizes and whose last kernel adds the GEMM's tile parts, the ranks and the residual."""
+        peer = self.world > 1 and self.mode == "row" and PEER is not None and self.lin is not None
+        if peer:
             rows = x.numel() // x.shape[-1]
-            if rows <= 64 and rows * self.widths[0] <= PEER.capacity:
-                return PEER.row_parallel_linear(x, self.lin.W_int8, self.lin.state_W)
-        return group_sum(self.partial(x), cfg.INPUT_OUTPUT_TORCH_TYPE, self.world)
+            peer = rows <= 64 and rows * self.widths[0] <= PEER.capacity
+        if peer and FUSE:
+            return PEER.row_parallel_linear(x, self.lin.W_int8, self.lin.state_W, op=op, x2=x2, residual=residual)
+        inp = rms_norm(x) if op == "rmsnorm" else (F.silu(x) * x2 if op == "silu_mul" else x)
+        if peer:
+            y = PEER.row_parallel_linear(inp, self.lin.W_int8, self.lin.state_W)
+        else:
+            y = group_sum(self.partial(inp), cfg.INPUT_OUTPUT_TORCH_TYPE, self.world)
+        return y if residual is None else residual + y
 
 
-def rms_norm(x, eps=1e-5):
+NORM_EPS = 1e-5
+FUSE = True      # producer steps and residual sums inside the library's calls (Int8Linear.fused); --no-fuse runs them as torch kernels
+
+
+def rms_norm(x, eps=NORM_EPS):
     return F.rms_norm(x, (x.shape[-1],), eps=eps)
 
 
@@ -146,14 +172,15 @@ class Layer(nn.Module):
         self.head_dim = a.head_dim
         self.kcache = self.vcache = None
 
-    def attn_partial(self, x, pos0, max_len, cis, mask=None, pos_dev=None, summed=False):
-        """Attention half of the layer up to the output projection, without the sum over ranks and the residual add.
+    def attn_partial(self, x, pos0, max_len, cis, mask=None, pos_dev=None, summed=False, residual=None):
+        """Attention half of the layer up to the output projection; without `residual` also without the sum over ranks
+        (unless `summed`) and the residual add, with it the half's complete output ``residual + o(att)``.
         Prefill: pos0 is a Python int and the cache is sliced.  Decode (pos_dev given, T == 1): the position is a device
         tensor, the cache is written with index_copy_ and attended in full under a mask, so that every shape is static and
         the step can be captured in a CUDA graph.  `cis` holds the rotary factors of this call's positions."""
         B, T, _ = x.shape
         hl, hd = self.heads_local, self.head_dim
-        qkv = self.qkv(rms_norm(x)).view(B, T, 3, hl, hd)
+        qkv = self.qkv.fused(x, "rmsnorm").view(B, T, 3, hl, hd)
         qk = rope(qkv[:, :, :2], cis)                                   # q and k in one pass: [B, T, 2, H, D]
         q, k, v = qk[:, :, 0].transpose(1, 2), qk[:, :, 1].transpose(1, 2), qkv[:, :, 2].transpose(1, 2)
         if self.kcache is None:
@@ -169,16 +196,24 @@ class Layer(nn.Module):
             self.vcache.index_copy_(2, pos_dev, v)
             att = F.scaled_dot_product_attention(q, self.kcache, self.vcache, attn_mask=mask)
         att = att.transpose(1, 2).reshape(B, T, hl * hd)
+        if residual is not None and self.o.fusable():
+            return self.o.fused(att, "none", residual=residual)
+        if residual is not None:
+            return self.o.summed(att, residual=residual)
         return self.o.summed(att) if summed else self.o.partial(att)
 
-    def mlp_partial(self, x, summed=False):
-        gate, up = self.gate_up(rms_norm(x)).split(self.gate_up.widths, dim=-1)
+    def mlp_partial(self, x, summed=False, residual=None):
+        gate, up = self.gate_up.fused(x, "rmsnorm").split(self.gate_up.widths, dim=-1)
+        if residual is not None and self.down.fusable():
+            return self.down.fused(gate, "silu_mul", x2=up, residual=residual)
+        if residual is not None:
+            return self.down.summed(gate, "silu_mul", x2=up, residual=residual)
         h = F.silu(gate) * up
         return self.down.summed(h) if summed else self.down.partial(h)
 
     def forward(self, x, pos0, max_len, cis, mask=None, pos_dev=None):
-        x = x + self.attn_partial(x, pos0, max_len, cis, mask, pos_dev, summed=True)
-        return x + self.mlp_partial(x, summed=True)
+        x = self.attn_partial(x, pos0, max_len, cis, mask, pos_dev, residual=x)
+        return self.mlp_partial(x, residual=x)
 
 
 PEER = None      # a blockwise_int8_linear_b200.peer.PeerAllReduce while the decode step uses the library's own reduction
@@ -215,7 +250,7 @@ class Llama(nn.Module):
 
     def local_logits(self, x):
         """[B, 1, V_local] of this rank, padded with -inf to the widest shard (all_gather wants equal sizes)."""
-        logits = self.head(rms_norm(x[:, -1:]))
+        logits = self.head.fused(x[:, -1:], "rmsnorm")
         if self.world == 1:
             return logits
         sizes = [hi - lo for lo, hi in block_aligned_bounds(self.vocab, self.world, self.block)]
@@ -304,6 +339,8 @@ def run(a, rank, world, dev, eager=False):
     the greedy decode, and returns the measurements and the generated tokens.  The process group, if any, is the
     caller's."""
     assert a.heads % world == 0, "heads must divide over the ranks"
+    global FUSE
+    FUSE = not getattr(a, "no_fuse", False)
     cfg.GROUP_SIZE, cfg.INPUT_OUTPUT_TORCH_TYPE = a.block, torch.bfloat16
     model = Llama(a, dev, rank, world)
     ids = torch.randint(0, a.vocab, (a.batch, a.prompt), generator=torch.Generator().manual_seed(4000)).to(dev)
@@ -409,6 +446,7 @@ def run(a, rank, world, dev, eager=False):
         "decode_mode": "eager" if eager else ("cuda graph" if world == 1 else
                                               "one cuda graph, peer-memory reductions" if graph is not None else
                                               "cuda graphs between the NCCL collectives"),
+        "fused_producers": FUSE,
         "first_tokens": toks[0, :8].tolist(), "tokens": toks.tolist(),
     }
 
@@ -427,6 +465,8 @@ def main():
     ap.add_argument("--eager", action="store_true", help="do not capture the decode step in a CUDA graph")
     ap.add_argument("--reduce", choices=["peer", "nccl"], default="peer",
                     help="tensor-parallel decode: the library's peer-memory reduction inside one CUDA graph, or NCCL between graphs")
+    ap.add_argument("--no-fuse", dest="no_fuse", action="store_true",
+                    help="run the normalisations, the gated activation and the residual sums as separate torch kernels")
     ap.add_argument("--out", default=None, help="also append the JSON line to this file")
     a = ap.parse_args()
     a.head_dim = a.hidden // a.heads

@@ -151,6 +151,35 @@ BI8_API int bi8_gemm_dequant_fused_quant(const void* x, int x_dtype, int64_t ldx
                                  const int8_t* Wq, int64_t ldw, const float* sW, const void* bias, int bias_dtype,
                                  void* C, int64_t ldc, int out_dtype, int64_t M, int64_t N, int64_t K, int block,
                                  void* workspace, size_t workspace_bytes, int flags, void* stream);
+
+/* The elementwise step that produces a projection's input, fused in front of the row-wise quantizer (no counterpart in the
+ * reference, whose layers quantize a tensor another kernel wrote just before: block_linear.py:141).  The value of every
+ * element is rounded to x_dtype exactly where the separate kernel would have stored it, then quantized with
+ * bi8_quantize_rowwise's arithmetic, so q / scales equal bi8_quantize_rowwise of that rounded tensor.
+ *   BI8_PRE_NONE      y = x                                                      (the plain quantizer)
+ *   BI8_PRE_RMSNORM   y = cast(x * rsqrt(sum_k(x^2) / K + eps) [* weight[k]])    fp32 arithmetic, one rounding; weight may
+ *                     be NULL, else [K] of x_dtype.  The sum of squares is taken in a fixed order (same bits on every call).
+ *   BI8_PRE_SILU_MUL  y = cast(cast(x / (1 + exp(-x))) * x2)                     x2 [M,K] of x_dtype with x's row stride;
+ *                     the two roundings of `F.silu(x) * x2` run as two kernels. */
+#define BI8_PRE_NONE 0
+#define BI8_PRE_RMSNORM 1
+#define BI8_PRE_SILU_MUL 2
+BI8_API int bi8_quantize_rowwise_pre(int op, const void* x, const void* x2, int x_dtype, int64_t ldx, const void* weight,
+                             float eps, int8_t* q, float* scales, int64_t M, int64_t K, int block, void* stream);
+/* bi8_gemm_dequant_fused_quant with that step in front of its quantizer and an optional residual behind its result:
+ *   C = cast(acc) (+ cast(bias)) (+ residual), every addition in the output type (a layer's `x + proj(...)`).
+ * residual [M,N] of out_dtype, row stride ldr, NULL for none.  For M <= 64 (N a multiple of 4, K of 16, workspace given) the
+ * quantizer kernel of `op` takes the decode quantizer's place in front of the weight-streaming GEMM (same overlap), and
+ * without bias the residual is added by the kernel that writes C; on that path, and only there, C may be the residual
+ * itself (a residual stream updated in place; any other overlap of the two is BI8_ERR_SHAPE, the same tensor on another
+ * path BI8_ERR_ALIGN).  Other shapes run quantizer, GEMM and one elementwise kernel back to back.  xq / sx are required
+ * scratch. */
+BI8_API int bi8_gemm_dequant_fused_pre(int op, const void* x, const void* x2, int x_dtype, int64_t ldx, const void* norm_weight,
+                               float eps, int8_t* xq, float* sx, const int8_t* Wq, int64_t ldw, const float* sW,
+                               const void* bias, int bias_dtype, const void* residual, int64_t ldr, void* C, int64_t ldc,
+                               int out_dtype, int64_t M, int64_t N, int64_t K, int block, void* workspace,
+                               size_t workspace_bytes, int flags, void* stream);
+
 /* Capture sequence number of `stream` if it is being captured into a CUDA graph, 0 otherwise (no counterpart in the
  * reference).  A host layer that caches workspaces uses it to give every captured graph a scratch buffer of its own:
  * an address baked into a graph must not be shared with another graph that may be replayed on a different stream. */
@@ -180,7 +209,11 @@ BI8_API int bi8_gemm_wait_selftest(const int8_t* A, int64_t lda, const int8_t* B
  *                 bit-identical on all ranks.
  *   wait_limit_us how long a CTA waits for the other ranks' flags (0 = one second); when it runs out the kernel records
  *                 BI8_ERR_TIMEOUT (bi8_device_status) and returns without writing its part of `out`.
+ *   bias          [N] of bias_dtype, or NULL.  With BI8_ADDEND_FULL or-ed into bias_dtype the operand is instead a
+ *                 contiguous [M,N] tensor added element by element in the output type: the residual of a transformer
+ *                 layer's `x + proj(...)` (it may be `out` itself).  These two entry points alone accept the flag.
  * Every rank must call it the same number of times with the same M and N.  world <= 8. */
+#define BI8_ADDEND_FULL 0x100
 BI8_API size_t bi8_peer_allreduce_buffer_bytes(int world, int64_t capacity);
 BI8_API int bi8_peer_allreduce(void* const* peer_bufs, int rank, int world, int64_t capacity, const float* partial,
                        int64_t M, int64_t N, const void* bias, int bias_dtype, void* out, int out_dtype,
@@ -199,6 +232,13 @@ BI8_API int bi8_row_parallel_linear(const void* x, int x_dtype, int64_t ldx, int
                             void* workspace, size_t workspace_bytes, void* const* peer_bufs, int rank, int world,
                             int64_t capacity, const void* bias, int bias_dtype, void* out, int out_dtype,
                             unsigned wait_limit_us, int flags, void* stream);
+/* The same with the producer step `op` (x2, norm_weight, eps as in bi8_quantize_rowwise_pre) in front of the quantizer. */
+BI8_API int bi8_row_parallel_linear_pre(int op, const void* x, const void* x2, int x_dtype, int64_t ldx, const void* norm_weight,
+                                float eps, int8_t* xq, float* sx, const int8_t* Wq, int64_t ldw, const float* sW,
+                                float* partial, int64_t M, int64_t N, int64_t K, int block, void* workspace,
+                                size_t workspace_bytes, void* const* peer_bufs, int rank, int world, int64_t capacity,
+                                const void* bias, int bias_dtype, void* out, int out_dtype, unsigned wait_limit_us, int flags,
+                                void* stream);
 
 /* Back-to-back tcgen05.mma kind::i8 issue rate of the current device: runs `iters` 128x256x32 MMAs per SM
  * with no loads or epilogue and returns the elapsed milliseconds in *ms (synchronises).  Used by the

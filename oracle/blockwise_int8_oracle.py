@@ -68,6 +68,37 @@ def quantize(x: torch.Tensor, block: int):
     return q, s.t().contiguous()
 
 
+def rmsnorm(x: torch.Tensor, eps: float = 1e-5, weight: torch.Tensor = None) -> torch.Tensor:
+    """The stored output of the normalisation that feeds a layer's q/k/v and gate/up projections:
+    ``cast(x * rsqrt(mean(x^2) + eps) [* weight])``, fp32 arithmetic, one rounding to ``x.dtype``.  The reference has no
+    such step of its own (its layers quantize whatever tensor they are given, ``block_linear.py:141``); this restates the
+    model code around the layer.  The order of the sum of squares is torch's on CPU, so against a GPU kernel the last
+    bit of ``rsqrt`` may differ: compare dequantized values, not bits."""
+    xf = x.to(torch.float32)
+    rstd = torch.rsqrt(xf.pow(2).sum(-1, keepdim=True) / x.shape[-1] + eps)
+    y = xf * rstd
+    if weight is not None:
+        y = y * weight.to(torch.float32)
+    return y.to(x.dtype)
+
+
+def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """``F.silu(gate) * up`` as two stored elementwise steps: ``cast(gate / (1 + exp(-gate)))``, then ``cast(. * up)``."""
+    gf = gate.to(torch.float32)
+    s = (gf / (1.0 + torch.exp(-gf))).to(gate.dtype)
+    return (s.to(torch.float32) * up.to(torch.float32)).to(gate.dtype)
+
+
+def rmsnorm_quantize(x: torch.Tensor, block: int, eps: float = 1e-5, weight: torch.Tensor = None):
+    """``quantize(rmsnorm(x))``: what the fused normalise-and-quantize step must return."""
+    return quantize(rmsnorm(x, eps, weight), block)
+
+
+def silu_mul_quantize(gate: torch.Tensor, up: torch.Tensor, block: int):
+    """``quantize(silu_mul(gate, up))``: what the fused activation-and-quantize step must return."""
+    return quantize(silu_mul(gate, up), block)
+
+
 def dequantize(q: torch.Tensor, scales: torch.Tensor, block: int,
                out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
     """``dequantize_block_rowwise`` (``triton_functions.py:492-500``, kernel line 487)."""

@@ -66,12 +66,25 @@ def test_llama_driver_logits_against_oracle_linears():
             y = O.gemm(xq, lin.W_int8.cpu().t(), xs, lin.state_W.cpu(), None, a.block, cfg.INPUT_OUTPUT_TORCH_TYPE)
             return y.to(x.device).view(*x.size()[:-1], -1)
 
+        def oracle_infer_pre(x, op="none", x2=None, norm_weight=None, eps=1e-5, residual=None, infer=oracle_infer):
+            # the fused producer steps and the residual sum, restated on the CPU around the oracle's layer
+            if op == "rmsnorm":
+                inp = O.rmsnorm(x.cpu(), eps, None if norm_weight is None else norm_weight.cpu()).to(x.device)
+            elif op == "silu_mul":
+                inp = O.silu_mul(x.cpu(), x2.cpu()).to(x.device)
+            else:
+                inp = x
+            y = infer(inp)
+            return y if residual is None else residual + y
+
         lin.infer = oracle_infer
+        lin.infer_pre = oracle_infer_pre
     for layer in model.layers:
         layer.kcache = layer.vcache = None
     ref = model(ids, 0, max_len)
     for lin, fn in saved:
         lin.infer = fn
+        del lin.infer_pre                      # the instance attribute set above; the class's method shows again
     _close(logits.cpu(), ref.cpu(), identical=0.90, rel=2.0 ** -6)
     assert_clean_device()
 

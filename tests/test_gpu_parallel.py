@@ -109,6 +109,20 @@ def _peer_worker(rank, world, port, results):
             want = peer(part, bias[:n] if n <= 4096 else None)
             got = peer.row_parallel_linear(x, wq, sw, bias[:n] if n <= 4096 else None)
             assert torch.equal(got, want), (m, k, n, (got.float() - want.float()).abs().max().item())
+        # the gated activation in front of the quantizer and the residual behind the sum, in the same call
+        import torch.nn.functional as F
+        for m, k, n in ((8, 2048, 4096), (70, 1024, 4096)):
+            w = (torch.randn((n, k), device=dev, generator=g) * 0.02).to(torch.bfloat16)
+            wq, sw = quantize_block_rowwise(w)
+            gu = torch.randn((m, 2 * k), device=dev, generator=g).to(torch.bfloat16)
+            res = torch.randn((m, n), device=dev, generator=torch.Generator(device=dev).manual_seed(6)).to(torch.bfloat16)
+            cfg.INPUT_OUTPUT_TORCH_TYPE = torch.float32
+            part = quantize_matmul_block_rowwise_dequantize(F.silu(gu[:, :k]) * gu[:, k:], wq.t(), sw)
+            cfg.INPUT_OUTPUT_TORCH_TYPE = torch.bfloat16
+            want = peer(part) + res
+            assert torch.equal(peer(part, residual=res), want)
+            got = peer.row_parallel_linear(gu[:, :k], wq, sw, op="silu_mul", x2=gu[:, k:], residual=res)
+            assert torch.equal(got, want), (m, k, n, (got.float() - want.float()).abs().max().item())
         # replayed from a graph: the sequence number continues on the device
         part = torch.randn((8, 4096), device=dev, generator=g)
         out = torch.empty((8, 4096), device=dev, dtype=torch.bfloat16)
@@ -182,6 +196,10 @@ def test_peer_allreduce_one_rank_and_bounded_wait():
         wq, sw = quantize_block_rowwise(w)
         x = torch.randn((m, 1024), device=DEV).to(torch.bfloat16)
         assert torch.equal(big.row_parallel_linear(x, wq, sw, bias), quantize_matmul_block_rowwise_dequantize(x, wq.t(), sw, bias))
+        gu = torch.randn((m, 2048), device=DEV).to(torch.bfloat16)
+        res = torch.randn((m, 4096), device=DEV).to(torch.bfloat16)
+        want = res + quantize_matmul_block_rowwise_dequantize(torch.nn.functional.silu(gu[:, :1024]) * gu[:, 1024:], wq.t(), sw)
+        assert torch.equal(big.row_parallel_linear(gu[:, :1024], wq, sw, op="silu_mul", x2=gu[:, 1024:], residual=res), want)
     assert _lib.device_status() == 0
     lonely = PeerAllReduce(8 * 4096, DEV, _local_world=2)
     out = torch.full((8, 4096), 7.0, device=DEV, dtype=torch.bfloat16)

@@ -94,3 +94,27 @@ def test_near_tie_inputs_use_ieee_division():
     qc, scc = C.quantize(x, block)
     assert torch.equal(q, qc) and torch.equal(sc, scc)
     assert q[0, 0].item() == 127 and q[0, block].item() == -127
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16, torch.float32])
+def test_producer_step_restatements_equal_torch_cpu(dt):
+    """The oracle's normalisation and gated activation (the steps the fused quantizers absorb) against torch's own CPU
+    implementations of the same model code, bit for bit."""
+    g = torch.Generator().manual_seed(31)
+    x = (torch.randn((16, 704), generator=g) * 1.5).to(dt)
+    u = torch.randn((16, 704), generator=g).to(dt)
+    w = (1.0 + 0.1 * torch.randn(704, generator=g)).to(dt)
+    if dt == torch.float32:
+        # torch's fused CPU kernels use a vectorised exp and sum the squares in another order: the last bits of an fp32
+        # result may differ; the 16-bit results absorb that in their rounding
+        assert torch.allclose(O.silu_mul(x, u), torch.nn.functional.silu(x) * u, rtol=1e-6, atol=1e-7)
+        assert torch.allclose(O.rmsnorm(x, 1e-5), torch.nn.functional.rms_norm(x, (704,), eps=1e-5), rtol=1e-6, atol=0)
+    else:
+        assert torch.equal(O.silu_mul(x, u), torch.nn.functional.silu(x) * u)
+        assert torch.equal(O.rmsnorm(x, 1e-5), torch.nn.functional.rms_norm(x, (704,), eps=1e-5))
+    q, s = O.rmsnorm_quantize(x, 64, 1e-5, w)
+    q2, s2 = O.quantize(O.rmsnorm(x, 1e-5, w), 64)
+    assert torch.equal(q, q2) and torch.equal(s, s2)
+    q, s = O.silu_mul_quantize(x, u, 64)
+    q2, s2 = O.quantize(O.silu_mul(x, u), 64)
+    assert torch.equal(q, q2) and torch.equal(s, s2)

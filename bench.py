@@ -523,6 +523,20 @@ def tp_bench(dev, rank, world, hbm_gbs):
             if flag.item() == 0:
                 peer = None
 
+        large = None
+        if world > 1 and M > 64:
+            from blockwise_int8_linear_b200.peer import PeerAllReduceLarge
+            from triton_functions import pre_quantize_matmul_block_rowwise_dequantize as pre_mm
+            try:
+                large = PeerAllReduceLarge(M * d, dev, wait_limit_us=20_000_000)
+            except Exception as e:       # no peer mapping on this machine: the NCCL figures stand alone
+                print(f"peer-memory prefill reduction unavailable ({type(e).__name__}: {e})", file=sys.stderr)
+                large = None
+            flag = torch.tensor([1 if large is not None else 0], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if flag.item() == 0:
+                large = None
+
         def pair(i, timed=False, use_peer=False):
             wq_gu, s_gu = gus[i % copies]
             wq_dn, s_dn = dns[i % copies]
@@ -540,6 +554,20 @@ def tp_bench(dev, rank, world, hbm_gbs):
                 y = peer.row_parallel_linear(a, wq_dn, s_dn)
                 if timed:
                     ev[1].record()
+                    ev[2].record()
+                return y
+            if use_peer == 3:
+                # prefill: the GEMM writes its fp32 partial result into the exchange buffer; one kernel per rank sums the ranks
+                # (reduce-scatter by peer loads, all-gather by peer stores) and casts
+                cfg.INPUT_OUTPUT_TORCH_TYPE = torch.float32
+                try:
+                    pre_mm("none", a, wq_dn.t(), s_dn, out=large.partial(M, d))
+                finally:
+                    cfg.INPUT_OUTPUT_TORCH_TYPE = torch.bfloat16
+                if timed:
+                    ev[1].record()
+                y = large.reduce(M, d)
+                if timed:
                     ev[2].record()
                 return y
             cfg.INPUT_OUTPUT_TORCH_TYPE = torch.float32 if world > 1 else torch.bfloat16
@@ -591,6 +619,31 @@ def tp_bench(dev, rank, world, hbm_gbs):
                     "tokens_per_s": M / (ms_pair * 1e-3), "rank_roofline_ms": roof_ms, "frac_of_rank_roofline": roof_ms / ms_pair,
                     "timing": "CUDA events, median of 15 eager steps, max over ranks; " +
                               ("weights rotate over copies larger than L2" if M <= 64 else "operands larger than L2")}
+        if large is not None:
+            for i in range(5):
+                pair(i, use_peer=3)
+            torch.cuda.synchronize()
+            dist.barrier()
+            tot, comp = [], []
+            for i in range(15):
+                dist.barrier()
+                pair(i, timed=True, use_peer=3)
+                ev[2].synchronize()
+                comp.append(ev[0].elapsed_time(ev[1]))
+                tot.append(ev[0].elapsed_time(ev[2]))
+            tot.sort()
+            comp.sort()
+            t = torch.tensor([tot[len(tot) // 2], comp[len(comp) // 2]], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            nv_in = (world - 1) / world * M * d * 4          # bytes a rank loads from its peers; it stores half as many (bf16)
+            out[tag]["peer_reduce_large"] = {
+                "kernel": "bi8_peer_allreduce_large (reduce-scatter by peer loads, all-gather by peer stores, one kernel per rank)",
+                "ms_per_pair": t[0].item(), "ms_reduce": (t[0] - t[1]).item(), "nvlink_bytes_in_per_rank": nv_in,
+                "nvlink_in_gbs": nv_in / ((t[0] - t[1]).item() * 1e-3) / 1e9 if (t[0] - t[1]).item() > 0 else None,
+                "frac_of_770_gbs_peer_copy": nv_in / ((t[0] - t[1]).item() * 1e-3) / 1e9 / 770.0 if (t[0] - t[1]).item() > 0 else None}
+            from blockwise_int8_linear_b200 import _lib
+            _lib.device_status()
+            del large
         if peer is not None:
             # the same pair with the library's peer-memory reduction (one kernel, plain stores over NVLink) instead of NCCL
             for i in range(5):

@@ -328,6 +328,23 @@ int bi8_gemm_dequant_fused_pre(int op, const void* x, const void* x2, int x_dtyp
     return launch_residual_add(C, ldc, residual, ldr, out_dtype, M, N, st);
 }
 
+size_t bi8_peer_allreduce_large_buffer_bytes(int world, int64_t capacity) {
+    if (world < 1 || world > 8 || capacity <= 0 || capacity % 1024 != 0) return 0;
+    return peer_allreduce_large_buffer_bytes(capacity);
+}
+
+size_t bi8_peer_allreduce_large_partial_offset(void) { return peer_allreduce_large_partial_offset(); }
+
+size_t bi8_peer_allreduce_large_out_offset(int64_t capacity) { return peer_allreduce_large_out_offset(capacity); }
+
+int bi8_peer_allreduce_large(void* const* peer_bufs, int rank, int world, int64_t capacity, int64_t M, int64_t N, const void* bias,
+                             int bias_dtype, int out_dtype, unsigned wait_limit_us, void* stream) {
+    if (!peer_bufs) return fail(BI8_ERR_NULL, "peer all-reduce: null pointer");
+    if (!dtype_ok(out_dtype) || (bias && !dtype_ok(bias_dtype & ~BI8_ADDEND_FULL))) return fail(BI8_ERR_DTYPE, "peer all-reduce: unknown dtype code");
+    return launch_peer_allreduce_large(peer_bufs, rank, world, capacity, M, N, bias, bias_dtype, out_dtype, wait_limit_us,
+                                       static_cast<cudaStream_t>(stream));
+}
+
 int bi8_row_parallel_linear_pre(int op, const void* x, const void* x2, int x_dtype, int64_t ldx, const void* norm_weight, float eps,
                                 int8_t* xq, float* sx, const int8_t* Wq, int64_t ldw, const float* sW, float* partial, int64_t M, int64_t N,
                                 int64_t K, int block, void* workspace, size_t workspace_bytes, void* const* peer_bufs, int rank, int world,

@@ -63,6 +63,12 @@ int launch_quantize_pre(int op, const void* x, const void* x2, int dt, int64_t l
                         int64_t M, int64_t K, int block, cudaStream_t st);
 // C[m, n] += R[m, n] in the type of C (C may be R)
 int launch_residual_add(void* C, int64_t ldc, const void* R, int64_t ldr, int dt, int64_t M, int64_t N, cudaStream_t st);
+// prefill-sized sum over ranks: reduce-scatter by peer loads, all-gather by peer stores (peer_reduce_large.cu)
+size_t peer_allreduce_large_buffer_bytes(int64_t capacity);
+size_t peer_allreduce_large_partial_offset();
+size_t peer_allreduce_large_out_offset(int64_t capacity);
+int launch_peer_allreduce_large(void* const* peer_bufs, int rank, int world, int64_t capacity, int64_t M, int64_t N, const void* bias,
+                                int bias_dtype, int out_dtype, unsigned wait_limit_us, cudaStream_t st);
 int launch_dequantize_rowwise(const int8_t* q, const float* s, void* out, int dt, int64_t M, int64_t K,
                               int block, cudaStream_t st);
 

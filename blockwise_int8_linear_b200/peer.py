@@ -19,9 +19,38 @@ import torch.distributed as dist
 
 from . import _lib, block_linear_config
 
-__all__ = ["PeerAllReduce"]
+__all__ = ["PeerAllReduce", "PeerAllReduceLarge"]
 
 _CHUNK = 1024
+
+
+def _exchange_buffers(nbytes: int, device, world: int, group, local: bool):
+    """One zero-filled buffer of `nbytes` per rank, mapped by all ranks of the group: returns (tensors kept alive, symmetric
+    memory handle or None, the eight device addresses the library's calls take).  With one rank, or `local` (a test hook:
+    `world` buffers on this one device), the buffers are ordinary device memory."""
+    if world == 1 or local:
+        bufs = [torch.zeros(nbytes, dtype=torch.uint8, device=device) for _ in range(world)]
+        handle, ptrs = None, [b.data_ptr() for b in bufs]
+    else:
+        # plain peer mappings are all this needs: keep the allocation off NVLink multicast objects
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm
+        pg = group if group is not None else dist.group.WORLD
+        name = pg.group_name
+        enable = getattr(symm, "enable_symm_mem_for_group", None)
+        if enable is not None:
+            try:
+                enable(name)
+            except Exception:       # newer torch versions need no registration
+                pass
+        buf = symm.empty(nbytes, dtype=torch.uint8, device=device)
+        buf.zero_()
+        handle = symm.rendezvous(buf, name)
+        bufs = [buf]
+        ptrs = [int(p) for p in handle.buffer_ptrs]
+        torch.cuda.synchronize(device)
+        dist.barrier(group)         # every rank's buffer is zeroed before anybody's first kernel writes into it
+    return bufs, handle, (ctypes.c_void_p * 8)(*(ptrs + [ptrs[0]] * (8 - len(ptrs))))
 
 
 class PeerAllReduce:
@@ -49,29 +78,7 @@ class PeerAllReduce:
         nbytes = L.bi8_peer_allreduce_buffer_bytes(self.world, self.capacity)
         if nbytes == 0:
             raise ValueError(f"bad exchange buffer geometry: world {self.world}, capacity {self.capacity}")
-        if self.world == 1 or _local_world:
-            self._bufs = [torch.zeros(nbytes, dtype=torch.uint8, device=self.device) for _ in range(self.world)]
-            ptrs = [b.data_ptr() for b in self._bufs]
-        else:
-            # plain peer mappings are all this needs: keep the allocation off NVLink multicast objects
-            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
-            import torch.distributed._symmetric_memory as symm
-            pg = group if group is not None else dist.group.WORLD
-            name = pg.group_name
-            enable = getattr(symm, "enable_symm_mem_for_group", None)
-            if enable is not None:
-                try:
-                    enable(name)
-                except Exception:       # newer torch versions need no registration
-                    pass
-            buf = symm.empty(nbytes, dtype=torch.uint8, device=self.device)
-            buf.zero_()
-            self._handle = symm.rendezvous(buf, name)
-            self._bufs = [buf]
-            ptrs = [int(p) for p in self._handle.buffer_ptrs]
-            torch.cuda.synchronize(self.device)
-            dist.barrier(group)         # every rank's buffer is zeroed before anybody's first kernel writes into it
-        self._ptrs = (ctypes.c_void_p * 8)(*(ptrs + [ptrs[0]] * (8 - len(ptrs))))
+        self._bufs, self._handle, self._ptrs = _exchange_buffers(nbytes, self.device, self.world, group, bool(_local_world))
 
     @staticmethod
     def _addend(bias, residual, m, n, out_dtype):
@@ -155,3 +162,57 @@ class PeerAllReduce:
                                                _lib.stream_ptr())
         _lib.check(rc, "bi8_row_parallel_linear_pre")
         return out.view(*lead, n)
+
+
+class PeerAllReduceLarge:
+    """The same sum for prefill-sized results (``bi8_peer_allreduce_large``): every rank owns one chunk in ``world`` of the
+    result, loads that chunk of every rank's partial result over NVLink, adds in rank order, casts, adds bias or residual
+    and stores the chunk into every rank's output — reduce-scatter by peer loads, all-gather by peer stores, one kernel.
+
+    The partial results and the output live inside the exchange buffer: ``partial(m, n)`` is the fp32 view the GEMM should
+    write into (``pre_quantize_matmul_block_rowwise_dequantize(..., out=...)`` with a float32 output type), ``reduce(m, n)``
+    returns the ``[m, n]`` view of the output region, valid until the next ``reduce``."""
+
+    def __init__(self, capacity: int, device, group=None, wait_limit_us: int = 0, _local_world: int = 0):
+        self.device = torch.device(device)
+        self.wait_limit_us = int(wait_limit_us)
+        self.capacity = -(-int(capacity) // _CHUNK) * _CHUNK
+        if _local_world:
+            self.rank, self.world = 0, _local_world
+        elif dist.is_initialized() and dist.get_world_size(group) > 1:
+            self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        else:
+            self.rank, self.world = 0, 1
+        if self.world > 8:
+            raise ValueError("PeerAllReduceLarge supports at most 8 ranks")
+        L = _lib.lib()
+        nbytes = L.bi8_peer_allreduce_large_buffer_bytes(self.world, self.capacity)
+        if nbytes == 0:
+            raise ValueError(f"bad exchange buffer geometry: world {self.world}, capacity {self.capacity}")
+        self._bufs, self._handle, self._ptrs = _exchange_buffers(nbytes, self.device, self.world, group, bool(_local_world))
+        own = self._bufs[0]
+        p_off, o_off = L.bi8_peer_allreduce_large_partial_offset(), L.bi8_peer_allreduce_large_out_offset(self.capacity)
+        self._partial = own[p_off:p_off + 4 * self.capacity].view(torch.float32)
+        self._out_bytes = own[o_off:o_off + 4 * self.capacity]
+
+    def partial(self, m: int, n: int) -> torch.Tensor:
+        """This rank's ``[m, n]`` float32 partial region (write the GEMM's result here, then call ``reduce``)."""
+        if m * n > self.capacity:
+            raise ValueError(f"{m} x {n} exceeds the capacity {self.capacity}")
+        return self._partial[: m * n].view(m, n)
+
+    def reduce(self, m: int, n: int, bias: torch.Tensor = None, residual: torch.Tensor = None, wait_limit_us: int = None) -> torch.Tensor:
+        """``cast(sum over ranks of partial(m, n)) + bias`` (or ``+ residual``, ``[m, n]`` of the output type, which may be
+        the previous result's view): a view of the output region in ``block_linear_config.INPUT_OUTPUT_TORCH_TYPE``."""
+        if m * n > self.capacity or n % 4:
+            raise ValueError(f"{m} x {n}: exceeds the capacity {self.capacity} or n is not a multiple of 4")
+        out_dtype = block_linear_config.INPUT_OUTPUT_TORCH_TYPE
+        addend, code = PeerAllReduce._addend(bias, residual, m, n, out_dtype)
+        if wait_limit_us is None:
+            wait_limit_us = self.wait_limit_us
+        with torch.cuda.device(self.device):
+            rc = _lib.lib().bi8_peer_allreduce_large(self._ptrs, self.rank, self.world, self.capacity, m, n, _lib.ptr(addend), code,
+                                                     _lib.dtype_code(out_dtype), int(wait_limit_us), _lib.stream_ptr())
+        _lib.check(rc, "bi8_peer_allreduce_large")
+        esz = torch.empty((), dtype=out_dtype).element_size()
+        return self._out_bytes[: m * n * esz].view(out_dtype).view(m, n)

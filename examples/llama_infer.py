@@ -33,6 +33,7 @@ if ROOT not in sys.path:
 import block_linear_config as cfg  # noqa: E402
 from block_linear import BlockInt8Linear  # noqa: E402
 from blockwise_int8_linear_b200.parallel import block_aligned_bounds  # noqa: E402
+from triton_functions import pre_quantize_matmul_block_rowwise_dequantize  # noqa: E402
 
 
 def seeded_weight(out_f, in_f, seed, dev, rows=None, cols=None):
@@ -130,6 +131,25 @@ class Int8Linear(nn.Module):
             peer = rows <= 64 and rows * self.widths[0] <= PEER.capacity
         if peer and FUSE:
             return PEER.row_parallel_linear(x, self.lin.W_int8, self.lin.state_W, op=op, x2=x2, residual=residual)
+        rows = x.numel() // x.shape[-1]
+        if (not peer and self.world > 1 and self.mode == "row" and PEER_LARGE is not None and self.lin is not None
+                and rows * self.widths[0] <= PEER_LARGE.capacity and self.widths[0] % 4 == 0):
+            # prefill: the GEMM writes its fp32 partial result into the exchange buffer, one kernel per rank sums the ranks
+            # (reduce-scatter by peer loads, all-gather by peer stores), casts and adds the residual
+            n = self.widths[0]
+            if not FUSE:
+                x, x2, op = (rms_norm(x) if op == "rmsnorm" else (F.silu(x) * x2 if op == "silu_mul" else x)), None, "none"
+            prev = cfg.INPUT_OUTPUT_TORCH_TYPE
+            cfg.INPUT_OUTPUT_TORCH_TYPE = torch.float32
+            try:
+                pre_quantize_matmul_block_rowwise_dequantize(op, x.reshape(rows, -1), self.lin.W_int8.t(), self.lin.state_W,
+                                                             x2=None if x2 is None else x2.reshape(rows, -1), eps=NORM_EPS,
+                                                             out=PEER_LARGE.partial(rows, n))
+            finally:
+                cfg.INPUT_OUTPUT_TORCH_TYPE = prev
+            res = residual.reshape(rows, n).contiguous() if residual is not None and FUSE else None
+            y = PEER_LARGE.reduce(rows, n, residual=res).clone().view(*x.shape[:-1], n)    # the view lives until the next sum
+            return y if residual is None or FUSE else residual + y
         inp = rms_norm(x) if op == "rmsnorm" else (F.silu(x) * x2 if op == "silu_mul" else x)
         if peer:
             y = PEER.row_parallel_linear(inp, self.lin.W_int8, self.lin.state_W)
@@ -217,6 +237,7 @@ class Layer(nn.Module):
 
 
 PEER = None      # a blockwise_int8_linear_b200.peer.PeerAllReduce while the decode step uses the library's own reduction
+PEER_LARGE = None   # a PeerAllReduceLarge while the prefill's row-parallel layers are summed by the library's own kernel
 
 
 def group_sum(part, dtype, world):
@@ -342,6 +363,19 @@ def run(a, rank, world, dev, eager=False):
     global FUSE
     FUSE = not getattr(a, "no_fuse", False)
     cfg.GROUP_SIZE, cfg.INPUT_OUTPUT_TORCH_TYPE = a.block, torch.bfloat16
+    global PEER_LARGE
+    PEER_LARGE = None
+    if world > 1 and getattr(a, "reduce", "peer") == "peer":
+        from blockwise_int8_linear_b200.peer import PeerAllReduceLarge
+        try:
+            PEER_LARGE = PeerAllReduceLarge(a.batch * a.prompt * a.hidden, dev, wait_limit_us=20_000_000)
+        except Exception as e:                                  # no peer mapping on this machine: NCCL
+            print(f"peer-memory prefill reduction unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
+            PEER_LARGE = None
+        flag = torch.tensor([1 if PEER_LARGE is not None else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)               # all ranks take the same path
+        if flag.item() == 0:
+            PEER_LARGE = None
     model = Llama(a, dev, rank, world)
     ids = torch.randint(0, a.vocab, (a.batch, a.prompt), generator=torch.Generator().manual_seed(4000)).to(dev)
     max_len = a.prompt + a.decode
@@ -434,10 +468,10 @@ def run(a, rank, world, dev, eager=False):
     torch.cuda.synchronize()
     t_decode = time.perf_counter() - t0
     toks = torch.cat(out, dim=1)
-    if PEER is not None:
+    if PEER is not None or PEER_LARGE is not None:
         from blockwise_int8_linear_b200 import _lib
         _lib.device_status()                                      # raises if a bounded flag wait gave up
-        PEER = None
+        PEER = PEER_LARGE = None
     return {
         "model": f"llama-arch {a.layers}x{a.hidden} ffn {a.ffn} vocab {a.vocab}, random init N(0,0.02), BlockInt8Linear block {a.block}",
         "n_gpus": world, "batch": a.batch, "prompt": a.prompt, "decode": a.decode,

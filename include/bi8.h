@@ -219,6 +219,24 @@ BI8_API int bi8_peer_allreduce(void* const* peer_bufs, int rank, int world, int6
                        int64_t M, int64_t N, const void* bias, int bias_dtype, void* out, int out_dtype,
                        unsigned wait_limit_us, void* stream);
 
+/* The same sum for prefill-sized results, where pushing every rank's whole partial result to every rank would move `world`
+ * times the bytes: every rank owns one chunk in `world` of the result, loads that chunk of every rank's partial result over
+ * NVLink, adds in rank order, casts, adds bias or addend, and stores the chunk into every rank's output (reduce-scatter by
+ * peer loads, all-gather by peer stores, in one kernel per rank; (world-1)/world of the fp32 result in and of the cast
+ * result out per rank).  The partial results and the outputs live INSIDE the peer-mapped buffers:
+ *   peer_bufs[r]  rank r's buffer, bi8_peer_allreduce_large_buffer_bytes(world, capacity) bytes, zero-filled once, mapped
+ *                 by every rank.  At byte offset bi8_peer_allreduce_large_partial_offset() lies the rank's partial region
+ *                 ([M,N] fp32, contiguous: hand it to the GEMM as its output C), at
+ *                 bi8_peer_allreduce_large_out_offset(capacity) the output region, where the call leaves [M,N] of
+ *                 out_dtype, contiguous, complete on every rank when the kernel ends; it stays valid until the next call.
+ * bias / bias_dtype (BI8_ADDEND_FULL for a residual, which may be the output region itself) and wait_limit_us as in
+ * bi8_peer_allreduce.  The kernel waits (bounded) for the other ranks at its start and at its end. */
+BI8_API size_t bi8_peer_allreduce_large_buffer_bytes(int world, int64_t capacity);
+BI8_API size_t bi8_peer_allreduce_large_partial_offset(void);
+BI8_API size_t bi8_peer_allreduce_large_out_offset(int64_t capacity);
+BI8_API int bi8_peer_allreduce_large(void* const* peer_bufs, int rank, int world, int64_t capacity, int64_t M, int64_t N,
+                             const void* bias, int bias_dtype, int out_dtype, unsigned wait_limit_us, void* stream);
+
 /* A whole row-parallel layer in one call: quantize x [M,K] (this rank's slice of the input features), multiply with this
  * rank's weight slice Wq [N,K] / sW, and sum the ranks' fp32 partial results as bi8_peer_allreduce does.  For M <= 64
  * (decode) the kernel that adds the weight-streaming GEMM's tile parts hands its sums straight to the exchange, so the layer

@@ -123,6 +123,53 @@ def _peer_worker(rank, world, port, results):
             assert torch.equal(peer(part, residual=res), want)
             got = peer.row_parallel_linear(gu[:, :k], wq, sw, op="silu_mul", x2=gu[:, k:], residual=res)
             assert torch.equal(got, want), (m, k, n, (got.float() - want.float()).abs().max().item())
+        # prefill-sized sums: reduce-scatter by peer loads, all-gather by peer stores, the partial result written into the
+        # exchange buffer by the GEMM itself; against the push kernel (same order of the sum: bit-identical) and NCCL
+        from blockwise_int8_linear_b200.peer import PeerAllReduceLarge
+        from triton_functions import pre_quantize_matmul_block_rowwise_dequantize
+        large = PeerAllReduceLarge(300 * 4096, dev)
+        small = PeerAllReduce(300 * 4096, dev)
+        for it, (m, n) in enumerate(((300, 4096), (64, 1000), (1, 4), (257, 2052), (300, 4096))):
+            part = torch.randn((m, n), device=dev, generator=g)
+            large.partial(m, n).copy_(part)
+            res = torch.randn((m, n), device=dev, generator=torch.Generator(device=dev).manual_seed(8)).to(torch.bfloat16)
+            kind = it % 3
+            got = large.reduce(m, n, bias=bias[:n] if kind == 1 else None, residual=res if kind == 2 else None).clone()
+            want = small(part, bias=bias[:n] if kind == 1 else None, residual=res if kind == 2 else None)
+            assert torch.equal(got, want), (m, n, kind, (got.float() - want.float()).abs().max().item())
+            ref = part.clone()
+            dist.all_reduce(ref)
+            ref = ref.to(torch.bfloat16)
+            ref = ref + bias[:n] if kind == 1 else (ref + res if kind == 2 else ref)
+            assert (got.float() - ref.float()).abs().max().item() <= 2.0 ** -6 * ref.float().abs().max().item()
+        # a row-parallel layer at prefill size: the GEMM's fp32 output goes straight into the exchange buffer
+        m, k, n = 300, 1024, 4096
+        w = (torch.randn((n, k), device=dev, generator=g) * 0.02).to(torch.bfloat16)
+        wq, sw = quantize_block_rowwise(w)
+        x = torch.randn((m, k), device=dev, generator=g).to(torch.bfloat16)
+        cfg.INPUT_OUTPUT_TORCH_TYPE = torch.float32
+        part = quantize_matmul_block_rowwise_dequantize(x, wq.t(), sw)
+        pre_quantize_matmul_block_rowwise_dequantize("none", x, wq.t(), sw, out=large.partial(m, n))
+        cfg.INPUT_OUTPUT_TORCH_TYPE = torch.bfloat16
+        assert torch.equal(large.reduce(m, n), small(part))
+        # replayed from a graph, output fed back as the next call's residual (a residual stream living in the buffer)
+        stream_view = large.reduce(m, n).clone()
+        large.partial(m, n).copy_(part)
+        gl = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            large.reduce(m, n)
+        torch.cuda.current_stream().wait_stream(side)
+        with torch.cuda.graph(gl):
+            outv = large.reduce(m, n, residual=large.reduce(m, n))
+        expect = small(part)
+        expect = small(part, residual=expect)
+        for _ in range(3):
+            gl.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(outv, expect)
+        del stream_view
         # replayed from a graph: the sequence number continues on the device
         part = torch.randn((8, 4096), device=dev, generator=g)
         out = torch.empty((8, 4096), device=dev, dtype=torch.bfloat16)
@@ -201,6 +248,24 @@ def test_peer_allreduce_one_rank_and_bounded_wait():
         want = res + quantize_matmul_block_rowwise_dequantize(torch.nn.functional.silu(gu[:, :1024]) * gu[:, 1024:], wq.t(), sw)
         assert torch.equal(big.row_parallel_linear(gu[:, :1024], wq, sw, op="silu_mul", x2=gu[:, 1024:], residual=res), want)
     assert _lib.device_status() == 0
+    # the prefill-sized kernel with one rank, and its bounded waits with a second rank that never runs
+    from blockwise_int8_linear_b200.peer import PeerAllReduceLarge
+    big1 = PeerAllReduceLarge(300 * 4096, DEV)
+    p300 = torch.randn((300, 4096), device=DEV)
+    r300 = torch.randn((300, 4096), device=DEV).to(torch.bfloat16)
+    for _ in range(3):
+        big1.partial(300, 4096).copy_(p300)
+        assert torch.equal(big1.reduce(300, 4096, residual=r300), p300.to(torch.bfloat16) + r300)
+        assert torch.equal(big1.reduce(300, 4096, bias=bias), p300.to(torch.bfloat16) + bias)
+    assert _lib.device_status() == 0
+    alone = PeerAllReduceLarge(8 * 4096, DEV, _local_world=2)
+    alone.partial(8, 4096).copy_(part)
+    alone.reduce(8, 4096, wait_limit_us=2000)
+    with pytest.raises(RuntimeError):
+        _lib.device_status()                      # BI8_ERR_TIMEOUT: the other rank's `ready` flag never came
+    assert _lib.device_status() == 0
+    big1.partial(8, 4096).copy_(part)
+    assert torch.equal(big1.reduce(8, 4096), part.to(torch.bfloat16))
     lonely = PeerAllReduce(8 * 4096, DEV, _local_world=2)
     out = torch.full((8, 4096), 7.0, device=DEV, dtype=torch.bfloat16)
     lonely(part, out=out, wait_limit_us=2000)

@@ -12,14 +12,16 @@ With N > 1 (launched by torchrun, one rank per GPU) every rank runs the same ste
 batch of tokens: the layer is data-parallel in the token dimension, there is no collective on the
 path, so scaling is weak and ``value`` is the sum over ranks divided by the slowest rank's time.
 The partitionings that do communicate are measured beside it at the same N (``roofline.tp``,
-``roofline.models``): the Llama MLP pair sharded column-/row-parallel with its NCCL all-reduce, the
-Llama-architecture inference driver (tensor parallel) and the GPT-2 training driver (data parallel).
+``roofline.models``): the Llama MLP pair sharded column-/row-parallel with its NCCL all-reduce and with the
+library's own peer-memory sums in its place (``peer_reduce``, ``peer_reduce_fused`` for decode, ``peer_reduce_large``
+for prefill), the Llama-architecture inference driver (tensor parallel) and the GPT-2 training driver (data parallel).
 
 Prints ONE JSON line.  Besides the headline it carries
   roofline      the GEMM kernel alone (CUDA events around its launches inside the timed region), and inside it
                 kernels (memory-bound kernels and the small-M GEMM rows against the HBM roof), sustained (the GEMM
                 back to back for two seconds), cublas_bf16_ms (torch.matmul on the same shape, comparator only),
-                tp and models (see above)
+                fused_producers (the quantizers with RMSNorm / SiLU*mul fused in front and the residual sum behind,
+                against the separate kernels), tp and models (see above)
   e2e           the same step through the public Python API with host buffers (pinned H2D of x, D2H of y)
   cpu_baseline  the CPU restatement of the reference timed on this host on a bounded sample (rank 0, N = 1)
   extra         the full sweep tables the rows in roofline.kernels are taken from
@@ -635,12 +637,15 @@ def tp_bench(dev, rank, world, hbm_gbs):
             comp.sort()
             t = torch.tensor([tot[len(tot) // 2], comp[len(comp) // 2]], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            nv_in = (world - 1) / world * M * d * 4          # bytes a rank loads from its peers; it stores half as many (bf16)
+            # per rank and direction: it loads (world-1)/world of the fp32 result from its peers and receives (world-1)/world of
+            # the bf16 result they store into its output; outwards it serves the same loads and issues the same stores
+            nv = (world - 1) / world * M * d * (4 + 2)
+            ms_red = (t[0] - t[1]).item()
             out[tag]["peer_reduce_large"] = {
                 "kernel": "bi8_peer_allreduce_large (reduce-scatter by peer loads, all-gather by peer stores, one kernel per rank)",
-                "ms_per_pair": t[0].item(), "ms_reduce": (t[0] - t[1]).item(), "nvlink_bytes_in_per_rank": nv_in,
-                "nvlink_in_gbs": nv_in / ((t[0] - t[1]).item() * 1e-3) / 1e9 if (t[0] - t[1]).item() > 0 else None,
-                "frac_of_770_gbs_peer_copy": nv_in / ((t[0] - t[1]).item() * 1e-3) / 1e9 / 770.0 if (t[0] - t[1]).item() > 0 else None}
+                "ms_per_pair": t[0].item(), "ms_reduce": ms_red, "nvlink_bytes_per_direction_per_rank": nv,
+                "nvlink_gbs_per_direction": nv / (ms_red * 1e-3) / 1e9 if ms_red > 0 else None,
+                "frac_of_770_gbs_peer_copy": nv / (ms_red * 1e-3) / 1e9 / 770.0 if ms_red > 0 else None}
             from blockwise_int8_linear_b200 import _lib
             _lib.device_status()
             del large

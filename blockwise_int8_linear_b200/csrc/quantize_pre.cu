@@ -113,11 +113,30 @@ __device__ __forceinline__ void quantize_unit(const float* y, bool valid, bool s
     for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(y[e]));
 #pragma unroll
     for (int off = 1; off < LPB; off <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-    if (!valid) return;
     BlockQ bq;
     bq.set(amax, short_mantissa);
-    const uint32_t lo = pack4(bq.q(y[0]), bq.q(y[1]), bq.q(y[2]), bq.q(y[3]));
-    const uint32_t hi = pack4(bq.q(y[4]), bq.q(y[5]), bq.q(y[6]), bq.q(y[7]));
+    // the exact-division shortcut on packed pairs when every block of the warp qualifies (a lane without a unit does not
+    // count); else the scalar form with its per-block choice
+    const bool warp_fast = __all_sync(0xffffffffu, bq.fast || !valid);
+    if (!valid) return;
+    uint32_t b[8];
+    if (warp_fast) {
+        const uint64_t r2 = f2_pack(bq.rcp, bq.rcp), ns2 = f2_pack(-amax, -amax);
+        const uint64_t c127 = f2_pack(127.0f, 127.0f), cmagic = f2_pack(kMagic, kMagic), cone = f2_pack(1.0f, 1.0f);
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+            const uint64_t v2 = f2_pack(y[2 * h], y[2 * h + 1]);
+            const uint64_t q0 = f2_mul(v2, r2);
+            const uint64_t e = f2_fma(ns2, q0, v2);
+            const uint64_t yq = f2_fma(e, r2, q0);
+            f2_bits(f2_fma(f2_mul(c127, yq), cone, cmagic), b[2 * h], b[2 * h + 1]);
+        }
+    } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) b[e] = bq.q(y[e]);
+    }
+    const uint32_t lo = pack4(b[0], b[1], b[2], b[3]);
+    const uint32_t hi = pack4(b[4], b[5], b[6], b[7]);
     int8_t* dst = q + (int64_t)m * K + k;
     if (vec && k + 8 <= K) {
         *reinterpret_cast<uint2*>(dst) = make_uint2(lo, hi);
@@ -134,14 +153,15 @@ __device__ __forceinline__ void quantize_unit(const float* y, bool valid, bool s
 // to kPreHold * THREADS * 8 elements stay in registers between the passes; longer rows are read again.  THREADS = 128
 // for rows of up to 4096 elements: a row is in flight for a load latency plus a reduction, so what bounds a large
 // batch is the number of rows resident per SM (ten CTAs of 128 threads against four of 256).
-template <int QB, int THREADS>
-__global__ void __launch_bounds__(THREADS, THREADS == 128 ? 10 : 4) rmsnorm_quantize_kernel(const void* __restrict__ x, int dt, int64_t ldx,
+template <int QB, int THREADS, int DT>
+__global__ void __launch_bounds__(THREADS, THREADS == 128 ? 10 : 4) rmsnorm_quantize_kernel(const void* __restrict__ x, int64_t ldx,
                                                                        const void* __restrict__ weight, float eps,
                                                                        int8_t* __restrict__ q, float* __restrict__ sx, int M, int K,
                                                                        int nb, int vec_in, int vec_out) {
     asm volatile("griddepcontrol.wait;" ::: "memory");           // a no-op unless launched as a programmatic dependent
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr int LPB = QB / 8;
+    constexpr int dt = DT;                                        // the element type is a template parameter: no per-element tests
     __shared__ float warp_sum[THREADS / 32];
     const int m = blockIdx.x, tid = threadIdx.x;
     const int upr = nb * LPB;                                   // units per row, padded to whole blocks
@@ -224,14 +244,15 @@ __global__ void __launch_bounds__(THREADS, THREADS == 128 ? 10 : 4) rmsnorm_quan
 }
 
 // One thread per unit of eight elements, as in the decode quantizer.
-template <int QB>
+template <int QB, int DT>
 __global__ void __launch_bounds__(kPreThreads) silu_mul_quantize_kernel(const void* __restrict__ gate, const void* __restrict__ up,
-                                                                        int dt, int64_t ldx, int8_t* __restrict__ q,
+                                                                        int64_t ldx, int8_t* __restrict__ q,
                                                                         float* __restrict__ sx, int M, int K, int nb, int vec_in,
                                                                         int vec_out) {
     asm volatile("griddepcontrol.wait;" ::: "memory");           // a no-op unless launched as a programmatic dependent
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr int LPB = QB / 8;
+    constexpr int dt = DT;
     const int upr = nb * LPB;
     const int64_t u = (int64_t)blockIdx.x * kPreThreads + threadIdx.x;
     const int m = (int)(u / upr), k = (int)(u % upr) * 8;
@@ -305,11 +326,15 @@ int launch_quantize_pre(int op, const void* x, const void* x2, int dt, int64_t l
         const bool narrow = (int64_t)nb * (block / 8) <= kPreHold * 128 && M > 1024;
         cfg.gridDim = dim3((unsigned)M);
         cfg.blockDim = dim3(narrow ? 128 : 256);
+#define BI8_PRE_RMS_T(QB, T)                                                                                                          \
+    do {                                                                                                                             \
+        if (dt == BI8_BF16) BI8_CUDA_TRY(cudaLaunchKernelEx(&cfg, rmsnorm_quantize_kernel<QB, T, BI8_BF16>, x, ldx, weight, eps, q, sx, Mi, Ki, nb, vec_in, vec_out)); \
+        else if (dt == BI8_F16) BI8_CUDA_TRY(cudaLaunchKernelEx(&cfg, rmsnorm_quantize_kernel<QB, T, BI8_F16>, x, ldx, weight, eps, q, sx, Mi, Ki, nb, vec_in, vec_out)); \
+        else BI8_CUDA_TRY(cudaLaunchKernelEx(&cfg, rmsnorm_quantize_kernel<QB, T, BI8_F32>, x, ldx, weight, eps, q, sx, Mi, Ki, nb, vec_in, vec_out)); \
+    } while (0)
 #define BI8_PRE_RMS(QB)                                                                                                              \
-    if (narrow)                                                                                                                      \
-        BI8_CUDA_TRY(cudaLaunchKernelEx(&cfg, rmsnorm_quantize_kernel<QB, 128>, x, dt, ldx, weight, eps, q, sx, Mi, Ki, nb, vec_in, vec_out)); \
-    else                                                                                                                             \
-        BI8_CUDA_TRY(cudaLaunchKernelEx(&cfg, rmsnorm_quantize_kernel<QB, 256>, x, dt, ldx, weight, eps, q, sx, Mi, Ki, nb, vec_in, vec_out))
+    if (narrow) BI8_PRE_RMS_T(QB, 128);                                                                                              \
+    else BI8_PRE_RMS_T(QB, 256)
         switch (block) {
             case 32: BI8_PRE_RMS(32); break;
             case 64: BI8_PRE_RMS(64); break;
@@ -317,12 +342,18 @@ int launch_quantize_pre(int op, const void* x, const void* x2, int dt, int64_t l
             default: return fail(BI8_ERR_BLOCK, "quantize_pre supports block 32, 64, 128 (got %d)", block);
         }
 #undef BI8_PRE_RMS
+#undef BI8_PRE_RMS_T
     } else if (op == BI8_PRE_SILU_MUL) {
         if (!x2) return fail(BI8_ERR_NULL, "quantize_pre: the gated activation needs its second operand");
         const int64_t units = M * nb * (block / 8);
         cfg.gridDim = dim3((unsigned)((units + kPreThreads - 1) / kPreThreads));
         cfg.blockDim = dim3(kPreThreads);
-#define BI8_PRE_SILU(QB) BI8_CUDA_TRY(cudaLaunchKernelEx(&cfg, silu_mul_quantize_kernel<QB>, x, x2, dt, ldx, q, sx, Mi, Ki, nb, vec_in, vec_out))
+#define BI8_PRE_SILU(QB)                                                                                                             \
+    do {                                                                                                                             \
+        if (dt == BI8_BF16) BI8_CUDA_TRY(cudaLaunchKernelEx(&cfg, silu_mul_quantize_kernel<QB, BI8_BF16>, x, x2, ldx, q, sx, Mi, Ki, nb, vec_in, vec_out)); \
+        else if (dt == BI8_F16) BI8_CUDA_TRY(cudaLaunchKernelEx(&cfg, silu_mul_quantize_kernel<QB, BI8_F16>, x, x2, ldx, q, sx, Mi, Ki, nb, vec_in, vec_out)); \
+        else BI8_CUDA_TRY(cudaLaunchKernelEx(&cfg, silu_mul_quantize_kernel<QB, BI8_F32>, x, x2, ldx, q, sx, Mi, Ki, nb, vec_in, vec_out)); \
+    } while (0)
         switch (block) {
             case 32: BI8_PRE_SILU(32); break;
             case 64: BI8_PRE_SILU(64); break;

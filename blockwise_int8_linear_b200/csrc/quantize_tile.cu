@@ -81,23 +81,6 @@ struct Pk<__half> {
     }
 };
 
-__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
-    uint64_t d;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
-    return d;
-}
-__device__ __forceinline__ void f2_bits(uint64_t v, uint32_t& lo, uint32_t& hi) { asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v)); }
-__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
-    uint64_t d;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
-    uint64_t d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
-}
-
 // Quantizer of a pair of values with (possibly different) block scales, on packed fp32 pairs.  The same operations, in
 // the same order and each rounded on its own, as BlockQ::q: q0 = x*r, e = fma(-s, q0, x), y = fma(e, r, q0),
 // z = 127*y, z + magic (written as fma(z, 1, magic) so that the multiply cannot be contracted into the addition).

@@ -140,3 +140,42 @@ def test_gpt2_driver_training_step_against_oracle():
             _close(rec["gx"].reshape(gx_ref.shape), gx_ref, identical=0.99, rel=2.0 ** -7)
         _close(m.weight.grad.cpu().reshape(gw_ref.shape), gw_ref, identical=0.99, rel=2.0 ** -7)
     assert_clean_device()
+
+
+def test_hf_llama_with_every_linear_replaced_against_oracle():
+    """An unmodified transformers LlamaForCausalLM (toy size, random weights) after
+    model.apply(replace_linear_with_blockwise_int8): all 7 x layers + 1 nn.Linear modules become BlockInt8Linear, the model's
+    own forward and generate run on them, and the logits agree with the same model whose linear layers are evaluated by the
+    CPU oracle on the same int8 weights; the int8 model stays close to the bf16 model it was made from."""
+    import block_linear_config as cfg
+    from block_linear import BlockInt8Linear
+    H = _load("hf_llama_infer")
+    set_config(64, torch.bfloat16)
+    a = argparse.Namespace(layers=2, hidden=256, heads=4, ffn=704, vocab=512, batch=2, prompt=24, decode=6, block=64, skip_dense=False)
+    dev = torch.device(DEV)
+    dense = H.build(a, dev)
+    ids = torch.randint(0, a.vocab, (a.batch, a.prompt), generator=torch.Generator().manual_seed(4000)).to(dev)
+    with torch.no_grad():
+        dense_logits = dense(ids).logits
+    res, model = H.run(a, dev)                                   # same seed: the same weights, swapped and quantized
+    assert res["int8"]["linear_layers_replaced"] == 7 * a.layers + 1
+    assert len(res["int8"]["first_tokens"]) == a.decode and len(res["bf16_dense"]["first_tokens"]) == a.decode
+    assert not any(type(m) is torch.nn.Linear for m in model.modules())
+    with torch.no_grad():
+        logits = model(ids).logits
+    # close to the bf16 model: per-layer int8 noise of about 1 % over two layers
+    assert (logits.float() - dense_logits.float()).abs().max().item() <= 0.1 * dense_logits.float().abs().max().item()
+    linears = [m for m in model.modules() if isinstance(m, BlockInt8Linear)]
+    for lin in linears:
+        def oracle_infer(x, lin=lin):
+            X = x.reshape(-1, x.size(-1)).cpu()
+            xq, xs = O.quantize(X, a.block)
+            y = O.gemm(xq, lin.W_int8.cpu().t(), xs, lin.state_W.cpu(), None, a.block, cfg.INPUT_OUTPUT_TORCH_TYPE)
+            return y.to(x.device).view(*x.size()[:-1], -1)
+        lin.infer = oracle_infer
+    with torch.no_grad():
+        ref = model(ids).logits
+    for lin in linears:
+        del lin.infer
+    _close(logits.cpu(), ref.cpu(), identical=0.90, rel=2.0 ** -6)
+    assert_clean_device()

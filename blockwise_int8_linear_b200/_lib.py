@@ -26,7 +26,7 @@ EXPORTS = [
     "bi8_gemm_dequant_fused_quant", "bi8_mma_peak_probe", "bi8_gemm_dequant_static", "bi8_gemm_static_scratch_bytes",
     "bi8_gemm_wait_selftest", "bi8_stream_capture_id", "bi8_quantize_rowwise_pre", "bi8_gemm_dequant_fused_pre",
     "bi8_row_parallel_linear_pre", "bi8_peer_allreduce_large", "bi8_peer_allreduce_large_buffer_bytes",
-    "bi8_peer_allreduce_large_partial_offset", "bi8_peer_allreduce_large_out_offset",
+    "bi8_peer_allreduce_large_partial_offset", "bi8_peer_allreduce_large_out_offset", "bi8_rope_cache_append",
 ]
 ADDEND_FULL = 0x100
 PRE_NONE, PRE_RMSNORM, PRE_SILU_MUL = 0, 1, 2
@@ -68,6 +68,7 @@ def lib() -> ctypes.CDLL:
         L.bi8_peer_allreduce_large_partial_offset.restype = sz
         L.bi8_peer_allreduce_large_out_offset.argtypes = [i64]
         L.bi8_peer_allreduce_large_out_offset.restype = sz
+        L.bi8_rope_cache_append.argtypes = [vp, i32, vp, vp, vp, vp, vp, i64, i64, i64, i64, vp]
         L.bi8_peer_allreduce.argtypes = [c.POINTER(vp), i32, i32, i64, vp, i64, i64, vp, i32, vp, i32, c.c_uint, vp]
         L.bi8_gemm_dequant.argtypes = [vp, i64, vp, i64, vp, vp, vp, i32, vp, i64, i32, i64, i64, i64, i32, vp, sz, i32, vp]
         L.bi8_gemm_workspace_bytes.argtypes = [i64, i64, i64, i32]

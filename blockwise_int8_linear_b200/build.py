@@ -18,7 +18,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libbi8.so")
-SOURCES = ["api.cu", "quantize.cu", "quantize_tile.cu", "gemm_generic.cu", "gemm_tc.cu", "gemm_tc_skinny.cu", "gemm_smallm.cu", "no_alloc.cu", "peer_reduce.cu", "peer_reduce_large.cu", "quantize_pre.cu"]
+SOURCES = ["api.cu", "quantize.cu", "quantize_tile.cu", "gemm_generic.cu", "gemm_tc.cu", "gemm_tc_skinny.cu", "gemm_smallm.cu", "no_alloc.cu", "peer_reduce.cu", "peer_reduce_large.cu", "quantize_pre.cu", "rope_cache.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",

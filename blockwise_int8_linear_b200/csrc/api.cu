@@ -390,6 +390,18 @@ int bi8_row_parallel_linear(const void* x, int x_dtype, int64_t ldx, int8_t* xq,
                                        wait_limit_us, flags, stream);
 }
 
+int bi8_rope_cache_append(const void* qkv, int dtype, const float* cis, const long long* pos, void* q_out, void* kcache, void* vcache,
+                          int64_t B, int64_t H, int64_t D, int64_t max_len, void* stream) {
+    if (dtype != BI8_BF16 && dtype != BI8_F16) return fail(BI8_ERR_DTYPE, "rope_cache_append: bf16 or fp16 activations (got code %d)", dtype);
+    if (B < 0 || H < 0 || D < 0 || D % 2 != 0 || max_len <= 0 || B > 0x7fffffff || H > 0x7fffffff || D > 0x7fffffff || max_len > 0x7fffffff)
+        return fail(BI8_ERR_SHAPE, "rope_cache_append: bad shape B %lld H %lld D %lld max_len %lld", (long long)B, (long long)H, (long long)D, (long long)max_len);
+    if (B == 0 || H == 0 || D == 0) return BI8_OK;
+    if (!qkv || !cis || !pos || !q_out || !kcache || !vcache) return fail(BI8_ERR_NULL, "rope_cache_append: null pointer");
+    if (!aligned(qkv, 4) || !aligned(q_out, 4) || !aligned(kcache, 4) || !aligned(vcache, 4) || !aligned(cis, 8) || !aligned(pos, 8))
+        return fail(BI8_ERR_ALIGN, "rope_cache_append: pointer not aligned to an element pair");
+    return launch_rope_cache_append(qkv, dtype, cis, pos, q_out, kcache, vcache, B, H, D, max_len, static_cast<cudaStream_t>(stream));
+}
+
 int bi8_stream_capture_id(void* stream, unsigned long long* id) {
     if (!id) return fail(BI8_ERR_NULL, "stream_capture_id: null output");
     cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;

@@ -69,6 +69,9 @@ size_t peer_allreduce_large_partial_offset();
 size_t peer_allreduce_large_out_offset(int64_t capacity);
 int launch_peer_allreduce_large(void* const* peer_bufs, int rank, int world, int64_t capacity, int64_t M, int64_t N, const void* bias,
                                 int bias_dtype, int out_dtype, unsigned wait_limit_us, cudaStream_t st);
+// rotary embedding of q and k and the append of k and v to the caches for one decode step (rope_cache.cu)
+int launch_rope_cache_append(const void* qkv, int dt, const float* cis, const long long* pos, void* q_out, void* kcache, void* vcache,
+                             int64_t B, int64_t H, int64_t D, int64_t max_len, cudaStream_t st);
 int launch_dequantize_rowwise(const int8_t* q, const float* s, void* out, int dt, int64_t M, int64_t K,
                               int block, cudaStream_t st);
 

@@ -32,6 +32,7 @@ if ROOT not in sys.path:
 
 import block_linear_config as cfg  # noqa: E402
 from block_linear import BlockInt8Linear  # noqa: E402
+from blockwise_int8_linear_b200.decode_ops import rope_cache_append  # noqa: E402
 from blockwise_int8_linear_b200.parallel import block_aligned_bounds  # noqa: E402
 from triton_functions import pre_quantize_matmul_block_rowwise_dequantize  # noqa: E402
 
@@ -201,6 +202,16 @@ class Layer(nn.Module):
         B, T, _ = x.shape
         hl, hd = self.heads_local, self.head_dim
         qkv = self.qkv.fused(x, "rmsnorm").view(B, T, 3, hl, hd)
+        if pos_dev is not None and T == 1 and FUSE and self.qkv.lin is not None and self.kcache is not None:
+            # decode: rotation of q and k and the append of k and v to the caches in one launch
+            q = rope_cache_append(qkv.view(B, 3, hl, hd), cis, pos_dev, self.kcache, self.vcache)
+            att = F.scaled_dot_product_attention(q, self.kcache, self.vcache, attn_mask=mask)
+            att = att.transpose(1, 2).reshape(B, T, hl * hd)
+            if residual is not None and self.o.fusable():
+                return self.o.fused(att, "none", residual=residual)
+            if residual is not None:
+                return self.o.summed(att, residual=residual)
+            return self.o.summed(att) if summed else self.o.partial(att)
         qk = rope(qkv[:, :, :2], cis)                                   # q and k in one pass: [B, T, 2, H, D]
         q, k, v = qk[:, :, 0].transpose(1, 2), qk[:, :, 1].transpose(1, 2), qkv[:, :, 2].transpose(1, 2)
         if self.kcache is None:
@@ -261,13 +272,17 @@ class Llama(nn.Module):
         self.layers = nn.ModuleList(Layer(i, a, dev, rank, world, ops) for i in range(a.layers))
         self.head = Int8Linear(a.hidden, (a.vocab,), (99,), dev, "col", rank, world, a.block, ops)
         self.world, self.vocab, self.block = world, a.vocab, a.block
-        self.cis = rope_table(a.prompt + a.decode, a.head_dim, dev)
-        self.positions = torch.arange(a.prompt + a.decode, device=dev)
+        self.cis = rope_table(a.prompt + a.decode + 16, a.head_dim, dev)
+        self.positions = torch.arange(a.prompt + a.decode + 16, device=dev)
 
     def positions_of(self, ids, pos0, max_len, pos_dev):
         if pos_dev is None:
             return self.cis[pos0:pos0 + ids.shape[1]], None
-        return self.cis.index_select(0, pos_dev), (self.positions[:max_len] <= pos_dev).view(1, 1, 1, max_len)
+        # an additive mask in the activation type, built once per step: given a boolean mask, every layer's attention call
+        # would convert it again (two fills and a select per layer)
+        keep = (self.positions[:max_len] <= pos_dev).view(1, 1, 1, max_len)
+        mask = torch.zeros((1, 1, 1, max_len), device=ids.device, dtype=self.emb.dtype).masked_fill_(~keep, float("-inf"))
+        return self.cis.index_select(0, pos_dev), mask
 
     def local_logits(self, x):
         """[B, 1, V_local] of this rank, padded with -inf to the widest shard (all_gather wants equal sizes)."""
@@ -378,8 +393,8 @@ def run(a, rank, world, dev, eager=False):
             PEER_LARGE = None
     model = Llama(a, dev, rank, world)
     ids = torch.randint(0, a.vocab, (a.batch, a.prompt), generator=torch.Generator().manual_seed(4000)).to(dev)
-    max_len = a.prompt + a.decode
-    torch.cuda.synchronize()
+    max_len = -(-(a.prompt + a.decode) // 16) * 16                # cache length: a multiple of 16, so that the attention call
+    torch.cuda.synchronize()                                      # takes the additive mask as it is (no padded copy per layer)
     t0 = time.perf_counter()
     model(ids, 0, max_len)                                        # first call: lazy initialisation, allocator growth
     torch.cuda.synchronize()

@@ -180,6 +180,17 @@ BI8_API int bi8_gemm_dequant_fused_pre(int op, const void* x, const void* x2, in
                                int out_dtype, int64_t M, int64_t N, int64_t K, int block, void* workspace,
                                size_t workspace_bytes, int flags, void* stream);
 
+/* Model-side helper for a decode step (no counterpart in the reference, which has no model code): rotary embedding of q and
+ * k and the append of k and v to the caches, in one launch, for the tensors a fused q/k/v projection leaves.
+ *   qkv      [B, 3, H, D] of dtype (bf16 or fp16), contiguous: q, k, v of one new token per sequence
+ *   cis      [D/2] pairs (cos, sin) fp32 of this step's position: (x0 + i x1) * (cos + i sin) per (even, odd) feature pair,
+ *            fp32 products and sums each rounded on their own, result rounded to dtype
+ *   pos      device address of the position (int64): row of the caches that receives k and v; read by the kernel, so the
+ *            launch can be replayed from a CUDA graph while the position advances; outside [0, max_len) nothing is written
+ *   q_out    [B, H, D]; kcache, vcache [B, H, max_len, D], all of dtype, contiguous. */
+BI8_API int bi8_rope_cache_append(const void* qkv, int dtype, const float* cis, const long long* pos, void* q_out, void* kcache,
+                          void* vcache, int64_t B, int64_t H, int64_t D, int64_t max_len, void* stream);
+
 /* Capture sequence number of `stream` if it is being captured into a CUDA graph, 0 otherwise (no counterpart in the
  * reference).  A host layer that caches workspaces uses it to give every captured graph a scratch buffer of its own:
  * an address baked into a graph must not be shared with another graph that may be replayed on a different stream. */

@@ -194,3 +194,62 @@ def test_module_infer_pre_and_graph_replay():
         torch.cuda.synchronize()
         assert torch.equal(stream, expect)
     assert_clean_device()
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(8, 32, 128, 545), (2, 4, 64, 30), (1, 1, 2, 3)])
+def test_rope_cache_append(dt, shape):
+    """One decode step's rotary embedding and cache append in one launch: bit-identical to the same arithmetic written with
+    tensor operations (fp32 products and sums rounded one by one), within one step of the activation type of torch's
+    complex multiply, and the caches change in row `pos` only; replayed from a CUDA graph the row follows the position."""
+    from blockwise_int8_linear_b200.decode_ops import rope_cache_append
+    b, h, d, max_len = shape
+    g = torch.Generator(device=DEV).manual_seed(b * 1000 + d)
+    qkv = torch.randn((b, 3, h, d), device=DEV, generator=g).to(dt)
+    ang = torch.rand((d // 2,), device=DEV, generator=g) * 6.28
+    cis = torch.polar(torch.ones_like(ang), ang)
+    kc = torch.randn((b, h, max_len, d), device=DEV, generator=g).to(dt)
+    vc = torch.randn((b, h, max_len, d), device=DEV, generator=g).to(dt)
+    k0, v0 = kc.clone(), vc.clone()
+    pos = torch.tensor([max_len - 2], device=DEV, dtype=torch.long)
+    q = rope_cache_append(qkv, cis, pos, kc, vc)
+
+    def rotate(x):                       # [b, h, d] -> rotated, explicit real arithmetic
+        x0, x1 = x[..., 0::2].float(), x[..., 1::2].float()
+        c, s = cis.real, cis.imag
+        return torch.stack(((x0 * c) - (x1 * s), (x0 * s) + (x1 * c)), dim=-1).flatten(-2).to(dt)
+
+    assert torch.equal(q[:, :, 0], rotate(qkv[:, 0]))
+    p = pos.item()
+    assert torch.equal(kc[:, :, p], rotate(qkv[:, 1])) and torch.equal(vc[:, :, p], qkv[:, 2])
+    keep = torch.ones(max_len, dtype=torch.bool, device=DEV)
+    keep[p] = False
+    assert torch.equal(kc[:, :, keep], k0[:, :, keep]) and torch.equal(vc[:, :, keep], v0[:, :, keep])
+    # torch's complex multiply (the driver's prefill path)
+    xc = torch.view_as_complex(qkv[:, 0].float().reshape(b, h, d // 2, 2))
+    ref = torch.view_as_real(xc * cis).flatten(-2).to(dt)
+    step = 2.0 ** -7 if dt == torch.bfloat16 else 2.0 ** -10
+    assert (q[:, :, 0].float() - ref.float()).abs().max().item() <= step * ref.float().abs().max().item()
+    # a position outside the cache writes nothing; a replayed graph follows the position
+    k1 = kc.clone()
+    rope_cache_append(qkv, cis, torch.tensor([max_len], device=DEV), kc, vc)
+    assert torch.equal(kc, k1)
+    pos.fill_(0)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        rope_cache_append(qkv, cis, pos, kc, vc)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        rope_cache_append(qkv, cis, pos, kc, vc)
+        pos.add_(1)
+    kc.copy_(k0)
+    pos.fill_(0)
+    for _ in range(min(3, max_len)):
+        graph.replay()
+    torch.cuda.synchronize()
+    want = rotate(qkv[:, 1])
+    for r in range(min(3, max_len)):
+        assert torch.equal(kc[:, :, r], want)
+    assert_clean_device()

@@ -10,7 +10,13 @@ Tensor parallel (N):   python -m torch.distributed.run --nproc-per-node N --mast
 
 Tensor parallelism follows ``blockwise_int8_linear_b200.parallel``: q/k/v, gate/up and the LM head are split over output
 features (bit-identical columns), o_proj and down_proj over input features on block boundaries (11008 = 172 blocks of 64 is
-split 22/21 blocks for 8 ranks) with fp32 partial results summed by one all-reduce per layer half.
+split 22/21 blocks for 8 ranks) with fp32 partial results summed once per layer half: by the library's peer-memory kernels
+(``--reduce peer``, the default: the decode step is then one CUDA graph per rank, and the prefill's sums are a reduce-scatter
+by peer loads and an all-gather by peer stores) or by NCCL (``--reduce nccl``).
+
+The elementwise steps between the layer's kernels run inside the library's calls (``BlockInt8Linear.infer_pre``: RMSNorm and
+``silu(gate) * up`` in the quantizer, the residual sum in the kernel that writes the GEMM's result; rotary embedding and
+cache append of a decode step in one kernel); ``--no-fuse`` runs them as torch kernels, for comparison.
 """
 from __future__ import annotations
 

@@ -73,6 +73,59 @@ def test_fused_entry_point_validates_and_flags_match_the_header(L):
     assert f(M=0) == 0
 
 
+def test_new_entry_points_validate_before_cuda(L):
+    """The entry points around the layer (fused producer steps, residual, prefill-sized peer sum, rotary/cache helper):
+    every argument check runs before the first CUDA call, so it can be exercised without a GPU."""
+    from blockwise_int8_linear_b200 import _lib
+    header = open(os.path.join(ROOT, "include", "bi8.h")).read()
+    pre = {name: int(value) for name, value in re.findall(r"#define BI8_PRE_(\w+)\s+(\d+)", header)}
+    assert pre == {"NONE": 0, "RMSNORM": 1, "SILU_MUL": 2}
+    assert (_lib.PRE_NONE, _lib.PRE_RMSNORM, _lib.PRE_SILU_MUL) == (0, 1, 2)
+    assert int(re.search(r"#define BI8_ADDEND_FULL\s+(0x[0-9a-fA-F]+)", header).group(1), 16) == _lib.ADDEND_FULL
+    vp = ctypes.c_void_p
+    one = vp(256)
+    err = lambda: L.bi8_last_error_string().decode()
+    q = lambda **kw: L.bi8_quantize_rowwise_pre(kw.get("op", 1), kw.get("x", one), kw.get("x2", None), kw.get("dt", 0), kw.get("ldx", 64),
+                                                None, 1e-5, one, one, kw.get("M", 4), 64, 64, None)
+    assert q(dt=9) == -1
+    assert q(op=5) == -4 and "operation" in err()
+    assert q(ldx=8) == -4
+    assert q(x=None) == -8
+    assert q(op=2) == -8                                   # the gated activation needs its second operand
+    assert q(x=vp(257)) == -3
+    assert q(M=0) == 0
+    f = lambda **kw: L.bi8_gemm_dequant_fused_pre(kw.get("op", 1), one, None, 0, 64, None, 1e-5, kw.get("xq", one), one, one, 64, one,
+                                                  None, 0, kw.get("res", None), kw.get("ldr", 64), kw.get("C", one), 64, kw.get("dt", 0),
+                                                  kw.get("M", 8), 64, 64, 64, None, 0, 0, None)
+    assert f(xq=None) == -7
+    assert f(res=one, ldr=8) == -4
+    assert f(dt=7) == -1
+    assert f(res=vp(257)) == -3
+    assert f(res=vp(256 + 64), C=vp(256)) == -4 and "overlap" in err()      # overlapping, not the same tensor
+    assert f(M=0) == 0
+    assert L.bi8_peer_allreduce_large_buffer_bytes(2, 1000) == 0            # capacity must be a multiple of 1024
+    assert L.bi8_peer_allreduce_large_buffer_bytes(9, 1024) == 0
+    n = L.bi8_peer_allreduce_large_buffer_bytes(2, 4096)
+    assert n == L.bi8_peer_allreduce_large_out_offset(4096) + 4 * 4096
+    assert L.bi8_peer_allreduce_large_out_offset(4096) == L.bi8_peer_allreduce_large_partial_offset() + 4 * 4096
+    bufs = (vp * 8)(*([256] * 8))
+    big = lambda **kw: L.bi8_peer_allreduce_large(bufs, kw.get("rank", 0), kw.get("world", 2), kw.get("cap", 4096), kw.get("M", 4),
+                                                  kw.get("N", 64), None, 0, kw.get("dt", 0), 0, None)
+    assert big(dt=9) == -1
+    assert big(rank=2) == -4
+    assert big(cap=1000) == -4
+    assert big(N=6) == -4                                  # N a multiple of 4
+    assert big(M=100) == -4                                # does not fit the capacity
+    r = lambda **kw: L.bi8_rope_cache_append(kw.get("qkv", one), kw.get("dt", 0), one, one, one, one, one, kw.get("B", 2), 4,
+                                             kw.get("D", 64), kw.get("max_len", 16), None)
+    assert r(dt=1) == -1                                   # 16-bit activations only
+    assert r(D=63) == -4
+    assert r(max_len=0) == -4
+    assert r(qkv=None) == -8
+    assert r(qkv=vp(258)) == -3
+    assert r(B=0) == 0
+
+
 def test_python_surface_mirrors_reference_names():
     import block_linear
     import block_linear_config
@@ -85,6 +138,13 @@ def test_python_surface_mirrors_reference_names():
         assert callable(getattr(triton_functions, name))
     for name in ("replace_linear_with_blockwise_int8", "fast_matmul", "blockwise_int8_linear", "BlockInt8Linear"):
         assert hasattr(block_linear, name)
+    # additions without a counterpart in the reference
+    for name in ("quantize_block_colwise", "quantize_block_dual", "quantize_matmul_block_rowwise_dequantize",
+                 "rmsnorm_quantize_block_rowwise", "silu_mul_quantize_block_rowwise", "pre_quantize_matmul_block_rowwise_dequantize"):
+        assert callable(getattr(triton_functions, name))
+    assert callable(block_linear.BlockInt8Linear.infer_pre)
+    from blockwise_int8_linear_b200 import decode_ops, peer
+    assert callable(decode_ops.rope_cache_append) and hasattr(peer, "PeerAllReduce") and hasattr(peer, "PeerAllReduceLarge")
     assert block_linear.BlockLinear is block_linear.BlockInt8Linear
     assert issubclass(block_linear.BlockInt8Linear, torch.nn.Linear)
     # defaults of the reference (block_linear_config.py:3-5)

@@ -157,3 +157,34 @@ def test_llama_driver_tensor_parallel_world2_equals_one_rank():
         p.join(timeout=600)
     assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
     assert dict(results) == {0: "ok", 1: "ok"}
+
+
+@pytest.mark.parametrize("world", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("count", [4, 1000, 1024, 4096 * 7 + 8, 300 * 4096, 4096 * 4096])
+def test_prefill_sized_peer_sum_covers_every_chunk_once(world, count):
+    """The index arithmetic of bi8_peer_allreduce_large, restated on the host (the kernel itself needs peer-mapped GPUs):
+    chunk c of 1024 values belongs to rank c mod world; a rank's CTA b takes the rank's chunks b, b + grid, ... in groups of
+    U = 8 / W per loop iteration.  Over all ranks, CTAs and iterations every chunk must come up exactly once, whatever the
+    grid size the launcher picked, and no element index may pass `count`."""
+    chunk = 1024
+    chunks = -(-count // chunk)
+    w_bound = 2 if world <= 2 else (4 if world <= 4 else 8)
+    u = 8 // w_bound
+    my_chunks = -(-chunks // world)
+    seen = [0] * chunks
+    for sms_times_occupancy in (1, 7, 148 * 3):
+        seen = [0] * chunks
+        want = -(-my_chunks // u)
+        grid = max(1, min(want, sms_times_occupancy))
+        for rank in range(world):
+            for block in range(grid):
+                k0 = block
+                while rank + world * k0 < chunks:
+                    for j in range(u):
+                        c = rank + world * (k0 + j * grid)
+                        if c < chunks:
+                            assert c % world == rank
+                            assert c * chunk < count          # the chunk's first element exists; the tail is cut per thread
+                            seen[c] += 1
+                    k0 += grid * u
+        assert seen == [1] * chunks, (world, count, grid)
